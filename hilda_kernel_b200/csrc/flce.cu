@@ -1,0 +1,392 @@
+// FusedLinearCrossEntropy for sm_100a: loss, d(hidden) and d(W) of CE(hidden @ W^T, targets) without
+// ever holding the full [BT, V] logits.
+//
+// What it replaces: fused_linear_cross_entropy_forward (kernels/fused_linear_cross_entropy.py:103-171
+// of hilda-kernel), a host loop over row chunks of {cuBLAS GEMM, Triton CE kernel, two more cuBLAS
+// GEMMs, grad_weight += ...}. Here the tokens are processed in row chunks too, but
+//   1. the lm_head GEMM runs on tcgen05/TMEM fed by TMA and its epilogue rounds the logits to the
+//      compute dtype (as the reference's cuBLAS call does), stores them to a [chunk, V] scratch and
+//      produces the online (max, sum-exp) statistics per (row, 256-column tile) in the same pass;
+//   2. a small kernel merges the tile statistics per row (this is the only data a vocab-parallel
+//      run has to exchange: max, sum-exp and the target logit per row);
+//   3. one streaming pass turns the scratch into dlogits = (softmax - onehot) * scale in place;
+//   4. dHidden = dlogits @ W and dW += dlogits^T @ hidden run on the same tcgen05 kernel with
+//      MN-major operands (no transposed copies); dW is accumulated across chunks in fp32 and
+//      rounded once at the end (the reference accumulates in the 16-bit dtype).
+#include "tcgen05_gemm.cuh"
+#include "reduce_kernels.cuh"
+
+namespace hilda {
+
+constexpr float FL_LOG2E = 1.4426950408889634f;
+constexpr float FL_LN2 = 0.6931471805599453f;
+
+// One warp per row: merge the per-tile (max2, sum2) pairs; fetch the target logit from the scratch.
+// rowstat layout [3][rows]: natural-log max, sum of exp(x - max), target logit (0 if not in this shard).
+__global__ void __launch_bounds__(256)
+flce_row_stats_kernel(const float2* __restrict__ stats, int64_t stats_ld, int n_tiles, const uint16_t* __restrict__ logits,
+                      int64_t pitch, const int64_t* __restrict__ targets, float* __restrict__ rowstat, int64_t rows,
+                      int64_t V, int64_t vocab_start, int is_bf16) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  float m = -INFINITY;
+  for (int t = lane; t < n_tiles; t += 32) m = fmaxf(m, stats[row * stats_ld + t].x);
+  m = warp_max(m);
+  float s = 0.f;
+  for (int t = lane; t < n_tiles; t += 32) {
+    const float2 v = stats[row * stats_ld + t];
+    if (v.x != -INFINITY) s += v.y * exp2f(v.x - m);
+  }
+  s = warp_sum(s);
+  if (lane == 0) {
+    const int64_t t = targets[row] - vocab_start;
+    float xt = 0.f;
+    if (t >= 0 && t < V) {
+      const uint16_t raw = logits[row * pitch + t];
+      xt = is_bf16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(__ushort_as_half(raw));
+    }
+    rowstat[row] = m * FL_LN2;
+    rowstat[rows + row] = s;
+    rowstat[2 * rows + row] = xt;
+  }
+}
+
+// lse = m + log(s); loss = lse - x_t on valid rows, 0 on ignored rows.
+__global__ void __launch_bounds__(256)
+flce_finalize_kernel(const float* __restrict__ rowstat, const int64_t* __restrict__ targets, int64_t ignore_index,
+                     float* __restrict__ lse, float* __restrict__ loss_rows, int64_t rows) {
+  const int64_t row = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (row >= rows) return;
+  const float l = rowstat[row] + logf(rowstat[rows + row]);
+  lse[row] = l;
+  loss_rows[row] = (targets[row] != ignore_index) ? (l - rowstat[2 * rows + row]) : 0.f;
+}
+
+// In place on the scratch: x -> (exp(x - lse) - [col == target]) * scale; ignored rows -> 0.
+template <typename T>
+__global__ void __launch_bounds__(256)
+flce_dlogits_kernel(T* __restrict__ logits, int64_t pitch, const float* __restrict__ lse,
+                    const int64_t* __restrict__ targets, int64_t ignore_index, const int* __restrict__ n_valid,
+                    int64_t V, int64_t vocab_start) {
+  constexpr int VEC = VT<T>::N;
+  const int64_t row = blockIdx.y;
+  T* xr = logits + row * pitch;
+  const int64_t tgt = targets[row];
+  const int64_t n_vec = (V + VEC - 1) / VEC;  // pitch is a multiple of 256: a ragged last vector stays in the row
+  const int64_t v_begin = (int64_t)blockIdx.x * 256 * 4;
+  if (tgt == ignore_index) {
+    const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t v = v_begin + u * 256 + threadIdx.x;
+      if (v < n_vec) st16(xr + v * VEC, z);
+    }
+    return;
+  }
+  const float scale = n_valid ? 1.0f / fmaxf((float)(*n_valid), 1.0f) : 1.0f;
+  const float l2 = lse[row] * FL_LOG2E;
+  const int64_t t = tgt - vocab_start;
+  const int64_t tvec = (t >= 0 && t < V) ? t / VEC : -1;
+  const int tsub = (int)(t - tvec * VEC);
+  uint4 xv[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int64_t v = v_begin + u * 256 + threadIdx.x;
+    xv[u] = (v < n_vec) ? ld16(xr + v * VEC) : make_uint4(0, 0, 0, 0);
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int64_t v = v_begin + u * 256 + threadIdx.x;
+    float f[VEC];
+    VT<T>::unpack(xv[u], f);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) f[j] = scale * ex2_fast(fmaf(f[j], FL_LOG2E, -l2));
+    if (v == tvec) {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j)
+        if (j == tsub) f[j] -= scale;
+    }
+    if (v < n_vec) st16(xr + v * VEC, VT<T>::pack(f));
+  }
+}
+
+static inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+
+static int flce_logits(const void* hidden, const void* W, void* logits, float* stats, int64_t rows, int64_t H,
+                       int64_t V, int is_bf16, int* status, cudaStream_t st) {
+  GemmParams p = {};
+  p.M = (int)rows; p.N = (int)V; p.K = (int)H; p.m_fast = 1; p.is_bf16 = is_bf16;
+  p.C16 = logits; p.ldc16 = round_up(V, BN);
+  p.stats = reinterpret_cast<float2*>(stats); p.stats_ld = (V + BN - 1) / BN;
+  p.status = status;
+  return launch_gemm<false, false, EPI_LOGITS_STATS>(hidden, H, W, H, p, st);
+}
+
+static int flce_grad_hidden(const void* dlogits, const void* W, void* dh16, float* dh32, int64_t rows, int64_t H,
+                            int64_t V, int is_bf16, int* status, cudaStream_t st) {
+  GemmParams p = {};
+  p.M = (int)rows; p.N = (int)H; p.K = (int)V; p.m_fast = 1; p.is_bf16 = is_bf16; p.status = status;
+  const int64_t pitch = round_up(V, BN);
+  if (dh16) {
+    p.C16 = dh16; p.ldc16 = H;
+    return launch_gemm<false, true, EPI_STORE16>(dlogits, pitch, W, H, p, st);
+  }
+  p.C32 = dh32; p.ldc32 = H;
+  return launch_gemm<false, true, EPI_STORE32>(dlogits, pitch, W, H, p, st);
+}
+
+// mode 0: dw32 = D^T h; 1: dw32 += D^T h; 2: dw16 = dw32 + D^T h; 3: dw16 = D^T h
+static int flce_grad_weight(const void* dlogits, const void* hidden, float* dw32, void* dw16, int mode, int64_t rows,
+                            int64_t H, int64_t V, int is_bf16, int* status, cudaStream_t st) {
+  GemmParams p = {};
+  p.M = (int)V; p.N = (int)H; p.K = (int)rows; p.m_fast = 0; p.is_bf16 = is_bf16; p.status = status;
+  p.C32 = dw32; p.ldc32 = H; p.C16 = dw16; p.ldc16 = H;
+  const int64_t pitch = round_up(V, BN);
+  switch (mode) {
+    case 0: return launch_gemm<true, true, EPI_STORE32>(dlogits, pitch, hidden, H, p, st);
+    case 1: return launch_gemm<true, true, EPI_ACCUM32>(dlogits, pitch, hidden, H, p, st);
+    case 2: return launch_gemm<true, true, EPI_ACCUM_FINAL16>(dlogits, pitch, hidden, H, p, st);
+    case 3: return launch_gemm<true, true, EPI_STORE16>(dlogits, pitch, hidden, H, p, st);
+  }
+  return HILDA_ERR_ARG;
+}
+
+static int flce_check(int64_t rows, int64_t H, int64_t V, int dtype) {
+  if (dtype != HILDA_BF16 && dtype != HILDA_F16) return HILDA_ERR_DTYPE;
+  if (rows <= 0 || H <= 0 || V <= 0 || rows > 0x7fffff00LL || V > 0x7fffff00LL || H > 0x7fffff00LL) return HILDA_ERR_SIZE;
+  if (H % 8 != 0) return HILDA_ERR_SIZE;  // TMA needs 16-byte row pitches
+  return HILDA_OK;
+}
+
+}  // namespace hilda
+
+using namespace hilda;
+
+extern "C" {
+
+int64_t hilda_flce_logits_pitch(int64_t V) { return round_up(V, BN); }
+int64_t hilda_flce_padded_rows(int64_t rows) { return round_up(rows, BM); }
+int64_t hilda_flce_stat_tiles(int64_t V) { return (V + BN - 1) / BN; }
+
+int hilda_count_valid(const int64_t* targets, int64_t n, int64_t ignore_index, int* out, void* stream) {
+  if (!targets || !out) return HILDA_ERR_NULL;
+  count_valid_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(targets, n, ignore_index, out);
+  HILDA_LAUNCH_CHECK();
+  return HILDA_OK;
+}
+
+int hilda_flce_logits(const void* hidden, const void* W, void* logits, float* stats, int64_t rows, int64_t H,
+                      int64_t V, int dtype, int* status, void* stream) {
+  if (!hidden || !W || !logits || !stats) return HILDA_ERR_NULL;
+  int rc = flce_check(rows, H, V, dtype);
+  if (rc) return rc;
+  return flce_logits(hidden, W, logits, stats, rows, H, V, dtype == HILDA_BF16, status, (cudaStream_t)stream);
+}
+
+int hilda_flce_row_stats(const float* stats, const void* logits, const int64_t* targets, float* rowstat, int64_t rows,
+                         int64_t V, int64_t vocab_start, int dtype, void* stream) {
+  if (!stats || !logits || !targets || !rowstat) return HILDA_ERR_NULL;
+  if (rows <= 0) return HILDA_OK;
+  const int n_tiles = (int)((V + BN - 1) / BN);
+  flce_row_stats_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<const float2*>(stats), n_tiles, n_tiles, reinterpret_cast<const uint16_t*>(logits),
+      round_up(V, BN), targets, rowstat, rows, V, vocab_start, dtype == HILDA_BF16);
+  HILDA_LAUNCH_CHECK();
+  return HILDA_OK;
+}
+
+int hilda_flce_finalize(const float* rowstat, const int64_t* targets, int64_t ignore_index, float* lse,
+                        float* loss_rows, int64_t rows, void* stream) {
+  if (!rowstat || !targets || !lse || !loss_rows) return HILDA_ERR_NULL;
+  if (rows <= 0) return HILDA_OK;
+  flce_finalize_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, (cudaStream_t)stream>>>(rowstat, targets, ignore_index,
+                                                                                        lse, loss_rows, rows);
+  HILDA_LAUNCH_CHECK();
+  return HILDA_OK;
+}
+
+int hilda_flce_dlogits(void* logits, const float* lse, const int64_t* targets, int64_t ignore_index,
+                       const int* n_valid, int64_t rows, int64_t V, int64_t vocab_start, int dtype, void* stream) {
+  if (!logits || !lse || !targets) return HILDA_ERR_NULL;
+  if (rows <= 0) return HILDA_OK;
+  if (rows > 65535LL * 65535LL) return HILDA_ERR_SIZE;
+  const int64_t pitch = round_up(V, BN);
+  const int64_t n_vec = (V + 7) / 8;
+  cudaStream_t st = (cudaStream_t)stream;
+  // grid.y is limited to 65535 rows per launch
+  for (int64_t r0 = 0; r0 < rows; r0 += 65535) {
+    const int64_t nr = (rows - r0 < 65535) ? rows - r0 : 65535;
+    dim3 grid((unsigned)((n_vec + 1023) / 1024), (unsigned)nr);
+    if (dtype == HILDA_BF16)
+      flce_dlogits_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(reinterpret_cast<__nv_bfloat16*>(logits) + r0 * pitch, pitch,
+                                                             lse + r0, targets + r0, ignore_index, n_valid, V, vocab_start);
+    else if (dtype == HILDA_F16)
+      flce_dlogits_kernel<__half><<<grid, 256, 0, st>>>(reinterpret_cast<__half*>(logits) + r0 * pitch, pitch, lse + r0,
+                                                      targets + r0, ignore_index, n_valid, V, vocab_start);
+    else return HILDA_ERR_DTYPE;
+    HILDA_LAUNCH_CHECK();
+  }
+  return HILDA_OK;
+}
+
+int hilda_flce_grad_hidden(const void* dlogits, const void* W, void* dh16, float* dh32, int64_t rows, int64_t H,
+                           int64_t V, int dtype, int* status, void* stream) {
+  if (!dlogits || !W || (!dh16 && !dh32)) return HILDA_ERR_NULL;
+  int rc = flce_check(rows, H, V, dtype);
+  if (rc) return rc;
+  return flce_grad_hidden(dlogits, W, dh16, dh32, rows, H, V, dtype == HILDA_BF16, status, (cudaStream_t)stream);
+}
+
+int hilda_flce_grad_weight(const void* dlogits, const void* hidden, float* dw32, void* dw16, int mode, int64_t rows,
+                           int64_t H, int64_t V, int dtype, int* status, void* stream) {
+  if (!dlogits || !hidden) return HILDA_ERR_NULL;
+  if ((mode != 3 && !dw32) || (mode >= 2 && !dw16)) return HILDA_ERR_NULL;
+  int rc = flce_check(rows, H, V, dtype);
+  if (rc) return rc;
+  return flce_grad_weight(dlogits, hidden, dw32, dw16, mode, rows, H, V, dtype == HILDA_BF16, status,
+                          (cudaStream_t)stream);
+}
+
+// Default rows per chunk: the scratch [chunk, pitch(V)] stays at or below 1 GiB (so at most a
+// quarter of the full logits for the 16384 x 128256 benchmark shape), in multiples of 128 rows.
+int64_t hilda_flce_default_chunk_rows(int64_t BT, int64_t H, int64_t V) {
+  (void)H;
+  const int64_t pitch = round_up(V > 0 ? V : 1, BN);
+  int64_t rows = ((int64_t)1 << 30) / (pitch * 2);
+  rows = rows / BM * BM;
+  if (rows < BM) rows = BM;
+  if (rows > BT) rows = BT;
+  return rows > 0 ? rows : 1;
+}
+
+// Workspace layout (all offsets 256-byte aligned), for chunk_rows rows per chunk:
+//   [0]      int status, int n_valid
+//   scratch  16-bit [padded(chunk_rows), pitch(V)]
+//   stats    float2 [chunk_rows, tiles(V)]
+//   rowstat  float [3, chunk_rows]
+//   lse      float [chunk_rows]
+//   loss     float [BT]            (when the caller passes loss_rows == null)
+//   dw32     float [V, H]          (only when BT > chunk_rows and gradients are requested)
+static int64_t flce_ws_layout(int64_t BT, int64_t H, int64_t V, int64_t chunk, int with_grad, int64_t* off) {
+  int64_t o = 256;
+  off[0] = o; o = round_up(o + round_up(chunk, BM) * round_up(V, BN) * 2, 256);
+  off[1] = o; o = round_up(o + chunk * ((V + BN - 1) / BN) * 8, 256);
+  off[2] = o; o = round_up(o + 3 * chunk * 4, 256);
+  off[3] = o; o = round_up(o + chunk * 4, 256);
+  off[4] = o; o = round_up(o + BT * 4, 256);
+  off[5] = o;
+  if (with_grad && BT > chunk) o = round_up(o + V * H * 4, 256);
+  return o;
+}
+
+int64_t hilda_flce_workspace_bytes(int64_t BT, int64_t H, int64_t V, int64_t chunk_rows, int with_grad) {
+  if (BT <= 0 || H <= 0 || V <= 0) return 256;
+  if (chunk_rows <= 0) chunk_rows = hilda_flce_default_chunk_rows(BT, H, V);
+  if (chunk_rows > BT) chunk_rows = BT;
+  int64_t off[6];
+  return flce_ws_layout(BT, H, V, chunk_rows, with_grad, off);
+}
+
+// The whole operator on one device. reduction: 0 none (loss_rows gets the per-row loss), 1 mean,
+// 2 sum (loss_out scalar). dh / dw null => loss only. Returns after enqueueing; the int at
+// workspace[0] is non-zero afterwards if a bounded wait inside a GEMM ran out.
+int hilda_fused_linear_cross_entropy_fwd(const void* hidden, const void* W, const int64_t* targets, float* loss_out,
+                                         float* loss_rows, void* dh, void* dw, void* workspace, int64_t BT, int64_t H,
+                                         int64_t V, int64_t ignore_index, int reduction, int64_t chunk_rows, int dtype,
+                                         void* stream) {
+  if (!hidden || !W || !targets || !workspace) return HILDA_ERR_NULL;
+  if (reduction < 0 || reduction > 2) return HILDA_ERR_ARG;
+  if (reduction == 0 ? !loss_rows : !loss_out) return HILDA_ERR_NULL;
+  if ((dh == nullptr) != (dw == nullptr)) return HILDA_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (BT == 0) {
+    if (loss_out && cudaMemsetAsync(loss_out, 0, 4, st) != cudaSuccess) return HILDA_ERR_CUDA;
+    if (dw && cudaMemsetAsync(dw, 0, (size_t)V * H * 2, st) != cudaSuccess) return HILDA_ERR_CUDA;
+    return HILDA_OK;
+  }
+  int rc = flce_check(BT, H, V, dtype);
+  if (rc) return rc;
+  if (!aligned16(hidden) || !aligned16(W) || (dh && (!aligned16(dh) || !aligned16(dw)))) return HILDA_ERR_ALIGN;
+  const int with_grad = dh != nullptr;
+  if (chunk_rows <= 0) chunk_rows = hilda_flce_default_chunk_rows(BT, H, V);
+  if (chunk_rows > BT) chunk_rows = BT;
+  int64_t off[6];
+  flce_ws_layout(BT, H, V, chunk_rows, with_grad, off);
+  char* ws = reinterpret_cast<char*>(workspace);
+  int* status = reinterpret_cast<int*>(ws);
+  int* n_valid = status + 1;
+  void* scratch = ws + off[0];
+  float* stats = reinterpret_cast<float*>(ws + off[1]);
+  float* rowstat = reinterpret_cast<float*>(ws + off[2]);
+  float* lse = reinterpret_cast<float*>(ws + off[3]);
+  float* rows_loss = loss_rows ? loss_rows : reinterpret_cast<float*>(ws + off[4]);
+  float* dw32 = reinterpret_cast<float*>(ws + off[5]);
+  const int is_bf16 = dtype == HILDA_BF16;
+  const int64_t esz = 2;
+
+  if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) return HILDA_ERR_CUDA;
+  count_valid_kernel<<<1, 1024, 0, st>>>(targets, BT, ignore_index, n_valid);
+  HILDA_LAUNCH_CHECK();
+  const int64_t n_chunks = (BT + chunk_rows - 1) / chunk_rows;
+  for (int64_t c = 0; c < n_chunks; ++c) {
+    const int64_t r0 = c * chunk_rows;
+    const int64_t rows = (BT - r0 < chunk_rows) ? BT - r0 : chunk_rows;
+    const char* hc = reinterpret_cast<const char*>(hidden) + r0 * H * esz;
+    rc = flce_logits(hc, W, scratch, stats, rows, H, V, is_bf16, status, st);
+    if (rc) return rc;
+    rc = hilda_flce_row_stats(stats, scratch, targets + r0, rowstat, rows, V, 0, dtype, stream);
+    if (rc) return rc;
+    rc = hilda_flce_finalize(rowstat, targets + r0, ignore_index, lse, rows_loss + r0, rows, stream);
+    if (rc) return rc;
+    if (!with_grad) continue;
+    rc = hilda_flce_dlogits(scratch, lse, targets + r0, ignore_index, reduction == 1 ? n_valid : nullptr, rows, V, 0,
+                            dtype, stream);
+    if (rc) return rc;
+    rc = flce_grad_hidden(scratch, W, reinterpret_cast<char*>(dh) + r0 * H * esz, nullptr, rows, H, V, is_bf16, status, st);
+    if (rc) return rc;
+    int mode;
+    if (n_chunks == 1) mode = 3;
+    else if (c == 0) mode = 0;
+    else if (c == n_chunks - 1) mode = 2;
+    else mode = 1;
+    rc = flce_grad_weight(scratch, hc, dw32, dw, mode, rows, H, V, is_bf16, status, st);
+    if (rc) return rc;
+  }
+  if (reduction != 0) {
+    sum_rows_kernel<<<1, 1024, 0, st>>>(rows_loss, BT, n_valid, reduction == 1 ? 1 : 0, loss_out);
+    HILDA_LAUNCH_CHECK();
+  }
+  return HILDA_OK;
+}
+
+// Plain GEMM through the same kernel, for validating operand layouts against a library matmul.
+// A is [M,K] (a_mn=0) or stored [K,M] (a_mn=1); B is [N,K] (b_mn=0) or stored [K,N] (b_mn=1);
+// exactly one of c16 / c32 is written. mn_lbo/mn_sbo = 0 selects the defaults.
+int hilda_debug_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* c16, float* c32, int64_t ldc, int M,
+                     int N, int K, int a_mn, int b_mn, int dtype, int mn_lbo, int mn_sbo, int* status, void* stream) {
+  if (!A || !B || (!c16 && !c32)) return HILDA_ERR_NULL;
+  if (dtype != HILDA_BF16 && dtype != HILDA_F16) return HILDA_ERR_DTYPE;
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K; p.m_fast = 1; p.is_bf16 = dtype == HILDA_BF16; p.status = status;
+  p.C16 = c16; p.ldc16 = ldc; p.C32 = c32; p.ldc32 = ldc;
+  p.mn_lbo = (uint32_t)mn_lbo; p.mn_sbo = (uint32_t)mn_sbo;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int key = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
+  if (c16) {
+    switch (key) {
+      case 0: return launch_gemm<false, false, EPI_STORE16>(A, lda, B, ldb, p, st);
+      case 1: return launch_gemm<false, true, EPI_STORE16>(A, lda, B, ldb, p, st);
+      case 2: return launch_gemm<true, false, EPI_STORE16>(A, lda, B, ldb, p, st);
+      default: return launch_gemm<true, true, EPI_STORE16>(A, lda, B, ldb, p, st);
+    }
+  }
+  switch (key) {
+    case 0: return launch_gemm<false, false, EPI_STORE32>(A, lda, B, ldb, p, st);
+    case 1: return launch_gemm<false, true, EPI_STORE32>(A, lda, B, ldb, p, st);
+    case 2: return launch_gemm<true, false, EPI_STORE32>(A, lda, B, ldb, p, st);
+    default: return launch_gemm<true, true, EPI_STORE32>(A, lda, B, ldb, p, st);
+  }
+}
+
+}  // extern "C"

@@ -1,0 +1,436 @@
+// RMSNorm and FusedAddRMSNorm, forward and backward, for sm_100a.
+//
+// Behaviour follows the reference kernels (kernels/rms_norm.py:78-142, :200-254 and
+// kernels/fused_add_rms_norm.py:40-77, :122-165 of hilda-kernel):
+//   forward : s = x (+ r, rounded to the input dtype); rstd = 1/sqrt(mean(s^2)+eps) in fp32;
+//             y = round_T(s * rstd) * w; only rstd is saved.
+//   backward: m = dy*w; dx = rstd*m - rstd^3 * (sum(m*s)/H) * s (+ ds); dW = sum_rows dy*(s*rstd).
+// Design: one CTA owns one row at a time and keeps it in registers as 128-bit vectors, so each
+// tensor is read once and written once. dW is accumulated per CTA in registers over the rows it
+// owns, written as one fp32 partial row per CTA, and reduced by a second small kernel (fixed
+// order, no atomics, bit-reproducible).
+#include "common.cuh"
+
+namespace hilda {
+
+// W (dtype only known at run time) -> VEC floats starting at element e0 (e0 % VEC == 0).
+template <int VEC>
+__device__ __forceinline__ void load_w_vec(const void* W, int w_dt, int e0, float* out) {
+  if (w_dt == HILDA_F32) {
+    const float* p = reinterpret_cast<const float*>(W) + e0;
+#pragma unroll
+    for (int j = 0; j < VEC; j += 4) VT<float>::unpack(ld16(p + j), out + j);
+  } else if (w_dt == HILDA_BF16) {
+    const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(W) + e0;
+    if constexpr (VEC == 8) {
+      VT<__nv_bfloat16>::unpack(ld16(p), out);
+    } else {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) out[j] = __bfloat162float(p[j]);
+    }
+  } else {
+    const __half* p = reinterpret_cast<const __half*>(W) + e0;
+    if constexpr (VEC == 8) {
+      VT<__half>::unpack(ld16(p), out);
+    } else {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) out[j] = __half2float(p[j]);
+    }
+  }
+}
+
+template <typename T, int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
+norm_fwd_kernel(const T* __restrict__ X, const T* __restrict__ R, const void* __restrict__ W, int w_dt,
+                T* __restrict__ Y, T* __restrict__ S, float* __restrict__ RSTD,
+                int64_t n_rows, int n_cols, float eps) {
+  constexpr int VEC = VT<T>::N;
+  const int n_vec = n_cols / VEC;
+  __shared__ float red[33];
+  const int tid = threadIdx.x;
+
+  for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
+    const T* xr = X + row * n_cols;
+    uint4 xv[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = tid + i * THREADS;
+      xv[i] = (v < n_vec) ? ld16_stream(xr + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
+    }
+    if (R != nullptr) {
+      const T* rr = R + row * n_cols;
+      T* sr = S + row * n_cols;
+      uint4 rv[VPT];
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int v = tid + i * THREADS;
+        rv[i] = (v < n_vec) ? ld16_stream(rr + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int v = tid + i * THREADS;
+        float a[VEC], b[VEC];
+        VT<T>::unpack(xv[i], a);
+        VT<T>::unpack(rv[i], b);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) a[j] = a[j] + b[j];  // rounded to T by pack()
+        xv[i] = VT<T>::pack(a);
+        if (v < n_vec) st16(sr + (int64_t)v * VEC, xv[i]);
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      float a[VEC];
+      VT<T>::unpack(xv[i], a);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) ss = fmaf(a[j], a[j], ss);
+    }
+    ss = block_sum<THREADS>(ss, red);
+    const float rstd = 1.0f / sqrtf(ss / (float)n_cols + eps);
+    if (tid == 0) RSTD[row] = rstd;
+    T* yr = Y + row * n_cols;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = tid + i * THREADS;
+      if (v < n_vec) {
+        float a[VEC], w[VEC];
+        VT<T>::unpack(xv[i], a);
+        load_w_vec<VEC>(W, w_dt, v * VEC, w);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) a[j] = VT<T>::round(a[j] * rstd) * w[j];
+        st16(yr + (int64_t)v * VEC, VT<T>::pack(a));
+      }
+    }
+  }
+}
+
+// Any n_cols (no alignment requirement): scalar access, row re-read from L1/L2.
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_fwd_generic_kernel(const T* __restrict__ X, const T* __restrict__ R, const void* __restrict__ W, int w_dt,
+                        T* __restrict__ Y, T* __restrict__ S, float* __restrict__ RSTD,
+                        int64_t n_rows, int64_t n_cols, float eps) {
+  __shared__ float red[33];
+  for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
+    const T* xr = X + row * n_cols;
+    const T* rr = R ? R + row * n_cols : nullptr;
+    T* sr = S ? S + row * n_cols : nullptr;
+    float ss = 0.f;
+    for (int64_t c = threadIdx.x; c < n_cols; c += 256) {
+      float s = VT<T>::load1(xr + c);
+      if (rr) {
+        s = VT<T>::round(s + VT<T>::load1(rr + c));
+        VT<T>::store1(sr + c, s);
+      }
+      ss = fmaf(s, s, ss);
+    }
+    ss = block_sum<256>(ss, red);
+    const float rstd = 1.0f / sqrtf(ss / (float)n_cols + eps);
+    if (threadIdx.x == 0) RSTD[row] = rstd;
+    T* yr = Y + row * n_cols;
+    for (int64_t c = threadIdx.x; c < n_cols; c += 256) {
+      // each thread re-reads exactly the elements it wrote above
+      float s = rr ? VT<T>::load1(sr + c) : VT<T>::load1(xr + c);
+      VT<T>::store1(yr + c, VT<T>::round(s * rstd) * load_any(W, w_dt, c));
+    }
+  }
+}
+
+template <typename T, int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
+norm_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __restrict__ X,
+                const void* __restrict__ W, int w_dt, const float* __restrict__ RSTD,
+                T* __restrict__ dX, float* __restrict__ partial, int64_t n_rows, int n_cols) {
+  constexpr int VEC = VT<T>::N;
+  const int n_vec = n_cols / VEC;
+  __shared__ float red[33];
+  const int tid = threadIdx.x;
+  const float inv_n = 1.0f / (float)n_cols;
+
+  // w is re-read per row (an L1 hit after the first row) rather than held in registers.
+  float dw[VPT][VEC];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i)
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) dw[i][j] = 0.f;
+
+  for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
+    uint4 dyv[VPT], xv[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = tid + i * THREADS;
+      const bool ok = v < n_vec;
+      dyv[i] = (ok && dY) ? ld16_stream(dY + row * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
+      xv[i] = ok ? ld16_stream(X + row * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
+    }
+    const float rstd = RSTD[row];
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = tid + i * THREADS;
+      float dy[VEC], x[VEC], w[VEC];
+      VT<T>::unpack(dyv[i], dy);
+      VT<T>::unpack(xv[i], x);
+      if (v < n_vec) {
+        load_w_vec<VEC>(W, w_dt, v * VEC, w);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) acc = fmaf(dy[j] * w[j], x[j], acc);
+      }
+    }
+    acc = block_sum<THREADS>(acc, red);
+    const float coef = rstd * rstd * rstd * (acc * inv_n);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = tid + i * THREADS;
+      float dy[VEC], x[VEC], dx[VEC], w[VEC];
+      VT<T>::unpack(dyv[i], dy);
+      VT<T>::unpack(xv[i], x);
+      if (v < n_vec) {
+        load_w_vec<VEC>(W, w_dt, v * VEC, w);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+          dx[j] = rstd * (dy[j] * w[j]) - coef * x[j];
+          dw[i][j] = fmaf(dy[j], x[j] * rstd, dw[i][j]);
+        }
+        if (dS != nullptr) {
+          float ds[VEC];
+          VT<T>::unpack(ld16_stream(dS + row * n_cols + (int64_t)v * VEC), ds);
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) dx[j] += ds[j];
+        }
+        st16(dX + row * n_cols + (int64_t)v * VEC, VT<T>::pack(dx));
+      }
+    }
+  }
+  float* pr = partial + (int64_t)blockIdx.x * n_cols;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * THREADS;
+    if (v < n_vec) {
+#pragma unroll
+      for (int j = 0; j < VEC; j += 4)
+        st16(pr + (int64_t)v * VEC + j, VT<float>::pack(&dw[i][j]));
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_bwd_generic_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __restrict__ X,
+                        const void* __restrict__ W, int w_dt, const float* __restrict__ RSTD,
+                        T* __restrict__ dX, float* __restrict__ partial, int64_t n_rows, int64_t n_cols) {
+  __shared__ float red[33];
+  float* pr = partial + (int64_t)blockIdx.x * n_cols;
+  for (int64_t c = threadIdx.x; c < n_cols; c += 256) pr[c] = 0.f;
+  for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
+    const T* dyr = dY ? dY + row * n_cols : nullptr;
+    const T* xr = X + row * n_cols;
+    const float rstd = RSTD[row];
+    float acc = 0.f;
+    for (int64_t c = threadIdx.x; c < n_cols; c += 256) {
+      const float dy = dyr ? VT<T>::load1(dyr + c) : 0.f;
+      acc = fmaf(dy * load_any(W, w_dt, c), VT<T>::load1(xr + c), acc);
+    }
+    acc = block_sum<256>(acc, red);
+    const float coef = rstd * rstd * rstd * (acc / (float)n_cols);
+    for (int64_t c = threadIdx.x; c < n_cols; c += 256) {
+      const float dy = dyr ? VT<T>::load1(dyr + c) : 0.f;
+      const float x = VT<T>::load1(xr + c);
+      float dx = rstd * (dy * load_any(W, w_dt, c)) - coef * x;
+      if (dS) dx += VT<T>::load1(dS + row * n_cols + c);
+      VT<T>::store1(dX + row * n_cols + c, dx);
+      pr[c] = fmaf(dy, x * rstd, pr[c]);  // same thread owns column c for every row
+    }
+  }
+}
+
+// partial [P, n_cols] fp32 -> dW [n_cols] in W's dtype. 32 columns x 32 row-groups per CTA.
+__global__ void __launch_bounds__(1024)
+dw_reduce_kernel(const float* __restrict__ partial, int P, int64_t n_cols, void* __restrict__ dW, int w_dt) {
+  __shared__ float tile[32][33];
+  const int cx = threadIdx.x & 31, gy = threadIdx.x >> 5;
+  const int64_t col = (int64_t)blockIdx.x * 32 + cx;
+  float acc = 0.f;
+  if (col < n_cols)
+    for (int p = gy; p < P; p += 32) acc += partial[(int64_t)p * n_cols + col];
+  tile[gy][cx] = acc;
+  __syncthreads();
+  if (gy == 0 && col < n_cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int g = 0; g < 32; ++g) t += tile[g][cx];
+    store_any(dW, w_dt, col, t);
+  }
+}
+
+// ---- host-side dispatch --------------------------------------------------------
+struct NormPlan { int threads; int vpt; bool generic; };
+
+static NormPlan plan_norm(int64_t n_cols, int vec, int pref_vpt, bool all_aligned) {
+  NormPlan p{256, 1, true};
+  if (!all_aligned || n_cols % vec != 0) return p;
+  const int64_t n_vec = n_cols / vec;
+  int vpt = pref_vpt;
+  while (vpt > 1 && n_vec / vpt < 128) vpt >>= 1;
+  while (vpt < 8 && n_vec > (int64_t)vpt * 1024) vpt <<= 1;
+  if (n_vec > (int64_t)vpt * 1024) return p;
+  int threads = 128;
+  while ((int64_t)threads * vpt < n_vec) threads <<= 1;
+  p.threads = threads; p.vpt = vpt; p.generic = false;
+  return p;
+}
+
+#define NORM_DISPATCH_TV(T, CALL)                                                     \
+  switch (plan.threads * 16 + plan.vpt) {                                             \
+    case 128 * 16 + 1: CALL(T, 128, 1); break;  case 128 * 16 + 2: CALL(T, 128, 2); break;   \
+    case 128 * 16 + 4: CALL(T, 128, 4); break;  case 128 * 16 + 8: CALL(T, 128, 8); break;   \
+    case 256 * 16 + 1: CALL(T, 256, 1); break;  case 256 * 16 + 2: CALL(T, 256, 2); break;   \
+    case 256 * 16 + 4: CALL(T, 256, 4); break;  case 256 * 16 + 8: CALL(T, 256, 8); break;   \
+    case 512 * 16 + 1: CALL(T, 512, 1); break;  case 512 * 16 + 2: CALL(T, 512, 2); break;   \
+    case 512 * 16 + 4: CALL(T, 512, 4); break;  case 512 * 16 + 8: CALL(T, 512, 8); break;   \
+    case 1024 * 16 + 1: CALL(T, 1024, 1); break; case 1024 * 16 + 2: CALL(T, 1024, 2); break; \
+    case 1024 * 16 + 4: CALL(T, 1024, 4); break; case 1024 * 16 + 8: CALL(T, 1024, 8); break; \
+    default: return HILDA_ERR_SIZE;                                                   \
+  }
+
+template <typename T>
+static int norm_fwd_t(const void* x, const void* r, const void* w, int w_dt, void* y, void* s, float* rstd,
+                      int64_t n_rows, int64_t n_cols, float eps, cudaStream_t st) {
+  const bool al = aligned16(x) && aligned16(y) && aligned16(w) && (!r || (aligned16(r) && aligned16(s)));
+  const int pref = (sizeof(T) == 4) ? 4 : 2;
+  NormPlan plan = plan_norm(n_cols, VT<T>::N, pref, al);
+  const int64_t max_grid = (int64_t)sm_count() * 64;
+  if (plan.generic) {
+    int grid = (int)(n_rows < max_grid ? n_rows : max_grid);
+    norm_fwd_generic_kernel<T><<<grid, 256, 0, st>>>((const T*)x, (const T*)r, w, w_dt, (T*)y, (T*)s, rstd,
+                                                       n_rows, n_cols, eps);
+    HILDA_LAUNCH_CHECK();
+    return HILDA_OK;
+  }
+  int grid = (int)(n_rows < max_grid ? n_rows : max_grid);
+#define FWD_CALL(TT, TH, VP)                                                                            \
+  norm_fwd_kernel<TT, TH, VP><<<grid, TH, 0, st>>>((const TT*)x, (const TT*)r, w, w_dt, (TT*)y, (TT*)s, rstd, \
+                                                    n_rows, (int)n_cols, eps)
+  NORM_DISPATCH_TV(T, FWD_CALL)
+#undef FWD_CALL
+  HILDA_LAUNCH_CHECK();
+  return HILDA_OK;
+}
+
+// Number of CTAs (= rows of the fp32 partial buffer) the backward uses.
+template <typename T>
+static int norm_bwd_ctas(int64_t n_rows, int64_t n_cols, bool al) {
+  const int pref = (sizeof(T) == 4) ? 4 : 2;
+  NormPlan plan = plan_norm(n_cols, VT<T>::N, pref, al);
+  int per_sm = 4;
+  if (!plan.generic) {
+#define OCC_CALL(TT, TH, VP) \
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, norm_bwd_kernel<TT, TH, VP>, TH, 0)
+    NORM_DISPATCH_TV(T, OCC_CALL)
+#undef OCC_CALL
+    if (per_sm < 1) per_sm = 1;
+  }
+  int64_t ctas = (int64_t)sm_count() * per_sm;
+  if (ctas > n_rows) ctas = n_rows;
+  if (ctas < 1) ctas = 1;
+  return (int)ctas;
+}
+
+template <typename T>
+static int norm_bwd_t(const void* dy, const void* ds, const void* x, const void* w, int w_dt, const float* rstd,
+                      void* dx, void* dw, float* workspace, int64_t n_rows, int64_t n_cols, cudaStream_t st) {
+  const bool al = aligned16(x) && aligned16(dx) && aligned16(w) && aligned16(workspace) &&
+                  (!dy || aligned16(dy)) && (!ds || aligned16(ds));
+  const int pref = (sizeof(T) == 4) ? 4 : 2;
+  NormPlan plan = plan_norm(n_cols, VT<T>::N, pref, al);
+  // The workspace is sized for the aligned plan; a misaligned call uses no more CTAs than that.
+  int grid = norm_bwd_ctas<T>(n_rows, n_cols, true);
+  if (plan.generic) {
+    int g2 = norm_bwd_ctas<T>(n_rows, n_cols, false);
+    if (g2 < grid) grid = g2;
+    norm_bwd_generic_kernel<T><<<grid, 256, 0, st>>>((const T*)dy, (const T*)ds, (const T*)x, w, w_dt, rstd,
+                                                       (T*)dx, workspace, n_rows, n_cols);
+  } else {
+#define BWD_CALL(TT, TH, VP)                                                                               \
+  norm_bwd_kernel<TT, TH, VP><<<grid, TH, 0, st>>>((const TT*)dy, (const TT*)ds, (const TT*)x, w, w_dt, rstd, \
+                                                    (TT*)dx, workspace, n_rows, (int)n_cols)
+    NORM_DISPATCH_TV(T, BWD_CALL)
+#undef BWD_CALL
+  }
+  HILDA_LAUNCH_CHECK();
+  dw_reduce_kernel<<<(unsigned)((n_cols + 31) / 32), 1024, 0, st>>>(workspace, grid, n_cols, dw, w_dt);
+  HILDA_LAUNCH_CHECK();
+  return HILDA_OK;
+}
+
+}  // namespace hilda
+
+using namespace hilda;
+
+extern "C" {
+
+int hilda_rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, int64_t n_rows, int64_t n_cols,
+                       float eps, int dtype, int w_dtype, void* stream) {
+  if (!x || !w || !y || !rstd) return HILDA_ERR_NULL;
+  if (n_rows < 0 || n_cols <= 0 || n_cols > 0x7fffffff) return HILDA_ERR_SIZE;
+  if (dtype_size(w_dtype) == 0) return HILDA_ERR_DTYPE;
+  if (n_rows == 0) return HILDA_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (dtype) {
+    case HILDA_F32: return norm_fwd_t<float>(x, nullptr, w, w_dtype, y, nullptr, rstd, n_rows, n_cols, eps, st);
+    case HILDA_BF16: return norm_fwd_t<__nv_bfloat16>(x, nullptr, w, w_dtype, y, nullptr, rstd, n_rows, n_cols, eps, st);
+    case HILDA_F16: return norm_fwd_t<__half>(x, nullptr, w, w_dtype, y, nullptr, rstd, n_rows, n_cols, eps, st);
+  }
+  return HILDA_ERR_DTYPE;
+}
+
+int hilda_fused_add_rms_norm_fwd(const void* x, const void* r, const void* w, void* y, void* s, float* rstd,
+                                 int64_t n_rows, int64_t n_cols, float eps, int dtype, int w_dtype, void* stream) {
+  if (!x || !r || !w || !y || !s || !rstd) return HILDA_ERR_NULL;
+  if (n_rows < 0 || n_cols <= 0 || n_cols > 0x7fffffff) return HILDA_ERR_SIZE;
+  if (dtype_size(w_dtype) == 0) return HILDA_ERR_DTYPE;
+  if (n_rows == 0) return HILDA_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (dtype) {
+    case HILDA_F32: return norm_fwd_t<float>(x, r, w, w_dtype, y, s, rstd, n_rows, n_cols, eps, st);
+    case HILDA_BF16: return norm_fwd_t<__nv_bfloat16>(x, r, w, w_dtype, y, s, rstd, n_rows, n_cols, eps, st);
+    case HILDA_F16: return norm_fwd_t<__half>(x, r, w, w_dtype, y, s, rstd, n_rows, n_cols, eps, st);
+  }
+  return HILDA_ERR_DTYPE;
+}
+
+int64_t hilda_norm_bwd_workspace_bytes(int64_t n_rows, int64_t n_cols, int dtype) {
+  if (n_rows <= 0 || n_cols <= 0) return 16;
+  int ctas;
+  switch (dtype) {
+    case HILDA_F32: ctas = norm_bwd_ctas<float>(n_rows, n_cols, true); break;
+    case HILDA_BF16: ctas = norm_bwd_ctas<__nv_bfloat16>(n_rows, n_cols, true); break;
+    case HILDA_F16: ctas = norm_bwd_ctas<__half>(n_rows, n_cols, true); break;
+    default: return HILDA_ERR_DTYPE;
+  }
+  return (int64_t)ctas * n_cols * 4;
+}
+
+// dy and ds may each be null (treated as zero); x is the saved input (RMSNorm) or saved sum S
+// (FusedAddRMSNorm).
+int hilda_norm_bwd(const void* dy, const void* ds, const void* x, const void* w, const float* rstd, void* dx,
+                   void* dw, float* workspace, int64_t n_rows, int64_t n_cols, int dtype, int w_dtype,
+                   void* stream) {
+  if (!x || !w || !rstd || !dx || !dw || !workspace) return HILDA_ERR_NULL;
+  if (n_rows < 0 || n_cols <= 0 || n_cols > 0x7fffffff) return HILDA_ERR_SIZE;
+  if (dtype_size(w_dtype) == 0) return HILDA_ERR_DTYPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (n_rows == 0) {
+    if (cudaMemsetAsync(dw, 0, (size_t)n_cols * dtype_size(w_dtype), st) != cudaSuccess) return HILDA_ERR_CUDA;
+    return HILDA_OK;
+  }
+  switch (dtype) {
+    case HILDA_F32: return norm_bwd_t<float>(dy, ds, x, w, w_dtype, rstd, dx, dw, workspace, n_rows, n_cols, st);
+    case HILDA_BF16: return norm_bwd_t<__nv_bfloat16>(dy, ds, x, w, w_dtype, rstd, dx, dw, workspace, n_rows, n_cols, st);
+    case HILDA_F16: return norm_bwd_t<__half>(dy, ds, x, w, w_dtype, rstd, dx, dw, workspace, n_rows, n_cols, st);
+  }
+  return HILDA_ERR_DTYPE;
+}
+
+}  // extern "C"

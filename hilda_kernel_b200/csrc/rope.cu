@@ -1,0 +1,192 @@
+// Rotate-half RoPE on q and k in one launch, optionally in place, for sm_100a.
+//
+// Semantics follow kernels/rope.py:28-83 of hilda-kernel: for every (batch, head, position) row of
+// head_dim elements, with half-width cos/sin tables indexed by position,
+//     y1 = x1*cos - x2*sin,  y2 = x2*cos + x1*sin      (x1 = first half, x2 = second half)
+// and the backward pass is the same map with -sin (rope.py:139-172). Arithmetic is carried out in
+// the dtype of the cos table (x is cast to it first, rope.py:76-77) with a rounding after every
+// multiply and add, which is also what the PyTorch reference (benchmarks/bench_rope.py:40-58)
+// does, and the result is cast to x's dtype on store.
+//
+// Layout: q/k are addressed as (batch, head, seq, head_dim) with arbitrary element strides on the
+// first three dims and a contiguous last dim, so both (B,H,S,D) and transposed views of (B,S,H,D)
+// memory work without a copy. One thread handles one 16-byte vector of x1 and the matching vector
+// of x2; q and k items are folded into one flat index space so a single launch covers both.
+#include "common.cuh"
+
+namespace hilda {
+
+struct RopeTensor {
+  const void* in;
+  void* out;
+  int64_t stride_b, stride_h, stride_s;     // element strides of `in`
+  int64_t ostride_b, ostride_h, ostride_s;  // element strides of `out`
+  int n_heads;
+};
+
+struct RopeArgs {
+  RopeTensor t[2];
+  const void* cos;
+  const void* sin;
+  int64_t cos_stride_b;  // 0 when the table has batch size 1
+  int64_t cos_stride_s;
+  int cs_dtype;
+  float sin_sign;  // +1 forward, -1 backward
+  int bsz, seq, half;  // half = head_dim / 2
+  int s_inner;         // 1: iterate seq faster than heads (memory order B,H,S,D)
+};
+
+template <int VEC>
+__device__ __forceinline__ void load_vec_any(const void* base, int dt, int64_t e0, float* out) {
+  if (dt == HILDA_F32) {
+    const float* p = reinterpret_cast<const float*>(base) + e0;
+    if constexpr (VEC % 4 == 0) {
+#pragma unroll
+      for (int j = 0; j < VEC; j += 4) VT<float>::unpack(ld16(p + j), out + j);
+    } else {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) out[j] = p[j];
+    }
+  } else if (dt == HILDA_BF16) {
+    const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(base) + e0;
+    if constexpr (VEC == 8) VT<__nv_bfloat16>::unpack(ld16(p), out);
+    else {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) out[j] = __bfloat162float(p[j]);
+    }
+  } else {
+    const __half* p = reinterpret_cast<const __half*>(base) + e0;
+    if constexpr (VEC == 8) VT<__half>::unpack(ld16(p), out);
+    else {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) out[j] = __half2float(p[j]);
+    }
+  }
+}
+
+template <typename T, int VEC>
+__device__ __forceinline__ void load_x(const T* p, float* out) {
+  if constexpr (VEC == VT<T>::N) VT<T>::unpack(ld16(p), out);
+  else {
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) out[j] = VT<T>::load1(p + j);
+  }
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void store_x(T* p, const float* v) {
+  if constexpr (VEC == VT<T>::N) st16(p, VT<T>::pack(v));
+  else {
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) VT<T>::store1(p + j, v[j]);
+  }
+}
+
+// grid.x = outer index (token b*S+s, or b*H+h when seq is the faster dim), grid.y = chunk of the
+// inner (head|position, vector) items. Only 32-bit divisions per item.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(512) rope_kernel(const RopeArgs a, int inner_items, int chunk_items) {
+  const unsigned vph = a.half / VEC;  // vectors per half head
+  const int h_total = a.t[0].n_heads + a.t[1].n_heads;
+  const unsigned outer = blockIdx.x;
+  const unsigned odiv = a.s_inner ? (unsigned)h_total : (unsigned)a.seq;
+  const int b = (int)(outer / odiv);
+  const int orem = (int)(outer - (unsigned)b * odiv);
+  const int i0 = blockIdx.y * chunk_items;
+  const int i1 = min(inner_items, i0 + chunk_items);
+  const int cd = a.cs_dtype;
+  for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
+    const unsigned mid = (unsigned)i / vph;
+    const int v = (int)((unsigned)i - mid * vph);
+    const int h = a.s_inner ? orem : (int)mid;
+    const int s = a.s_inner ? (int)mid : orem;
+    const int ti = (h >= a.t[0].n_heads) ? 1 : 0;
+    const RopeTensor& t = a.t[ti];
+    const int hh = ti ? h - a.t[0].n_heads : h;
+    const int64_t off = b * t.stride_b + hh * t.stride_h + s * t.stride_s + (int64_t)v * VEC;
+    const T* xin = reinterpret_cast<const T*>(t.in) + off;
+    T* xout = reinterpret_cast<T*>(t.out) + b * t.ostride_b + hh * t.ostride_h + s * t.ostride_s + (int64_t)v * VEC;
+    const int64_t coff = b * a.cos_stride_b + s * a.cos_stride_s + (int64_t)v * VEC;
+
+    float x1[VEC], x2[VEC], c[VEC], sn[VEC], y1[VEC], y2[VEC];
+    load_x<T, VEC>(xin, x1);
+    load_x<T, VEC>(xin + a.half, x2);
+    load_vec_any<VEC>(a.cos, cd, coff, c);
+    load_vec_any<VEC>(a.sin, cd, coff, sn);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const float sj = sn[j] * a.sin_sign;
+      const float a1 = round_any(x1[j], cd), a2 = round_any(x2[j], cd);
+      const float p1 = round_any(__fmul_rn(a1, c[j]), cd), p2 = round_any(__fmul_rn(a2, sj), cd);
+      const float p3 = round_any(__fmul_rn(a2, c[j]), cd), p4 = round_any(__fmul_rn(a1, sj), cd);
+      y1[j] = round_any(__fsub_rn(p1, p2), cd);
+      y2[j] = round_any(__fadd_rn(p3, p4), cd);
+    }
+    store_x<T, VEC>(xout, y1);
+    store_x<T, VEC>(xout + a.half, y2);
+  }
+}
+
+template <typename T>
+static int rope_launch(const RopeArgs& a, bool vec_ok, cudaStream_t st) {
+  const int h_total = a.t[0].n_heads + a.t[1].n_heads;
+  const int vec = vec_ok ? VT<T>::N : 1;
+  const int64_t vph = a.half / vec;
+  const int64_t outer = (int64_t)a.bsz * (a.s_inner ? h_total : a.seq);
+  const int64_t inner = (int64_t)(a.s_inner ? a.seq : h_total) * vph;
+  if (outer == 0 || inner == 0) return HILDA_OK;
+  if (outer > 0x7fffffffLL || inner > 0x7fffffffLL) return HILDA_ERR_SIZE;
+  int threads, chunk;
+  if (inner <= 512) { threads = (int)((inner + 31) / 32 * 32); chunk = threads; }
+  else { threads = 256; chunk = 1024; }
+  const int64_t chunks = (inner + chunk - 1) / chunk;
+  if (chunks > 65535) return HILDA_ERR_SIZE;
+  dim3 grid((unsigned)outer, (unsigned)chunks);
+  if (vec_ok) rope_kernel<T, VT<T>::N><<<grid, threads, 0, st>>>(a, (int)inner, chunk);
+  else rope_kernel<T, 1><<<grid, threads, 0, st>>>(a, (int)inner, chunk);
+  HILDA_LAUNCH_CHECK();
+  return HILDA_OK;
+}
+
+}  // namespace hilda
+
+using namespace hilda;
+
+extern "C" int hilda_rope(const void* q_in, void* q_out, const int64_t* q_strides, int n_q_heads,
+                          const void* k_in, void* k_out, const int64_t* k_strides, int n_k_heads,
+                          const void* cos, const void* sin, int64_t cos_stride_b, int64_t cos_stride_s,
+                          int bsz, int seq, int head_dim, int dtype, int cs_dtype, int backward, void* stream) {
+  if (!cos || !sin) return HILDA_ERR_NULL;
+  if ((n_q_heads > 0 && (!q_in || !q_out || !q_strides)) || (n_k_heads > 0 && (!k_in || !k_out || !k_strides)))
+    return HILDA_ERR_NULL;
+  if (head_dim <= 0 || (head_dim & 1) || bsz < 0 || seq < 0 || n_q_heads < 0 || n_k_heads < 0) return HILDA_ERR_SIZE;
+  if (dtype_size(dtype) == 0 || dtype_size(cs_dtype) == 0) return HILDA_ERR_DTYPE;
+  RopeArgs a;
+  // q_strides / k_strides: six element strides each, (b, h, s) of the input then of the output
+  const int64_t zero6[6] = {0, 0, 0, 0, 0, 0};
+  const int64_t* qs = q_strides ? q_strides : zero6;
+  const int64_t* ks = k_strides ? k_strides : zero6;
+  a.t[0] = RopeTensor{q_in, q_out, qs[0], qs[1], qs[2], qs[3], qs[4], qs[5], n_q_heads};
+  a.t[1] = RopeTensor{k_in, k_out, ks[0], ks[1], ks[2], ks[3], ks[4], ks[5], n_k_heads};
+  a.cos = cos; a.sin = sin; a.cos_stride_b = cos_stride_b; a.cos_stride_s = cos_stride_s;
+  a.cs_dtype = cs_dtype; a.sin_sign = backward ? -1.f : 1.f;
+  a.bsz = bsz; a.seq = seq; a.half = head_dim / 2;
+  const RopeTensor& ref = n_q_heads > 0 ? a.t[0] : a.t[1];
+  a.s_inner = (ref.stride_s < ref.stride_h) ? 1 : 0;
+
+  const int vec = 16 / dtype_size(dtype);
+  bool vec_ok = (a.half % vec == 0) && aligned16(cos) && aligned16(sin) && (cos_stride_b % 8 == 0) &&
+                (cos_stride_s % 8 == 0);
+  for (int i = 0; i < 2 && vec_ok; ++i) {
+    const RopeTensor& t = a.t[i];
+    if (t.n_heads == 0) continue;
+    vec_ok = aligned16(t.in) && aligned16(t.out) && t.stride_b % vec == 0 && t.stride_h % vec == 0 &&
+             t.stride_s % vec == 0 && t.ostride_b % vec == 0 && t.ostride_h % vec == 0 && t.ostride_s % vec == 0;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (dtype) {
+    case HILDA_F32: return rope_launch<float>(a, vec_ok, st);
+    case HILDA_BF16: return rope_launch<__nv_bfloat16>(a, vec_ok, st);
+    case HILDA_F16: return rope_launch<__half>(a, vec_ok, st);
+  }
+  return HILDA_ERR_DTYPE;
+}

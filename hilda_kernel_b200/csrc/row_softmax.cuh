@@ -1,0 +1,285 @@
+// One-pass row softmax engine shared by CrossEntropy, the GRPO loss and selective log-softmax.
+//
+// A vocabulary row (128K-152K logits, 256-304 KB in bf16) does not fit one SM's registers or
+// shared memory, so a row is owned by a thread-block CLUSTER: each of the CLUSTER CTAs (on
+// different SMs) loads a contiguous slice of the row into registers with 128-bit loads, reduces
+// its own (max, sum-exp) pair, and the pairs are exchanged through distributed shared memory
+// with a single cluster barrier. Every CTA then knows the row's logsumexp and writes the
+// gradient of its slice straight from registers. HBM traffic is therefore exactly one read of
+// the row and one write of the gradient row.
+//
+// The per-row "Op" supplies: which rows are active, the target column, 1/temperature, and how
+// the per-row scalars (loss, kl, ...) and the gradient coefficients follow from (lse, x_target):
+//     grad[j] = alpha * softmax(x/T)[j] + (j == target ? beta : 0).
+#pragma once
+#include "common.cuh"
+
+namespace hilda {
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_arrive_release() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_acquire() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+
+template <typename T> __device__ __forceinline__ uint4 neg_inf_vec();
+template <> __device__ __forceinline__ uint4 neg_inf_vec<float>() {
+  return make_uint4(0xff800000u, 0xff800000u, 0xff800000u, 0xff800000u);
+}
+template <> __device__ __forceinline__ uint4 neg_inf_vec<__nv_bfloat16>() {
+  return make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);
+}
+template <> __device__ __forceinline__ uint4 neg_inf_vec<__half>() {
+  return make_uint4(0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u);
+}
+
+struct RowCoef { float alpha, beta; };
+
+// Compiler barrier on a packed vector: stops the unpacked fp32 copy of the row from being kept
+// live across passes (which would triple the register footprint).
+__device__ __forceinline__ void opaque(uint4& v) {
+  asm volatile("" : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w));
+}
+
+constexpr int ROW_THREADS = 256;
+
+// Register-resident, cluster-per-row kernel. Requires V % VEC == 0 and 16-byte aligned rows.
+template <typename T, int NV, int CLUSTER, class Op>
+__global__ void __launch_bounds__(ROW_THREADS)
+row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V, Op op) {
+  constexpr int VEC = VT<T>::N;
+  __shared__ float red[33];
+  __shared__ float xchg[2 * CLUSTER];
+  const int tid = threadIdx.x;
+  const uint32_t rank = (CLUSTER > 1) ? cluster_ctarank() : 0u;
+  const int64_t row = blockIdx.x / CLUSTER;
+  const int n_vec = (int)(V / VEC);
+  const int slice = (n_vec + CLUSTER - 1) / CLUSTER;
+  const int v0 = (int)rank * slice;
+  const int v1 = min(n_vec, v0 + slice);
+  const int64_t roff = op.row_offset(row, V);
+  const T* xr = logits + roff;
+  T* gr = grad ? grad + roff : nullptr;
+  const bool writer = (rank == 0 && tid == 0);
+
+  int64_t target = -1;
+  const bool active = op.begin(row, target);  // identical in every CTA of the cluster
+  if (!active) {
+    if (gr) {
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      for (int v = v0 + tid; v < v1; v += ROW_THREADS) st16_stream(gr + (int64_t)v * VEC, z);
+    }
+    if (writer) op.inactive(row);
+    return;
+  }
+
+  uint4 xv[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = v0 + tid + i * ROW_THREADS;
+    xv[i] = (v < v1) ? ld16_stream(xr + (int64_t)v * VEC) : neg_inf_vec<T>();
+  }
+  const float inv_t = op.inv_temperature();
+  const float k = inv_t * LOG2E;  // logits -> log2 domain
+  float x_t = 0.f;
+  if (target >= 0 && target < V) x_t = VT<T>::load1(xr + target) * inv_t;
+
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    float f[VEC];
+    VT<T>::unpack(xv[i], f);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) m = fmaxf(m, f[j] * k);
+  }
+  m = block_max<ROW_THREADS>(m, red);
+  const float m_safe = (m == -INFINITY) ? 0.f : m;
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    float f[VEC];
+    opaque(xv[i]);
+    VT<T>::unpack(xv[i], f);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) s += ex2_approx(fmaf(f[j], k, -m_safe));
+  }
+  s = block_sum<ROW_THREADS>(s, red);
+
+  float M = m, S = s;
+  if constexpr (CLUSTER > 1) {
+    if (tid < CLUSTER) {
+      const uint32_t base = (uint32_t)__cvta_generic_to_shared(xchg);
+      const uint32_t remote = map_to_cta(base, (uint32_t)tid);
+      st_cluster_f32(remote + 8u * rank, m);
+      st_cluster_f32(remote + 8u * rank + 4u, s);
+    }
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    M = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < CLUSTER; ++c) M = fmaxf(M, xchg[2 * c]);
+    S = 0.f;
+#pragma unroll
+    for (int c = 0; c < CLUSTER; ++c) {
+      const float mc = xchg[2 * c];
+      S += (mc == -INFINITY) ? 0.f : xchg[2 * c + 1] * exp2f(mc - M);
+    }
+  }
+  const float lse2 = M + log2f(S);
+  const float lse = lse2 * LN2;  // natural-log logsumexp of logits/T
+
+  const RowCoef co = op.finish(row, lse, x_t, writer);
+  if (!gr) return;
+
+  const int64_t tvec = (target >= 0 && target < V) ? target / VEC : -1;
+  const int tsub = (int)(target - tvec * VEC);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = v0 + tid + i * ROW_THREADS;
+    float f[VEC];
+    opaque(xv[i]);
+    VT<T>::unpack(xv[i], f);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) f[j] = co.alpha * ex2_approx(fmaf(f[j], k, -lse2));
+    if (v == tvec) {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j)
+        if (j == tsub) f[j] += co.beta;
+    }
+    if (v < v1) st16_stream(gr + (int64_t)v * VEC, VT<T>::pack(f));
+  }
+}
+
+// Any V / alignment: one CTA per row, scalar access, row read twice (second read from L2).
+template <typename T, class Op>
+__global__ void __launch_bounds__(512)
+row_softmax_generic_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V, Op op) {
+  __shared__ float red[33];
+  const int tid = threadIdx.x;
+  const int64_t row = blockIdx.x;
+  const int64_t roff = op.row_offset(row, V);
+  const T* xr = logits + roff;
+  T* gr = grad ? grad + roff : nullptr;
+  const bool writer = (tid == 0);
+  int64_t target = -1;
+  const bool active = op.begin(row, target);
+  if (!active) {
+    if (gr)
+      for (int64_t c = tid; c < V; c += 512) VT<T>::store1(gr + c, 0.f);
+    if (writer) op.inactive(row);
+    return;
+  }
+  const float inv_t = op.inv_temperature();
+  const float k = inv_t * LOG2E;
+  float x_t = 0.f;
+  if (target >= 0 && target < V) x_t = VT<T>::load1(xr + target) * inv_t;
+  float m = -INFINITY;
+  for (int64_t c = tid; c < V; c += 512) m = fmaxf(m, VT<T>::load1(xr + c) * k);
+  m = block_max<512>(m, red);
+  const float m_safe = (m == -INFINITY) ? 0.f : m;
+  float s = 0.f;
+  for (int64_t c = tid; c < V; c += 512) s += ex2_approx(fmaf(VT<T>::load1(xr + c), k, -m_safe));
+  s = block_sum<512>(s, red);
+  const float lse2 = m + log2f(s);
+  const float lse = lse2 * LN2;
+  const RowCoef co = op.finish(row, lse, x_t, writer);
+  if (!gr) return;
+  for (int64_t c = tid; c < V; c += 512) {
+    float g = co.alpha * ex2_approx(fmaf(VT<T>::load1(xr + c), k, -lse2));
+    if (c == target) g += co.beta;
+    VT<T>::store1(gr + c, g);
+  }
+}
+
+struct RowPlan { int nv; int cluster; bool generic; };
+
+// Pick (vectors per thread, cluster size) so that cluster * 256 * nv vectors cover the row.
+static inline RowPlan plan_row(int64_t V, int vec, bool aligned, int force_nv, int force_cluster) {
+  RowPlan p{0, 1, true};
+  if (!aligned || V % vec != 0 || V / vec > 0x7fffffff) return p;
+  const int64_t n_vec = V / vec;
+  if (force_nv > 0 && force_cluster > 0) {
+    if ((int64_t)force_nv * force_cluster * ROW_THREADS >= n_vec) { p.nv = force_nv; p.cluster = force_cluster; p.generic = false; }
+    return p;
+  }
+  const int64_t per = ROW_THREADS;
+  if (n_vec <= per * 1) { p.nv = 1; }
+  else if (n_vec <= per * 2) { p.nv = 2; }
+  else if (n_vec <= per * 4) { p.nv = 4; }
+  else if (n_vec <= per * 8) { p.nv = 8; }
+  else if (n_vec <= per * 8 * 2) { p.nv = 8; p.cluster = 2; }
+  else if (n_vec <= per * 8 * 4) { p.nv = 8; p.cluster = 4; }
+  else if (n_vec <= per * 8 * 8) { p.nv = 8; p.cluster = 8; }
+  else if (n_vec <= per * 10 * 8) { p.nv = 10; p.cluster = 8; }
+  else if (n_vec <= per * 12 * 8) { p.nv = 12; p.cluster = 8; }
+  else if (n_vec <= per * 16 * 8) { p.nv = 16; p.cluster = 8; }
+  else return p;
+  p.generic = false;
+  return p;
+}
+
+template <typename T, int NV, int CLUSTER, class Op>
+static int launch_row_cfg(const T* logits, T* grad, int64_t n_rows, int64_t V, const Op& op, cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(n_rows * CLUSTER), 1, 1);
+  cfg.blockDim = dim3(ROW_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CLUSTER;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, row_softmax_kernel<T, NV, CLUSTER, Op>, logits, grad, V, op);
+  return e == cudaSuccess ? HILDA_OK : HILDA_ERR_CUDA;
+}
+
+// Process-wide override of the plan, for tuning runs (0 = automatic).
+extern int g_row_force_nv, g_row_force_cluster;
+
+template <typename T, class Op>
+static int launch_rows(const void* logits_v, void* grad_v, int64_t n_rows, int64_t V, const Op& op, cudaStream_t st) {
+  const T* logits = (const T*)logits_v;
+  T* grad = (T*)grad_v;
+  if (n_rows == 0) return HILDA_OK;
+  if (n_rows * 8 > 0x7fffffffLL) return HILDA_ERR_SIZE;
+  const bool al = aligned16(logits) && (!grad || aligned16(grad)) && op.rows_aligned(V, VT<T>::N);
+  const RowPlan p = plan_row(V, VT<T>::N, al, g_row_force_nv, g_row_force_cluster);
+  if (p.generic) {
+    row_softmax_generic_kernel<T, Op><<<(unsigned)n_rows, 512, 0, st>>>(logits, grad, V, op);
+    HILDA_LAUNCH_CHECK();
+    return HILDA_OK;
+  }
+#define ROW_CFG(NV_, CL_) \
+  if (p.nv == NV_ && p.cluster == CL_) return launch_row_cfg<T, NV_, CL_, Op>(logits, grad, n_rows, V, op, st);
+  ROW_CFG(1, 1) ROW_CFG(2, 1) ROW_CFG(4, 1) ROW_CFG(8, 1) ROW_CFG(8, 2) ROW_CFG(8, 4) ROW_CFG(8, 8)
+  ROW_CFG(10, 8) ROW_CFG(12, 8) ROW_CFG(16, 8) ROW_CFG(16, 4) ROW_CFG(16, 2)
+#undef ROW_CFG
+  return HILDA_ERR_SIZE;
+}
+
+}  // namespace hilda

@@ -1,0 +1,201 @@
+"""Multi-GPU forms of the operator path: one process per GPU, torch.distributed (NCCL) for the
+few small exchanges the path needs. The reference is single-device; these have no counterpart
+there and are checked against the single-device result.
+
+* Row-sharded operators (RMSNorm, FusedAddRMSNorm, RoPE, SwiGLU, CrossEntropy, GRPO): tokens or
+  sequences are split over ranks and every rank runs the ordinary operator on its rows. The only
+  exchanges are: dW of the norms (sum all-reduce of [H]), the CE loss numerator and valid-row
+  count, and the four GRPO reduction numerators.
+* Vocab-parallel FusedLinearCrossEntropy: W is split by rows (vocabulary) over ranks, hidden and
+  targets are replicated. Per row only (max, sum-exp, target logit) cross the wire, gathered in
+  one all_gather of 3 floats per row; d(hidden) partial sums are then all-reduced once.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import _lib as L
+from ._lib import device_guard
+
+
+# ------------------------------------------------------------------ partitioning (pure host logic)
+def shard_bounds(n: int, world: int, rank: int, multiple: int = 1) -> tuple[int, int]:
+    """[start, end) of rank's contiguous share of n items; shares are multiples of `multiple`
+    except the last, differ by at most one multiple, and cover [0, n) exactly."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError(f"bad rank/world {rank}/{world}")
+    units = -(-n // multiple)
+    base, extra = divmod(units, world)
+    start_u = rank * base + min(rank, extra)
+    end_u = start_u + base + (1 if rank < extra else 0)
+    return min(start_u * multiple, n), min(end_u * multiple, n)
+
+
+def combine_rowstats(gathered: torch.Tensor) -> torch.Tensor:
+    """gathered [G, 3, rows] of per-shard (max, sum exp(x - max), target logit) -> [3, rows] for the
+    whole vocabulary: M = max_g m_g; S = sum_g s_g * exp(m_g - M); x_t = sum_g x_t,g (exactly one
+    shard holds the target, the others contribute 0)."""
+    m = gathered[:, 0]
+    M = m.max(dim=0).values
+    w = torch.exp(m - M)
+    w = torch.where(torch.isinf(m) & (m < 0), torch.zeros_like(w), w)
+    S = (gathered[:, 1] * w).sum(dim=0)
+    xt = gathered[:, 2].sum(dim=0)
+    return torch.stack([M, S, xt])
+
+
+def _world(group):
+    if not (dist.is_available() and dist.is_initialized()):
+        return 1, 0
+    return dist.get_world_size(group), dist.get_rank(group)
+
+
+# ------------------------------------------------------------------ row-sharded helpers
+def allreduce_weight_grad(dW: torch.Tensor, group=None) -> torch.Tensor:
+    """Sum the norm weight gradient over row shards (in fp32, then back to dW's dtype)."""
+    world, _ = _world(group)
+    if world == 1:
+        return dW
+    buf = dW.float()
+    dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group)
+    return buf.to(dW.dtype)
+
+
+def sharded_cross_entropy(logits_local, targets_local, ignore_index=-100, group=None):
+    """Mean cross entropy over ALL ranks' rows. Each rank holds a row shard. Returns (loss, dlogits_local)
+    with dlogits scaled by the global 1/n_valid. One all-reduce of two floats."""
+    from .kernels.cross_entropy import cross_entropy_forward
+    loss_sum, grad, n_valid = cross_entropy_forward(logits_local, targets_local, ignore_index, 'sum', needs_grad=True)
+    pair = torch.stack([loss_sum, n_valid.to(torch.float32)])
+    world, _ = _world(group)
+    if world > 1:
+        dist.all_reduce(pair, op=dist.ReduceOp.SUM, group=group)
+    inv = 1.0 / pair[1].clamp_min(1.0)
+    scale = inv.reshape(1).contiguous()
+    with device_guard(grad.device):
+        rc = L.lib().hilda_scale_rows(L.ptr(grad), L.ptr(grad), L.ptr(scale), 0, grad.shape[0], grad.shape[1],
+                                      L.dt(grad), L.stream(grad.device))
+    L.check(rc, "scale_rows")
+    return pair[0] * inv, grad
+
+
+def sharded_grpo_loss(logits_local, ids_local, adv_local, old_logp=None, ref_logp=None, mask_local=None,
+                      temperature=1.0, beta=0.0, eps_low=0.2, eps_high=0.2, group=None):
+    """GRPO loss over sequences sharded across ranks (equal sequences per rank). Returns
+    (loss, kl_mean | None, clip_ratio, dlogits_local). One all-reduce of four floats."""
+    from .kernels.grpo_loss import grpo_loss_forward
+    world, _ = _world(group)
+    loss, kl_mean, clip, lse, mask, dlogits = grpo_loss_forward(
+        logits_local, ids_local, adv_local, old_logp, ref_logp, mask_local, temperature, beta, eps_low, eps_high,
+        needs_grad=True)
+    if world == 1:
+        return loss, kl_mean, clip, dlogits
+    msum = mask.sum()
+    mden = msum.clamp(min=1.0)
+    z = torch.zeros((), device=loss.device)
+    vec = torch.stack([loss, (kl_mean * mden) if kl_mean is not None else z, clip * mden, msum])
+    dist.all_reduce(vec, op=dist.ReduceOp.SUM, group=group)
+    gden = vec[3].clamp(min=1.0)
+    # the local gradient was scaled by 1/B_local; the global mean over sequences needs 1/(B_local*world)
+    scale = torch.full((1,), 1.0 / world, device=loss.device, dtype=torch.float32)
+    B, Lp1, V = dlogits.shape
+    with device_guard(dlogits.device):
+        rc = L.lib().hilda_scale_rows(L.ptr(dlogits), L.ptr(dlogits), L.ptr(scale), 0, B * Lp1, V, L.dt(dlogits),
+                                      L.stream(dlogits.device))
+    L.check(rc, "scale_rows")
+    return vec[0] / world, (vec[1] / gden) if kl_mean is not None else None, vec[2] / gden, dlogits
+
+
+# ------------------------------------------------------------------ vocab-parallel FusedLinearCE
+class VocabParallelFLCE:
+    """Vocab-parallel fused linear + cross entropy. Every rank holds ``weight_shard`` = rows
+    [vocab_start, vocab_start + V_local) of the lm_head and the full hidden / targets."""
+
+    def __init__(self, group=None, comm_dtype=torch.float32):
+        self.group = group
+        self.comm_dtype = comm_dtype  # dtype of the d(hidden) all-reduce
+        self.last_status = None
+
+    def __call__(self, hidden, weight_shard, targets, vocab_start, ignore_index=-100, reduction='mean',
+                 compute_grad=True, chunk_rows=None):
+        dev = L.require_cuda(hidden, weight_shard, targets)
+        world, rank = _world(self.group)
+        BT, H = hidden.shape
+        V = weight_shard.shape[0]
+        assert weight_shard.shape[1] == H and hidden.dtype == weight_shard.dtype
+        assert hidden.dtype in (torch.bfloat16, torch.float16)
+        hidden = hidden.contiguous()
+        weight_shard = weight_shard.contiguous()
+        targets = targets.contiguous().long()
+        dt = L.dt(hidden)
+        lib = L.lib()
+        with device_guard(dev):
+            st = L.stream(dev)
+            if chunk_rows is None:
+                chunk_rows = int(lib.hilda_flce_default_chunk_rows(BT, H, V))
+            chunk_rows = max(1, min(chunk_rows, BT))
+            n_chunks = -(-BT // chunk_rows)
+            pitch, tiles = lib.hilda_flce_logits_pitch(V), lib.hilda_flce_stat_tiles(V)
+            scratch = torch.empty(lib.hilda_flce_padded_rows(chunk_rows) * pitch, dtype=hidden.dtype, device=dev)
+            stats = torch.empty(chunk_rows * tiles * 2, dtype=torch.float32, device=dev)
+            rowstat = torch.empty(3, chunk_rows, dtype=torch.float32, device=dev)
+            lse = torch.empty(chunk_rows, dtype=torch.float32, device=dev)
+            loss_rows = torch.empty(BT, dtype=torch.float32, device=dev)
+            head = torch.zeros(2, dtype=torch.int32, device=dev)  # [status, n_valid]
+            status_p, n_valid_p = head.data_ptr(), head.data_ptr() + 4
+            L.check(lib.hilda_count_valid(L.ptr(targets), BT, int(ignore_index), n_valid_p, st), "count_valid")
+            dh32 = torch.empty(BT, H, dtype=torch.float32, device=dev) if (compute_grad and world > 1) else None
+            dh = torch.empty_like(hidden) if compute_grad else None
+            dw = torch.empty_like(weight_shard) if compute_grad else None
+            dw32 = torch.empty(V, H, dtype=torch.float32, device=dev) if (compute_grad and n_chunks > 1) else None
+            for c in range(n_chunks):
+                r0 = c * chunk_rows
+                rows = min(chunk_rows, BT - r0)
+                hc = hidden[r0:r0 + rows]
+                tc = targets[r0:r0 + rows]
+                L.check(lib.hilda_flce_logits(L.ptr(hc), L.ptr(weight_shard), L.ptr(scratch), L.ptr(stats), rows, H, V,
+                                              dt, status_p, st), "flce_logits")
+                rs = rowstat[:, :rows].contiguous() if rows != chunk_rows else rowstat
+                L.check(lib.hilda_flce_row_stats(L.ptr(stats), L.ptr(scratch), L.ptr(tc), L.ptr(rs), rows, V,
+                                                 int(vocab_start), dt, st), "flce_row_stats")
+                if world > 1:
+                    gathered = torch.empty(world, 3, rows, dtype=torch.float32, device=dev)
+                    dist.all_gather_into_tensor(gathered, rs, group=self.group)
+                    rs = combine_rowstats(gathered).contiguous()
+                L.check(lib.hilda_flce_finalize(L.ptr(rs), L.ptr(tc), int(ignore_index), L.ptr(lse),
+                                                loss_rows.data_ptr() + 4 * r0, rows, st), "flce_finalize")
+                if not compute_grad:
+                    continue
+                L.check(lib.hilda_flce_dlogits(L.ptr(scratch), L.ptr(lse), L.ptr(tc), int(ignore_index),
+                                               n_valid_p if reduction == 'mean' else None, rows, V, int(vocab_start),
+                                               dt, st), "flce_dlogits")
+                if world > 1:
+                    L.check(lib.hilda_flce_grad_hidden(L.ptr(scratch), L.ptr(weight_shard), None,
+                                                       dh32.data_ptr() + 4 * r0 * H, rows, H, V, dt, status_p, st),
+                            "flce_grad_hidden")
+                else:
+                    L.check(lib.hilda_flce_grad_hidden(L.ptr(scratch), L.ptr(weight_shard),
+                                                       dh.data_ptr() + 2 * r0 * H, None, rows, H, V, dt, status_p, st),
+                            "flce_grad_hidden")
+                mode = 3 if n_chunks == 1 else (0 if c == 0 else (2 if c == n_chunks - 1 else 1))
+                L.check(lib.hilda_flce_grad_weight(L.ptr(scratch), L.ptr(hc), L.ptr(dw32), L.ptr(dw), mode, rows, H, V,
+                                                   dt, status_p, st), "flce_grad_weight")
+            if compute_grad and world > 1:
+                buf = dh32 if self.comm_dtype == torch.float32 else dh32.to(self.comm_dtype)
+                dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=self.group)
+                dh.copy_(buf)
+        self.last_status = head
+        n_valid = head[1]
+        if reduction == 'none':
+            loss = loss_rows
+        elif reduction == 'sum':
+            loss = loss_rows.sum()
+        else:
+            loss = loss_rows.sum() / n_valid.clamp_min(1).to(torch.float32)
+        return loss, dh, dw
+
+    def check_status(self):
+        """Synchronises; raises if a device-side bounded wait ran out during the last call."""
+        if self.last_status is not None and int(self.last_status[0]) != 0:
+            raise RuntimeError(f"vocab-parallel FLCE: device status {int(self.last_status[0])}")

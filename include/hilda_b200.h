@@ -1,0 +1,175 @@
+/* C ABI of libhilda_b200.so: hand-written sm_100a CUDA kernels for the token-parallel operator
+ * path of hilda-kernel (RMSNorm, FusedAddRMSNorm, RoPE, SwiGLU, CrossEntropy,
+ * FusedLinearCrossEntropy, GRPO loss).
+ *
+ * The reference library has no native layer: each operator is a Python launcher around a Triton
+ * kernel. Each entry point below replaces one such launcher; the reference function it stands in
+ * for is cited by file:line (paths relative to triton-kernels/ in hilda-kernel).
+ *
+ * Conventions
+ *  - every pointer is a DEVICE pointer unless stated otherwise; nothing is allocated inside the
+ *    library: outputs and workspaces are supplied by the caller (sizes via *_workspace_bytes);
+ *  - `stream` is a cudaStream_t passed as void*; all work is enqueued on it, no host sync;
+ *  - dtype enum: 0 = float32, 1 = bfloat16, 2 = float16;
+ *  - return value: 0 on success, negative HILDA_ERR_* otherwise;
+ *  - 16-byte aligned pointers and row lengths that are multiples of 16 bytes take the vectorised
+ *    kernels; anything else takes a slower generic kernel with identical results.
+ */
+#ifndef HILDA_B200_H
+#define HILDA_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HILDA_OK 0
+#define HILDA_ERR_DTYPE (-1)
+#define HILDA_ERR_ALIGN (-2)
+#define HILDA_ERR_SIZE (-3)
+#define HILDA_ERR_CUDA (-4)
+#define HILDA_ERR_NULL (-5)
+#define HILDA_ERR_DEVICE (-6)
+#define HILDA_ERR_ARG (-7)
+
+#define HILDA_F32 0
+#define HILDA_BF16 1
+#define HILDA_F16 2
+
+/* ---- RMSNorm ------------------------------------------------------------------------------ */
+/* Replaces rms_norm_forward (kernels/rms_norm.py:261-306). x,y: [n_rows, n_cols] row-major in
+ * `dtype`; w: [n_cols] in `w_dtype`; rstd: [n_rows] fp32 (the only saved statistic). */
+int hilda_rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, int64_t n_rows, int64_t n_cols,
+                       float eps, int dtype, int w_dtype, void* stream);
+
+/* Replaces fused_add_rms_norm_forward (kernels/fused_add_rms_norm.py:172-188):
+ * s = x + r (rounded to dtype), y = rmsnorm(s) * w. */
+int hilda_fused_add_rms_norm_fwd(const void* x, const void* r, const void* w, void* y, void* s, float* rstd,
+                                 int64_t n_rows, int64_t n_cols, float eps, int dtype, int w_dtype, void* stream);
+
+/* Bytes of fp32 scratch hilda_norm_bwd needs (one partial dW row per CTA). */
+int64_t hilda_norm_bwd_workspace_bytes(int64_t n_rows, int64_t n_cols, int dtype);
+
+/* Replaces rms_norm_backward (kernels/rms_norm.py:309-359) and fused_add_rms_norm_backward
+ * (kernels/fused_add_rms_norm.py:191-232). x is the saved input (RMSNorm) or the saved sum S
+ * (FusedAddRMSNorm); dy and ds may each be null (treated as zeros); dx = norm_bwd(dy) + ds;
+ * dw: [n_cols] in w_dtype, reduced in a fixed order (bit-reproducible). */
+int hilda_norm_bwd(const void* dy, const void* ds, const void* x, const void* w, const float* rstd, void* dx,
+                   void* dw, float* workspace, int64_t n_rows, int64_t n_cols, int dtype, int w_dtype,
+                   void* stream);
+
+/* ---- RoPE --------------------------------------------------------------------------------- */
+/* Replaces rope_forward / rope_backward (kernels/rope.py:113-136, :139-172) for q and k in one
+ * launch. Tensors are indexed (batch, head, seq, head_dim) with a contiguous last dim;
+ * q_strides / k_strides hold six element strides: (b, h, s) of the input, then of the output.
+ * q_out may equal q_in (in place). cos/sin: half-width tables [1 or bsz, seq, head_dim/2] in
+ * cs_dtype, cos_stride_b = 0 for a batch-1 table. backward != 0 applies the transpose rotation
+ * (-sin). Either tensor may be skipped with n_*_heads = 0. */
+int hilda_rope(const void* q_in, void* q_out, const int64_t* q_strides, int n_q_heads, const void* k_in,
+               void* k_out, const int64_t* k_strides, int n_k_heads, const void* cos, const void* sin,
+               int64_t cos_stride_b, int64_t cos_stride_s, int bsz, int seq, int head_dim, int dtype,
+               int cs_dtype, int backward, void* stream);
+
+/* ---- SwiGLU ------------------------------------------------------------------------------- */
+/* Replaces swiglu_forward (kernels/swiglu.py:112-124): c = silu(a) * b over n elements. */
+int hilda_swiglu_fwd(const void* a, const void* b, void* c, int64_t n, int dtype, void* stream);
+/* Replaces swiglu_backward (kernels/swiglu.py:127-141). da/db may alias a/b (the reference
+ * overwrites the saved inputs). */
+int hilda_swiglu_bwd(const void* a, const void* b, const void* dc, void* da, void* db, int64_t n, int dtype,
+                     void* stream);
+
+/* ---- CrossEntropy ------------------------------------------------------------------------- */
+int64_t hilda_cross_entropy_workspace_bytes(int64_t n_rows);
+/* Replaces cross_entropy_forward (kernels/cross_entropy.py:206-249). logits [n_rows, V] in dtype,
+ * targets int64. grad != null: training path, grad = d loss / d logits for the given reduction
+ * (0 none, 1 mean, 2 sum), written in the same pass; grad == null: inference path. loss_rows
+ * [n_rows] fp32 (may be null -> kept in workspace), lse_rows optional, loss_out fp32 scalar for
+ * mean/sum. Rows whose target equals ignore_index give loss 0 and a zero gradient row. */
+int hilda_cross_entropy_fwd(const void* logits, const int64_t* targets, void* grad, float* loss_rows,
+                            float* lse_rows, float* loss_out, void* workspace, int64_t n_rows, int64_t V,
+                            int64_t ignore_index, int reduction, int dtype, void* stream);
+
+/* Replaces _ce_scale_grad_kernel (kernels/cross_entropy.py:173-189) and _element_mul_kernel
+ * (kernels/fused_linear_cross_entropy.py:84-96): out = in * scale[0] or in[r,:] * scale[r];
+ * scale is a device fp32 pointer; in and out may alias. */
+int hilda_scale_rows(const void* in, void* out, const float* scale, int per_row, int64_t n_rows, int64_t n_cols,
+                     int dtype, void* stream);
+
+/* ---- FusedLinearCrossEntropy -------------------------------------------------------------- */
+/* Replaces fused_linear_cross_entropy_forward (kernels/fused_linear_cross_entropy.py:103-171) on one
+ * device: hidden [BT, H], W [V, H], targets [BT] int64; bf16 or fp16; H % 8 == 0. reduction 0
+ * none (per-row loss in loss_rows), 1 mean, 2 sum (fp32 scalar loss_out). dh [BT, H] and dw [V, H]
+ * (both or neither) receive the gradients for a unit upstream gradient. Rows are processed in
+ * chunks of chunk_rows (<= 0: library default, scratch <= 1 GiB); the chunk's logits live in the
+ * workspace, the full [BT, V] logits never exist. The call only enqueues work; afterwards the
+ * int at workspace[0] is non-zero if a bounded device-side wait ran out (HILDA_ERR_DEVICE). */
+int64_t hilda_flce_default_chunk_rows(int64_t BT, int64_t H, int64_t V);
+int64_t hilda_flce_workspace_bytes(int64_t BT, int64_t H, int64_t V, int64_t chunk_rows, int with_grad);
+int hilda_fused_linear_cross_entropy_fwd(const void* hidden, const void* W, const int64_t* targets, float* loss_out,
+                                         float* loss_rows, void* dh, void* dw, void* workspace, int64_t BT,
+                                         int64_t H, int64_t V, int64_t ignore_index, int reduction,
+                                         int64_t chunk_rows, int dtype, void* stream);
+
+/* The same operator as separate steps, for the vocab-parallel form (W sharded by rows over
+ * ranks; no counterpart in the reference, which is single-device): between row_stats and
+ * finalize the caller combines the per-row (max, sum-exp, target logit) triples of all ranks.
+ *   logits scratch: [hilda_flce_padded_rows(rows), hilda_flce_logits_pitch(V)] 16-bit
+ *   stats:          [rows, hilda_flce_stat_tiles(V), 2] fp32
+ *   rowstat:        [3, rows] fp32 = natural-log max, sum exp(x - max), target logit (0 if the
+ *                   target is outside [vocab_start, vocab_start + V)) */
+int64_t hilda_flce_logits_pitch(int64_t V);
+int64_t hilda_flce_padded_rows(int64_t rows);
+int64_t hilda_flce_stat_tiles(int64_t V);
+/* *out = number of targets != ignore_index (kernels/fused_linear_cross_entropy.py:121, on device). */
+int hilda_count_valid(const int64_t* targets, int64_t n, int64_t ignore_index, int* out, void* stream);
+/* logits = hidden @ W^T rounded to dtype (fused_linear_cross_entropy.py:140) + online-LSE tile stats. */
+int hilda_flce_logits(const void* hidden, const void* W, void* logits, float* stats, int64_t rows, int64_t H,
+                      int64_t V, int dtype, int* status, void* stream);
+int hilda_flce_row_stats(const float* stats, const void* logits, const int64_t* targets, float* rowstat,
+                         int64_t rows, int64_t V, int64_t vocab_start, int dtype, void* stream);
+int hilda_flce_finalize(const float* rowstat, const int64_t* targets, int64_t ignore_index, float* lse,
+                        float* loss_rows, int64_t rows, void* stream);
+/* In place: logits -> (softmax - onehot) * (n_valid ? 1/max(*n_valid,1) : 1); ignored rows -> 0
+ * (the second pass of _ce_fwd_inplace_kernel, fused_linear_cross_entropy.py:66-77). */
+int hilda_flce_dlogits(void* logits, const float* lse, const int64_t* targets, int64_t ignore_index,
+                       const int* n_valid, int64_t rows, int64_t V, int64_t vocab_start, int dtype, void* stream);
+/* dh = dlogits @ W (fused_linear_cross_entropy.py:158); exactly one of dh16 / dh32 non-null. */
+int hilda_flce_grad_hidden(const void* dlogits, const void* W, void* dh16, float* dh32, int64_t rows, int64_t H,
+                           int64_t V, int dtype, int* status, void* stream);
+/* dW (+)= dlogits^T @ hidden (fused_linear_cross_entropy.py:161). mode 0: dw32 = .; 1: dw32 += .;
+ * 2: dw16 = dw32 + .; 3: dw16 = . */
+int hilda_flce_grad_weight(const void* dlogits, const void* hidden, float* dw32, void* dw16, int mode,
+                           int64_t rows, int64_t H, int64_t V, int dtype, int* status, void* stream);
+
+/* Validation hook: plain C = A x B through the tcgen05 kernel with either operand K-major
+ * ([M,K] / [N,K]) or MN-major (stored [K,M] / [K,N]). No counterpart in the reference. */
+int hilda_debug_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* c16, float* c32, int64_t ldc,
+                     int M, int N, int K, int a_mn, int b_mn, int dtype, int mn_lbo, int mn_sbo, int* status,
+                     void* stream);
+
+/* ---- GRPO --------------------------------------------------------------------------------- */
+int64_t hilda_grpo_workspace_bytes(int64_t B);
+/* Replaces grpo_loss_forward + grpo_loss_backward (kernels/grpo_loss.py:241-297, :300-330) in one
+ * pass. logits [B, L+1, V]; ids [B, L] int64; mask [B, L] int32 or null; advantages [B] fp32;
+ * old_logp/ref_logp [B, L] fp32 or null. Per-token fp32 outputs loss/kl/clipped/lse [B, L];
+ * scalars_out[3] = {loss, kl_mean, clip_ratio}. grad (nullable): d loss / d logits for a unit
+ * upstream gradient, [B, L+1, V] in dtype, last position and masked tokens zero. */
+int hilda_grpo_loss_fwd(const void* logits, const int64_t* ids, const float* advantages, const float* old_logp,
+                        const float* ref_logp, const int32_t* mask, void* grad, float* loss, float* kl,
+                        float* clipped, float* lse, float* scalars_out, void* workspace, int64_t B, int64_t L,
+                        int64_t V, float temperature, float beta, float eps_low, float eps_high, int dtype,
+                        void* stream);
+
+/* Replaces fused_selective_log_softmax (kernels/grpo_loss.py:65-80). */
+int hilda_selective_log_softmax(const void* logits, const int64_t* ids, const int32_t* mask, float* logp,
+                                int64_t B, int64_t L, int64_t V, float temperature, int dtype, void* stream);
+
+/* Tuning hook for the row engine behind CrossEntropy/GRPO: force (vectors per thread, CTAs per
+ * cluster); (0, 0) restores the automatic plan. No counterpart in the reference. */
+void hilda_row_engine_force(int nv, int cluster);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HILDA_B200_H */

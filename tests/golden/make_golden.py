@@ -1,0 +1,145 @@
+"""Generate tests/golden/golden.pt from hilda-kernel's OWN PyTorch reference functions.
+
+Run once, in a container where the reference checkout is available:
+
+    python tests/golden/make_golden.py /path/to/hilda-kernel
+
+It imports the reference benchmark modules (``triton-kernels/benchmarks/bench_*.py``; importing them
+needs triton but no GPU) and calls the reference implementations they define
+(``pytorch_rms_norm``, ``pytorch_fused_add_rms_norm``, ``pytorch_rope``, ``pytorch_swiglu``,
+``pytorch_linear_ce``, ``pytorch_grpo_loss``) plus ``torch.nn.functional.cross_entropy`` exactly as
+``bench_cross_entropy.py:77-79`` calls it, on small seeded CPU inputs, including their autograd
+gradients. Inputs and outputs are stored together so the tests need neither the reference nor
+this script at run time.
+"""
+import contextlib
+import io
+import os
+import sys
+
+import torch
+
+
+def _import_reference(root):
+    tk = os.path.join(root, "triton-kernels")
+    sys.path.insert(0, os.path.join(tk, "benchmarks"))
+    sys.path.insert(0, tk)
+    mods = {}
+    with contextlib.redirect_stdout(io.StringIO()):
+        for name in ("bench_rms_norm", "bench_fused_add_rms_norm", "bench_rope", "bench_swiglu",
+                     "bench_fused_linear_ce", "bench_grpo"):
+            mods[name] = __import__(name)
+    return mods
+
+
+def _g(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def main(root):
+    m = _import_reference(root)
+    out = {}
+
+    # ---- RMSNorm (fp32 and bf16) with autograd gradients
+    for tag, dtype in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        g = _g(0)
+        x = torch.randn(6, 256, generator=g).to(dtype)
+        w = (1 + 0.1 * torch.randn(256, generator=g)).to(dtype)
+        dy = torch.randn(6, 256, generator=g).to(dtype)
+        xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        y = m["bench_rms_norm"].pytorch_rms_norm(xr, wr, 1e-6)
+        y.backward(dy.to(y.dtype))
+        out[f"rms_norm_{tag}"] = dict(x=x, w=w, dy=dy, eps=1e-6, y=y.detach(), dx=xr.grad, dw=wr.grad)
+
+    # ---- FusedAddRMSNorm
+    for tag, dtype in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        g = _g(1)
+        x = torch.randn(5, 384, generator=g).to(dtype)
+        r = torch.randn(5, 384, generator=g).to(dtype)
+        w = (1 + 0.1 * torch.randn(384, generator=g)).to(dtype)
+        dy = torch.randn(5, 384, generator=g).to(dtype)
+        ds = torch.randn(5, 384, generator=g).to(dtype)
+        xr, rr, wr = (t.clone().requires_grad_(True) for t in (x, r, w))
+        y, s = m["bench_fused_add_rms_norm"].pytorch_fused_add_rms_norm(xr, rr, wr, 1e-6)
+        torch.autograd.backward([y, s], [dy, ds])
+        out[f"fused_add_rms_norm_{tag}"] = dict(x=x, r=r, w=w, dy=dy, ds=ds, eps=1e-6, y=y.detach(), s=s.detach(),
+                                                dx=xr.grad, dr=rr.grad, dw=wr.grad)
+
+    # ---- RoPE (fp32 tables; and bf16 q/k with bf16 tables, the bench convention bench_rope.py:79-80)
+    for tag, dtype in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        g = _g(2)
+        bsz, seq, nq, nk, hd = 2, 16, 4, 2, 32
+        q = torch.randn(bsz, nq, seq, hd, generator=g).to(dtype)
+        k = torch.randn(bsz, nk, seq, hd, generator=g).to(dtype)
+        inv_freq = 1.0 / (10000.0 ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))
+        freqs = torch.outer(torch.arange(seq, dtype=torch.float32), inv_freq)
+        cos, sin = freqs.cos()[None].to(dtype), freqs.sin()[None].to(dtype)
+        dq = torch.randn(bsz, nq, seq, hd, generator=g).to(dtype)
+        dk = torch.randn(bsz, nk, seq, hd, generator=g).to(dtype)
+        qr, kr = q.clone().requires_grad_(True), k.clone().requires_grad_(True)
+        qo, ko = m["bench_rope"].pytorch_rope(qr, kr, cos, sin)
+        torch.autograd.backward([qo, ko], [dq, dk])
+        out[f"rope_{tag}"] = dict(q=q, k=k, cos=cos, sin=sin, dq=dq, dk=dk, q_out=qo.detach(), k_out=ko.detach(),
+                                  dq_in=qr.grad, dk_in=kr.grad)
+
+    # ---- SwiGLU
+    for tag, dtype in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        g = _g(3)
+        a = torch.randn(7, 200, generator=g).to(dtype)
+        b = torch.randn(7, 200, generator=g).to(dtype)
+        dc = torch.randn(7, 200, generator=g).to(dtype)
+        ar, br = a.clone().requires_grad_(True), b.clone().requires_grad_(True)
+        c = m["bench_swiglu"].pytorch_swiglu(ar, br)
+        c.backward(dc)
+        out[f"swiglu_{tag}"] = dict(a=a, b=b, dc=dc, c=c.detach(), da=ar.grad, db=br.grad)
+
+    # ---- CrossEntropy: F.cross_entropy(ignore_index=-100, reduction='mean') as bench_cross_entropy.py:77-79
+    g = _g(4)
+    n, v = 24, 1000
+    logits = 2.0 * torch.randn(n, v, generator=g)
+    targets = torch.randint(0, v, (n,), generator=g)
+    targets[torch.randperm(n, generator=g)[:3]] = -100
+    lr = logits.clone().requires_grad_(True)
+    loss = torch.nn.functional.cross_entropy(lr, targets, ignore_index=-100, reduction="mean")
+    loss.backward()
+    out["cross_entropy_f32"] = dict(logits=logits, targets=targets, loss=loss.detach(), dlogits=lr.grad)
+
+    # ---- FusedLinearCE: pytorch_linear_ce takes no ignore arg (bench_fused_linear_ce.py:36-38)
+    g = _g(5)
+    bt, h, v = 48, 64, 520
+    hidden = torch.randn(bt, h, generator=g)
+    weight = 0.02 * torch.randn(v, h, generator=g)
+    targets = torch.randint(0, v, (bt,), generator=g)
+    hr, wr = hidden.clone().requires_grad_(True), weight.clone().requires_grad_(True)
+    loss = m["bench_fused_linear_ce"].pytorch_linear_ce(hr, wr, targets)
+    loss.backward()
+    out["linear_ce_f32"] = dict(hidden=hidden, weight=weight, targets=targets, loss=loss.detach(), dh=hr.grad,
+                                dw=wr.grad)
+
+    # ---- GRPO: pytorch_grpo_loss on fp32 logits (the bench passes logits.float(), bench_grpo.py:80)
+    for tag, beta in (("beta0", 0.0), ("beta01", 0.1)):
+        g = _g(6)
+        B, L, V = 3, 12, 300
+        logits = 2.0 * torch.randn(B, L + 1, V, generator=g)
+        ids = torch.randint(0, V, (B, L), generator=g)
+        adv = torch.randn(B, generator=g)
+        with torch.no_grad():
+            cur = (logits[:, :-1]).log_softmax(-1).gather(-1, ids.unsqueeze(-1)).squeeze(-1)
+        old = cur + 0.3 * torch.randn(B, L, generator=g)  # wide enough that some ratios clip
+        ref = cur + 0.1 * torch.randn(B, L, generator=g)
+        mask = torch.ones(B, L, dtype=torch.int32)
+        mask[0, -4:] = 0
+        mask[2, -7:] = 0
+        lr = logits.clone().requires_grad_(True)
+        loss = m["bench_grpo"].pytorch_grpo_loss(lr, ids, adv, old, ref if beta else None, mask, beta=beta)
+        loss.backward()
+        out[f"grpo_{tag}"] = dict(logits=logits, ids=ids, adv=adv, old=old, ref=ref, mask=mask, beta=beta,
+                                  loss=loss.detach(), dlogits=lr.grad)
+
+    dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden.pt")
+    torch.save(out, dst)
+    print("wrote", dst, os.path.getsize(dst), "bytes;", len(out), "cases")
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

@@ -1,0 +1,89 @@
+"""CPU: the C-ABI library is built, loads, and exports every symbol include/hilda_b200.h declares;
+the ctypes signature table covers the same set. No compute call is made (no GPU here)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    src = open(os.path.join(ROOT, "include", "hilda_b200.h")).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(hilda_[a-z0-9_]+)\s*\(", src)))
+
+
+@pytest.fixture(scope="module")
+def libpath():
+    from hilda_kernel_b200 import _build
+    return _build.build()
+
+
+def test_header_symbols_exported(libpath):
+    lib = ctypes.CDLL(libpath)
+    names = _declared()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/hilda_b200.h but not exported"
+
+
+def test_signature_table_matches_header(libpath):
+    from hilda_kernel_b200 import _lib
+    assert sorted(_lib.SIGNATURES) == _declared()
+    assert _lib.lib() is not None  # binds every signature
+
+
+def test_size_queries_need_no_gpu(libpath):
+    from hilda_kernel_b200 import _lib
+    lib = _lib.lib()
+    assert lib.hilda_flce_logits_pitch(128256) == 128256
+    assert lib.hilda_flce_logits_pitch(16032) == 16128
+    assert lib.hilda_flce_padded_rows(100) == 128
+    assert lib.hilda_flce_stat_tiles(128256) == 501
+    assert lib.hilda_flce_default_chunk_rows(16384, 4096, 128256) == 4096
+    assert lib.hilda_flce_default_chunk_rows(100, 64, 1000) == 100
+    one = lib.hilda_flce_workspace_bytes(4096, 4096, 128256, 4096, 1)
+    four = lib.hilda_flce_workspace_bytes(16384, 4096, 128256, 4096, 1)
+    assert four - one >= 128256 * 4096 * 4  # the fp32 dW accumulator appears only with > 1 chunk
+    assert lib.hilda_cross_entropy_workspace_bytes(8192) >= 16
+    assert lib.hilda_grpo_workspace_bytes(16) >= 16 + 64
+
+
+def test_no_cpu_fallback():
+    import torch
+    import hilda_kernel_b200 as hk
+    x = torch.randn(4, 64)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        hk.hilda_rms_norm(x, torch.ones(64))
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        hk.hilda_swiglu(x, x)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        hk.hilda_cross_entropy(x, torch.zeros(4, dtype=torch.long))
+
+
+def test_product_does_not_import_oracle():
+    pkg = os.path.join(ROOT, "hilda_kernel_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text, f"{f} mentions the oracle"
+
+
+def test_exported_names_match_reference_api():
+    import hilda_kernel_b200 as hk
+    for name in ["HildaRMSNormFunction", "hilda_rms_norm", "RMSNorm", "HildaRopeFunction", "hilda_rope",
+                 "RotaryEmbedding", "HildaCrossEntropyFunction", "hilda_cross_entropy", "CrossEntropyLoss",
+                 "HildaSwiGLUFunction", "hilda_swiglu", "SwiGLU", "HildaFusedAddRMSNormFunction",
+                 "hilda_fused_add_rms_norm", "FusedAddRMSNorm", "HildaFusedLinearCrossEntropyFunction",
+                 "hilda_fused_linear_cross_entropy", "FusedLinearCrossEntropyLoss", "HildaGRPOLossFunction",
+                 "hilda_grpo_loss", "GRPOLoss", "fused_selective_log_softmax"]:
+        assert hasattr(hk, name), name
+    from hilda_kernel_b200.kernels.rope import rope_backward, rope_forward  # used by bench_rope.py:19
+    import inspect
+    sig = inspect.signature(hk.hilda_grpo_loss)
+    assert list(sig.parameters) == ["logits", "completion_ids", "advantages", "old_logp", "ref_logp",
+                                    "completion_mask", "temperature", "beta", "eps_low", "eps_high"]
+    assert inspect.signature(hk.RMSNorm.__init__).parameters["hidden_dim"] is not None

@@ -367,6 +367,8 @@ int hilda_debug_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, voi
                      int N, int K, int a_mn, int b_mn, int dtype, int mn_lbo, int mn_sbo, int* status, void* stream) {
   if (!A || !B || (!c16 && !c32)) return HILDA_ERR_NULL;
   if (dtype != HILDA_BF16 && dtype != HILDA_F16) return HILDA_ERR_DTYPE;
+  // the epilogue stores 16-byte vectors: rows of C must start on 16-byte boundaries
+  if (ldc % 8 != 0 || N % 8 != 0 || !aligned16(c16) || !aligned16(c32)) return HILDA_ERR_ALIGN;
   GemmParams p = {};
   p.M = M; p.N = N; p.K = K; p.m_fast = 1; p.is_bf16 = dtype == HILDA_BF16; p.status = status;
   p.C16 = c16; p.ldc16 = ldc; p.C32 = c32; p.ldc32 = ldc;

@@ -372,10 +372,10 @@ extern "C" {
 
 int hilda_rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, int64_t n_rows, int64_t n_cols,
                        float eps, int dtype, int w_dtype, void* stream) {
+  if (n_rows == 0) return HILDA_OK;
   if (!x || !w || !y || !rstd) return HILDA_ERR_NULL;
   if (n_rows < 0 || n_cols <= 0 || n_cols > 0x7fffffff) return HILDA_ERR_SIZE;
   if (dtype_size(w_dtype) == 0) return HILDA_ERR_DTYPE;
-  if (n_rows == 0) return HILDA_OK;
   cudaStream_t st = (cudaStream_t)stream;
   switch (dtype) {
     case HILDA_F32: return norm_fwd_t<float>(x, nullptr, w, w_dtype, y, nullptr, rstd, n_rows, n_cols, eps, st);
@@ -387,10 +387,10 @@ int hilda_rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, int64
 
 int hilda_fused_add_rms_norm_fwd(const void* x, const void* r, const void* w, void* y, void* s, float* rstd,
                                  int64_t n_rows, int64_t n_cols, float eps, int dtype, int w_dtype, void* stream) {
+  if (n_rows == 0) return HILDA_OK;
   if (!x || !r || !w || !y || !s || !rstd) return HILDA_ERR_NULL;
   if (n_rows < 0 || n_cols <= 0 || n_cols > 0x7fffffff) return HILDA_ERR_SIZE;
   if (dtype_size(w_dtype) == 0) return HILDA_ERR_DTYPE;
-  if (n_rows == 0) return HILDA_OK;
   cudaStream_t st = (cudaStream_t)stream;
   switch (dtype) {
     case HILDA_F32: return norm_fwd_t<float>(x, r, w, w_dtype, y, s, rstd, n_rows, n_cols, eps, st);
@@ -417,7 +417,8 @@ int64_t hilda_norm_bwd_workspace_bytes(int64_t n_rows, int64_t n_cols, int dtype
 int hilda_norm_bwd(const void* dy, const void* ds, const void* x, const void* w, const float* rstd, void* dx,
                    void* dw, float* workspace, int64_t n_rows, int64_t n_cols, int dtype, int w_dtype,
                    void* stream) {
-  if (!x || !w || !rstd || !dx || !dw || !workspace) return HILDA_ERR_NULL;
+  if (!w || !dw) return HILDA_ERR_NULL;
+  if (n_rows > 0 && (!x || !rstd || !dx || !workspace)) return HILDA_ERR_NULL;
   if (n_rows < 0 || n_cols <= 0 || n_cols > 0x7fffffff) return HILDA_ERR_SIZE;
   if (dtype_size(w_dtype) == 0) return HILDA_ERR_DTYPE;
   cudaStream_t st = (cudaStream_t)stream;

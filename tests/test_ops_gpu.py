@@ -33,7 +33,7 @@ def test_rms_norm_fwd_bwd(shape, dtype):
     w = (1 + 0.1 * torch.randn(shape[-1], generator=g)).to(dtype)
     dy = torch.randn(*shape, generator=g).to(dtype)
     # oracle in fp32 on the same (already rounded) inputs
-    xr, wr = x.float().requires_grad_(True), w.float().requires_grad_(True)
+    xr, wr = x.float().clone().requires_grad_(True), w.float().clone().requires_grad_(True)
     y_ref = R.rms_norm(xr, wr, 1e-6)
     y_ref.backward(dy.float())
     xd, wd = x.to(DEV).requires_grad_(True), w.to(DEV).requires_grad_(True)
@@ -144,8 +144,8 @@ def test_fused_add_rms_norm(shape, dtype, use_ds):
     # forward oracle in the op's dtype (S must be rounded to dtype before the statistics)
     y_ref, s_ref = R.fused_add_rms_norm(x, r, w, 1e-6)
     # backward oracle in fp32, starting from the rounded S
-    s32 = s_ref.float().requires_grad_(True)
-    w32 = w.float().requires_grad_(True)
+    s32 = s_ref.float().clone().requires_grad_(True)
+    w32 = w.float().clone().requires_grad_(True)
     rms = torch.sqrt(torch.mean(s32 ** 2, dim=-1, keepdim=True) + 1e-6)
     y32 = (s32 / rms) * w32
     y32.backward(dy.float())
@@ -284,7 +284,7 @@ def test_swiglu(shape, dtype):
     b = torch.randn(*shape, generator=g).to(dtype)
     dc = torch.randn(*shape, generator=g).to(dtype)
     c_ref = R.swiglu(a, b)
-    a32, b32 = a.float().requires_grad_(True), b.float().requires_grad_(True)
+    a32, b32 = a.float().clone().requires_grad_(True), b.float().clone().requires_grad_(True)
     R.swiglu(a32, b32).backward(dc.float())
     ad, bd = a.to(DEV).requires_grad_(True), b.to(DEV).requires_grad_(True)
     c = hk.hilda_swiglu(ad, bd)
@@ -330,7 +330,7 @@ def test_cross_entropy(nv, dtype, reduction):
     if reduction != "mean" and v > 60000:
         pytest.skip("large-vocabulary cases run with mean only")
     logits, targets = _ce_inputs(n, v, dtype)
-    lr = logits.float().requires_grad_(True)
+    lr = logits.float().clone().requires_grad_(True)
     loss_ref = R.cross_entropy_clamped(lr, targets, -100, reduction)
     g = gen(8)
     up = torch.randn(loss_ref.shape, generator=g) if reduction == "none" else None
@@ -382,7 +382,7 @@ def test_cross_entropy_golden_and_edges(golden):
     # every cluster/vector plan of the row engine gives the same answer
     import hilda_kernel_b200._lib as L
     logits, targets = _ce_inputs(8, 16384, torch.bfloat16)
-    lr = logits.float().requires_grad_(True)
+    lr = logits.float().clone().requires_grad_(True)
     R.cross_entropy_clamped(lr, targets).backward()
     try:
         for nv_, cl in [(8, 1), (8, 2), (8, 4), (8, 8), (16, 2), (16, 4), (16, 8), (10, 8), (12, 8)]:
@@ -418,7 +418,7 @@ def test_grpo(dims, dtype, beta, masked):
     hk = ops()
     B, L, V = dims
     logits, ids, adv, old, ref, mask = _grpo_inputs(B, L, V, dtype, masked=masked)
-    lr = logits.float().requires_grad_(True)
+    lr = logits.float().clone().requires_grad_(True)
     loss_ref = R.grpo_loss(lr, ids, adv, old, ref if beta else None, mask, beta=beta)
     loss_ref.backward()
     kl_ref, clip_ref = R.grpo_aux(logits.float(), ids, adv, old, ref, mask, beta=beta)

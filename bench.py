@@ -1,0 +1,400 @@
+#!/usr/bin/env python
+"""Headline benchmark: FusedLinearCrossEntropy forward+backward tokens/s on 1-8 B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-ops]
+
+Workload (BASELINE config 4): hidden bf16 [16384, 4096] ~N(0,1); lm_head W bf16 [128256, 4096]
+~N(0, 0.02^2); targets uniform with 5 % ignore_index; mean reduction; gradients for hidden and W.
+Synthetic, seeded. One step = one forward+backward pass of the operator over the whole batch.
+With N > 1 (launched under torchrun) W is sharded by vocabulary rows over the ranks, hidden and
+targets are replicated, and only per-row (max, sum-exp, target logit) plus the d(hidden) partial
+sums cross NVLink: total work is fixed, so scaling is "strong".
+
+Prints ONE JSON line on rank 0. `value` is timed with CUDA events with inputs resident in HBM;
+`e2e` is the same metric through the public operator with HOST (pinned) hidden/targets, the
+host->device copies and the loss read-back inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BT, H, V = 16384, 4096, 128256
+IGNORE_FRAC = 0.05
+METRIC = "FusedLinearCE fwd+bwd tokens/s"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm=float(d["hbm_gbs"]), tf_burst=float(d["bf16_tflops"]),
+                    tf_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), source="measured")
+    return dict(hbm=6650.0, tf_burst=1590.0, tf_sustained=1400.0, source="fallback")
+
+
+def make_inputs(device, seed=4):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    targets = torch.randint(0, V, (BT,), generator=g)
+    targets[torch.randperm(BT, generator=g)[: int(round(IGNORE_FRAC * BT))]] = -100
+    gd = torch.Generator(device=device).manual_seed(seed)
+    hidden = torch.randn(BT, H, device=device, generator=gd).to(torch.bfloat16)
+    weight = (0.02 * torch.randn(V, H, device=device, generator=gd)).to(torch.bfloat16)
+    return hidden, weight, targets.to(device)
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.idx)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2])); power.append(float(r[3]))
+                for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                                  ("sw_power_cap", 8)):
+                    if r[col].lower().startswith("active"):
+                        reasons.add(name)
+            except (ValueError, IndexError):
+                continue
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_env():
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return world, rank, local
+
+
+# ------------------------------------------------------------------------------------------------
+def cpu_reference_tokens_per_s(seconds_target=12.0, threads=None):
+    """hilda-kernel's own PyTorch reference (benchmarks/bench_fused_linear_ce.py:36-38, restated in
+    oracle/reference_ops.py) forward+backward on the host cores, on a bounded row sample of the same
+    workload (full V and H; rows are independent)."""
+    from oracle import reference_ops as R
+    threads = threads or os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(4)
+    weight = (0.02 * torch.randn(V, H, generator=g)).to(torch.bfloat16).requires_grad_(True)
+
+    def run(rows):
+        hidden = torch.randn(rows, H, generator=g).to(torch.bfloat16).requires_grad_(True)
+        targets = torch.randint(0, V, (rows,), generator=g)
+        t0 = time.perf_counter()
+        loss = R.linear_cross_entropy(hidden, weight, targets)
+        loss.backward()
+        weight.grad = None
+        return time.perf_counter() - t0
+
+    rows = 32
+    dt = run(rows)  # also the warm-up
+    dt = run(rows)
+    while dt < seconds_target / 4 and rows < 4096:
+        rows *= 2
+        dt = run(rows)
+    return rows / dt, rows, dt, threads
+
+
+def run_reference(args):
+    world, rank, _ = dist_env()
+    if rank != 0:
+        return
+    vals, rows_used = [], 0
+    for i in range(args.warmup + args.steps):
+        v, rows_used, dt, threads = cpu_reference_tokens_per_s(seconds_target=6.0 if args.steps > 3 else 12.0)
+        if i >= args.warmup:
+            vals.append(v)
+    value = statistics.mean(vals)
+    sample = f"{rows_used} of {BT} rows x full V={V}, H={H}; bf16 hidden @ W.T + F.cross_entropy + autograd"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * rows_used / value,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"FusedLinearCE fwd+bwd BT={BT} H={H} V={V} bf16, 5% ignored, mean",
+                   "note": "PyTorch reference of hilda-kernel on host CPU cores; each step is a bounded row sample"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ------------------------------------------------------------------------------------------------
+def per_op_table(device, pk):
+    """Device-timed GB/s of the six HBM-bound operators at their BASELINE configs (N = 1)."""
+    from hilda_kernel_b200.kernels import (cross_entropy as CE, fused_add_rms_norm as FA, grpo_loss as GR,
+                                           rms_norm as RN, rope as RP, swiglu as SW)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+    g = torch.Generator(device=device).manual_seed(1)
+
+    def timed(fn, reps=10, warm=3):
+        for _ in range(warm):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()  # evict L2 between reps
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return statistics.median(ts)
+
+    out = {}
+
+    def add(name, ms, nbytes, rows):
+        gbs = nbytes / ms / 1e6
+        out[name] = {"us": round(ms * 1e3, 1), "GB/s": round(gbs), "frac_of_measured_hbm": round(gbs / pk["hbm"], 3),
+                     "frac_of_8TBs": round(gbs / 8000.0, 3), "tokens/s": round(rows / ms * 1e3)}
+
+    rn = lambda *s: torch.randn(*s, device=device, generator=g)
+    # config 1: RMSNorm fp32 [4096, 4096] fwd+bwd (5 tensor passes)
+    x, w, dy = rn(4096, 4096), 1 + 0.1 * rn(4096), rn(4096, 4096)
+    _, xf, rstd = RN.rms_norm_forward(x, w)
+    add("rms_norm_fp32_fwd+bwd", timed(lambda: (RN.rms_norm_forward(x, w), RN.rms_norm_backward(dy, xf, w, rstd))),
+        5 * x.numel() * 4, 4096)
+    # config 2a: FusedAddRMSNorm bf16 [16384, 4096] fwd+bwd with dY and dS (8 passes)
+    x, r, w = rn(16384, 4096).bfloat16(), rn(16384, 4096).bfloat16(), (1 + 0.1 * rn(4096)).bfloat16()
+    dy, ds = rn(16384, 4096).bfloat16(), rn(16384, 4096).bfloat16()
+    _, s, rstd = FA.fused_add_rms_norm_forward(x, r, w)
+    add("fused_add_rms_norm_bf16_fwd+bwd",
+        timed(lambda: (FA.fused_add_rms_norm_forward(x, r, w), FA.fused_add_rms_norm_backward(dy, ds, s, w, rstd))),
+        8 * x.numel() * 2, 16384)
+    del x, r, dy, ds, s
+    # config 2b: RoPE bf16 in place, q [4,4096,32,128] k [4,4096,8,128] in (B,S,H,D) memory, theta 5e5
+    q = rn(4, 4096, 32, 128).bfloat16().transpose(1, 2)
+    k = rn(4, 4096, 8, 128).bfloat16().transpose(1, 2)
+    inv = 1.0 / (500000.0 ** (torch.arange(0, 128, 2, device=device).float() / 128))
+    fr = torch.outer(torch.arange(4096, device=device).float(), inv)
+    cos, sin = fr.cos()[None].bfloat16(), fr.sin()[None].bfloat16()
+    add("rope_bf16_fwd+bwd", timed(lambda: (RP.rope_forward(q, k, cos, sin, inplace=True), RP.rope_backward(q, k, cos, sin))),
+        4 * (q.numel() + k.numel()) * 2, 16384)
+    del q, k
+    # config 2c: SwiGLU bf16 [16384, 14336] fwd+bwd (3 + 5 passes)
+    a, b, dc = rn(16384, 14336).bfloat16(), rn(16384, 14336).bfloat16(), rn(16384, 14336).bfloat16()
+    add("swiglu_bf16_fwd+bwd", timed(lambda: (SW.swiglu_forward(a, b), SW.swiglu_backward(a, b, dc))), 8 * a.numel() * 2,
+        16384)
+    del a, b, dc
+    # config 3: CrossEntropy bf16 [8192, 128256], 10 % ignored: read valid rows once, write all grad rows
+    n, v = 8192, 128256
+    logits = (2 * rn(n, v)).bfloat16()
+    t = torch.randint(0, v, (n,), device=device, generator=g)
+    t[torch.randperm(n, device=device, generator=g)[: n // 10]] = -100
+    nvalid = int((t != -100).sum())
+    add("cross_entropy_bf16_fwd+bwd", timed(lambda: CE.cross_entropy_forward(logits, t, -100, "mean", True)),
+        (nvalid + n) * v * 2, n)
+    del logits
+    # config 5: GRPO bf16 logits [16, 1024, 151936] (L = 1023), beta 0.1
+    B, Lc, v = 16, 1023, 151936
+    logits = (2 * rn(B, Lc + 1, v)).bfloat16()
+    ids = torch.randint(0, v, (B, Lc), device=device, generator=g)
+    adv = rn(B)
+    lens = torch.randint(256, 1025, (B,), device=device, generator=g).clamp(max=Lc)
+    mask = (torch.arange(Lc, device=device)[None] < lens[:, None]).int()
+    cur = GR.fused_selective_log_softmax(logits, ids)
+    old, ref = cur + 0.05 * rn(B, Lc), cur + 0.1 * rn(B, Lc)
+    A = int(mask.sum())
+    add("grpo_bf16_fwd+bwd", timed(lambda: GR.grpo_loss_forward(logits, ids, adv, old, ref, mask, 1.0, 0.1, 0.2, 0.2, True),
+                                   reps=5),
+        (A + B * (Lc + 1)) * v * 2, B * Lc)
+    out["grpo_bf16_fwd+bwd"]["active_tokens"] = A
+    return out
+
+
+def run_ours(args):
+    world, rank, local = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the operators have no CPU path)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    import hilda_kernel_b200._lib as L
+    from hilda_kernel_b200.kernels import fused_linear_cross_entropy as FL
+    from hilda_kernel_b200.parallel import VocabParallelFLCE, shard_bounds
+    lib = L.lib()
+    pk = peaks()
+
+    hidden, weight, targets = make_inputs(device)
+    v0, v1 = shard_bounds(V, world, rank, 8)
+    w_local = weight[v0:v1].contiguous() if world > 1 else weight
+    if world > 1:
+        del weight
+    vp = VocabParallelFLCE(comm_dtype=torch.bfloat16) if world > 1 else None
+
+    def step():
+        if world == 1:
+            return FL.fused_linear_cross_entropy_forward(hidden, w_local, targets, -100, "mean", True)
+        return vp(hidden, w_local, targets, v0, -100, "mean", True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        out = step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    lib.hilda_flce_profile(1)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        out = step()
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    import ctypes
+    ms_kind = (ctypes.c_float * 3)()
+    n_kind = (ctypes.c_int * 3)()
+    L.check(lib.hilda_flce_profile_collect(ms_kind, n_kind), "profile_collect")
+    lib.hilda_flce_profile(0)
+    clocks = sampler.stop() if rank == 0 else None
+    loss = float(out[0])
+    t = torch.tensor([ms_total], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t[0]) / args.steps
+    value = BT / ms_step * 1e3
+
+    # ---- end to end: host (pinned) hidden + targets -> device -> operator -> loss read back
+    h_host = hidden.cpu().pin_memory()
+    t_host = targets.cpu().pin_memory()
+    h_dev, t_dev = torch.empty_like(hidden), torch.empty_like(targets)
+
+    def e2e_step():
+        h_dev.copy_(h_host, non_blocking=True)
+        t_dev.copy_(t_host, non_blocking=True)
+        if world == 1:
+            r = FL.fused_linear_cross_entropy_forward(h_dev, w_local, t_dev, -100, "mean", True)
+        else:
+            r = vp(h_dev, w_local, t_dev, v0, -100, "mean", True)
+        return float(r[0])  # device -> host read of the loss (synchronises)
+
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = BT / float(t[0]) * 1e3
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    gemm_ms = sum(ms_kind)
+    gemm_launches = sum(n_kind)
+    flops_rank = 6.0 * BT * (v1 - v0) * H  # algorithmic: three GEMMs of 2*BT*V*H on this rank's shard
+    achieved = flops_rank * args.steps / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+    n_chunks = -(-BT // int(lib.hilda_flce_default_chunk_rows(BT, H, v1 - v0)))
+    launches_per_step = 2 + 6 * n_chunks
+    result = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "loss": loss,
+        "config": {"workload": f"FusedLinearCE fwd+bwd, hidden [{BT},{H}] bf16, W [{V},{H}] bf16, 5% ignored, mean, "
+                               f"grads for hidden and W", "BT": BT, "H": H, "V": V,
+                   "sharding": "single GPU" if world == 1 else f"W vocab-sharded over {world} ranks, hidden replicated",
+                   "row_chunks": n_chunks, "l2": "inputs (1.05 GB W per pass) exceed the 126 MB L2; no flush needed"},
+        "tflops_whole_step": 6.0 * BT * V * H / world / (ms_step * 1e-3) / 1e12,
+        "roofline": {"bound": "tensor", "kernel": "tcgen05_gemm_kernel (logits, d hidden, d W instantiations)",
+                     "achieved": achieved, "peak": pk["tf_sustained"], "unit": "TFLOP/s",
+                     "frac": (achieved / pk["tf_sustained"]) if achieved else None,
+                     "frac_of_burst_peak": (achieved / pk["tf_burst"]) if achieved else None,
+                     "frac_of_nominal_2250": (achieved / 2250.0) if achieved else None,
+                     "peak_source": pk["source"] + " (sustained cuBLAS bf16, kernel timed inside a long step)",
+                     "gemm_ms_per_step": gemm_ms / args.steps, "gemm_launches_per_step": gemm_launches / args.steps,
+                     "per_kind_ms_per_step": {"logits": ms_kind[0] / args.steps, "d_hidden": ms_kind[1] / args.steps,
+                                              "d_weight": ms_kind[2] / args.steps},
+                     "traffic": None},
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h_host.numel() * 2 + t_host.numel() * 8,
+                "d2h_bytes_per_step": 4, "steps": e2e_steps},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks,
+    }
+    if world == 1:
+        del h_host, h_dev
+        if not args.no_ops:
+            try:
+                torch.cuda.empty_cache()
+                result["ops"] = per_op_table(device, pk)
+            except Exception as e:  # the headline line must still print
+                result["ops"] = {"error": repr(e)}
+        if not args.no_cpu:
+            v, rows, dt, threads = cpu_reference_tokens_per_s()
+            result["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                      "sample": f"{rows} of {BT} rows x full V={V}, H={H}, {dt:.1f} s; PyTorch "
+                                                f"reference (bf16 matmul + F.cross_entropy + autograd) on host cores"}
+    print(json.dumps(result))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-ops", action="store_true", help="skip the per-operator table")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

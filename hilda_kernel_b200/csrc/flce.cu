@@ -113,6 +113,34 @@ flce_dlogits_kernel(T* __restrict__ logits, int64_t pitch, const float* __restri
 
 static inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
 
+// Optional timing of the GEMM launches with CUDA events on the launching stream (off by default).
+// kind 0 = logits GEMM, 1 = d(hidden) GEMM, 2 = d(W) GEMM.
+constexpr int PROF_MAX = 4096;
+static bool g_prof_on = false;
+static int g_prof_n = 0;
+static cudaEvent_t g_prof_ev[PROF_MAX][2];
+static int g_prof_kind[PROF_MAX];
+static int g_prof_created = 0;
+
+struct ProfScope {
+  int idx;
+  cudaStream_t st;
+  ProfScope(int kind, cudaStream_t s) : idx(-1), st(s) {
+    if (!g_prof_on || g_prof_n >= PROF_MAX) return;
+    idx = g_prof_n++;
+    if (idx >= g_prof_created) {
+      cudaEventCreate(&g_prof_ev[idx][0]);
+      cudaEventCreate(&g_prof_ev[idx][1]);
+      g_prof_created = idx + 1;
+    }
+    g_prof_kind[idx] = kind;
+    cudaEventRecord(g_prof_ev[idx][0], st);
+  }
+  ~ProfScope() {
+    if (idx >= 0) cudaEventRecord(g_prof_ev[idx][1], st);
+  }
+};
+
 static int flce_logits(const void* hidden, const void* W, void* logits, float* stats, int64_t rows, int64_t H,
                        int64_t V, int is_bf16, int* status, cudaStream_t st) {
   GemmParams p = {};
@@ -120,6 +148,7 @@ static int flce_logits(const void* hidden, const void* W, void* logits, float* s
   p.C16 = logits; p.ldc16 = round_up(V, BN);
   p.stats = reinterpret_cast<float2*>(stats); p.stats_ld = (V + BN - 1) / BN;
   p.status = status;
+  ProfScope prof(0, st);
   return launch_gemm<false, false, EPI_LOGITS_STATS>(hidden, H, W, H, p, st);
 }
 
@@ -128,6 +157,7 @@ static int flce_grad_hidden(const void* dlogits, const void* W, void* dh16, floa
   GemmParams p = {};
   p.M = (int)rows; p.N = (int)H; p.K = (int)V; p.m_fast = 1; p.is_bf16 = is_bf16; p.status = status;
   const int64_t pitch = round_up(V, BN);
+  ProfScope prof(1, st);
   if (dh16) {
     p.C16 = dh16; p.ldc16 = H;
     return launch_gemm<false, true, EPI_STORE16>(dlogits, pitch, W, H, p, st);
@@ -143,6 +173,7 @@ static int flce_grad_weight(const void* dlogits, const void* hidden, float* dw32
   p.M = (int)V; p.N = (int)H; p.K = (int)rows; p.m_fast = 0; p.is_bf16 = is_bf16; p.status = status;
   p.C32 = dw32; p.ldc32 = H; p.C16 = dw16; p.ldc16 = H;
   const int64_t pitch = round_up(V, BN);
+  ProfScope prof(2, st);
   switch (mode) {
     case 0: return launch_gemm<true, true, EPI_STORE32>(dlogits, pitch, hidden, H, p, st);
     case 1: return launch_gemm<true, true, EPI_ACCUM32>(dlogits, pitch, hidden, H, p, st);
@@ -356,6 +387,26 @@ int hilda_fused_linear_cross_entropy_fwd(const void* hidden, const void* W, cons
   if (reduction != 0) {
     sum_rows_kernel<<<1, 1024, 0, st>>>(rows_loss, BT, n_valid, reduction == 1 ? 1 : 0, loss_out);
     HILDA_LAUNCH_CHECK();
+  }
+  return HILDA_OK;
+}
+
+// Time every GEMM launch of the FLCE entry points with CUDA events (enable != 0 also resets the
+// record). hilda_flce_profile_collect waits for the recorded events and returns, per kind
+// (0 logits, 1 d hidden, 2 d W), the summed device time in ms and the launch count.
+void hilda_flce_profile(int enable) {
+  g_prof_on = enable != 0;
+  g_prof_n = 0;
+}
+int hilda_flce_profile_collect(float* ms_per_kind, int* launches_per_kind) {
+  if (!ms_per_kind || !launches_per_kind) return HILDA_ERR_NULL;
+  for (int k = 0; k < 3; ++k) { ms_per_kind[k] = 0.f; launches_per_kind[k] = 0; }
+  for (int i = 0; i < g_prof_n; ++i) {
+    if (cudaEventSynchronize(g_prof_ev[i][1]) != cudaSuccess) return HILDA_ERR_CUDA;
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, g_prof_ev[i][0], g_prof_ev[i][1]) != cudaSuccess) return HILDA_ERR_CUDA;
+    ms_per_kind[g_prof_kind[i]] += ms;
+    launches_per_kind[g_prof_kind[i]] += 1;
   }
   return HILDA_OK;
 }

@@ -142,6 +142,13 @@ int hilda_flce_grad_hidden(const void* dlogits, const void* W, void* dh16, float
 int hilda_flce_grad_weight(const void* dlogits, const void* hidden, float* dw32, void* dw16, int mode,
                            int64_t rows, int64_t H, int64_t V, int dtype, int* status, void* stream);
 
+/* Measurement hook (no counterpart in the reference): while enabled, every GEMM launch of the
+ * FLCE entry points is bracketed by CUDA events on its stream. collect waits for them and returns
+ * per kind (0 logits, 1 d hidden, 2 d W) the summed device milliseconds and the launch count
+ * (HOST pointers, 3 entries each). enable != 0 also clears the record. */
+void hilda_flce_profile(int enable);
+int hilda_flce_profile_collect(float* ms_per_kind, int* launches_per_kind);
+
 /* Validation hook: plain C = A x B through the tcgen05 kernel with either operand K-major
  * ([M,K] / [N,K]) or MN-major (stored [K,M] / [K,N]). No counterpart in the reference. */
 int hilda_debug_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* c16, float* c32, int64_t ldc,

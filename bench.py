@@ -131,8 +131,8 @@ def cpu_reference_tokens_per_s(seconds_target=12.0, threads=None):
     rows = 32
     dt = run(rows)  # also the warm-up
     dt = run(rows)
-    while dt < seconds_target / 4 and rows < 4096:
-        rows *= 2
+    while dt < seconds_target / 2 and rows < BT:
+        rows = min(rows * 2, BT)
         dt = run(rows)
     return rows / dt, rows, dt, threads
 
@@ -161,8 +161,9 @@ def run_reference(args):
 
 
 # ------------------------------------------------------------------------------------------------
-def per_op_table(device, pk):
-    """Device-timed GB/s of the six HBM-bound operators at their BASELINE configs (N = 1)."""
+def per_op_table(device, pk, only=None, small=False):
+    """Device-timed GB/s of the six HBM-bound operators at their BASELINE configs (N = 1).
+    `only` restricts to one operator; `small` divides the row counts by 8 (for profiler captures)."""
     from hilda_kernel_b200.kernels import (cross_entropy as CE, fused_add_rms_norm as FA, grpo_loss as GR,
                                            rms_norm as RN, rope as RP, swiglu as SW)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
@@ -181,6 +182,8 @@ def per_op_table(device, pk):
         return statistics.median(ts)
 
     out = {}
+    div = 8 if small else 1
+    want = lambda name: only is None or only in name
 
     def add(name, ms, nbytes, rows):
         gbs = nbytes / ms / 1e6
@@ -189,43 +192,52 @@ def per_op_table(device, pk):
 
     rn = lambda *s: torch.randn(*s, device=device, generator=g)
     # config 1: RMSNorm fp32 [4096, 4096] fwd+bwd (5 tensor passes)
-    x, w, dy = rn(4096, 4096), 1 + 0.1 * rn(4096), rn(4096, 4096)
-    _, xf, rstd = RN.rms_norm_forward(x, w)
-    add("rms_norm_fp32_fwd+bwd", timed(lambda: (RN.rms_norm_forward(x, w), RN.rms_norm_backward(dy, xf, w, rstd))),
-        5 * x.numel() * 4, 4096)
+    if want("rms_norm_fp32"):
+        x, w, dy = rn(4096, 4096), 1 + 0.1 * rn(4096), rn(4096, 4096)
+        _, xf, rstd = RN.rms_norm_forward(x, w)
+        add("rms_norm_fp32_fwd+bwd", timed(lambda: (RN.rms_norm_forward(x, w), RN.rms_norm_backward(dy, xf, w, rstd))),
+            5 * x.numel() * 4, 4096)
     # config 2a: FusedAddRMSNorm bf16 [16384, 4096] fwd+bwd with dY and dS (8 passes)
-    x, r, w = rn(16384, 4096).bfloat16(), rn(16384, 4096).bfloat16(), (1 + 0.1 * rn(4096)).bfloat16()
-    dy, ds = rn(16384, 4096).bfloat16(), rn(16384, 4096).bfloat16()
-    _, s, rstd = FA.fused_add_rms_norm_forward(x, r, w)
-    add("fused_add_rms_norm_bf16_fwd+bwd",
-        timed(lambda: (FA.fused_add_rms_norm_forward(x, r, w), FA.fused_add_rms_norm_backward(dy, ds, s, w, rstd))),
-        8 * x.numel() * 2, 16384)
-    del x, r, dy, ds, s
+    if want("fused_add_rms_norm"):
+        x, r, w = rn(16384, 4096).bfloat16(), rn(16384, 4096).bfloat16(), (1 + 0.1 * rn(4096)).bfloat16()
+        dy, ds = rn(16384, 4096).bfloat16(), rn(16384, 4096).bfloat16()
+        _, s, rstd = FA.fused_add_rms_norm_forward(x, r, w)
+        add("fused_add_rms_norm_bf16_fwd+bwd",
+            timed(lambda: (FA.fused_add_rms_norm_forward(x, r, w), FA.fused_add_rms_norm_backward(dy, ds, s, w, rstd))),
+            8 * x.numel() * 2, 16384)
+        del x, r, dy, ds, s
     # config 2b: RoPE bf16 in place, q [4,4096,32,128] k [4,4096,8,128] in (B,S,H,D) memory, theta 5e5
-    q = rn(4, 4096, 32, 128).bfloat16().transpose(1, 2)
-    k = rn(4, 4096, 8, 128).bfloat16().transpose(1, 2)
-    inv = 1.0 / (500000.0 ** (torch.arange(0, 128, 2, device=device).float() / 128))
-    fr = torch.outer(torch.arange(4096, device=device).float(), inv)
-    cos, sin = fr.cos()[None].bfloat16(), fr.sin()[None].bfloat16()
-    add("rope_bf16_fwd+bwd", timed(lambda: (RP.rope_forward(q, k, cos, sin, inplace=True), RP.rope_backward(q, k, cos, sin))),
-        4 * (q.numel() + k.numel()) * 2, 16384)
-    del q, k
+    if want("rope"):
+        q = rn(4, 4096, 32, 128).bfloat16().transpose(1, 2)
+        k = rn(4, 4096, 8, 128).bfloat16().transpose(1, 2)
+        inv = 1.0 / (500000.0 ** (torch.arange(0, 128, 2, device=device).float() / 128))
+        fr = torch.outer(torch.arange(4096, device=device).float(), inv)
+        cos, sin = fr.cos()[None].bfloat16(), fr.sin()[None].bfloat16()
+        add("rope_bf16_fwd+bwd",
+            timed(lambda: (RP.rope_forward(q, k, cos, sin, inplace=True), RP.rope_backward(q, k, cos, sin))),
+            4 * (q.numel() + k.numel()) * 2, 16384)
+        del q, k
     # config 2c: SwiGLU bf16 [16384, 14336] fwd+bwd (3 + 5 passes)
-    a, b, dc = rn(16384, 14336).bfloat16(), rn(16384, 14336).bfloat16(), rn(16384, 14336).bfloat16()
-    add("swiglu_bf16_fwd+bwd", timed(lambda: (SW.swiglu_forward(a, b), SW.swiglu_backward(a, b, dc))), 8 * a.numel() * 2,
-        16384)
-    del a, b, dc
+    if want("swiglu"):
+        nr = 16384 // div
+        a, b, dc = rn(nr, 14336).bfloat16(), rn(nr, 14336).bfloat16(), rn(nr, 14336).bfloat16()
+        add("swiglu_bf16_fwd+bwd", timed(lambda: (SW.swiglu_forward(a, b), SW.swiglu_backward(a, b, dc))),
+            8 * a.numel() * 2, nr)
+        del a, b, dc
     # config 3: CrossEntropy bf16 [8192, 128256], 10 % ignored: read valid rows once, write all grad rows
-    n, v = 8192, 128256
-    logits = (2 * rn(n, v)).bfloat16()
-    t = torch.randint(0, v, (n,), device=device, generator=g)
-    t[torch.randperm(n, device=device, generator=g)[: n // 10]] = -100
-    nvalid = int((t != -100).sum())
-    add("cross_entropy_bf16_fwd+bwd", timed(lambda: CE.cross_entropy_forward(logits, t, -100, "mean", True)),
-        (nvalid + n) * v * 2, n)
-    del logits
+    if want("cross_entropy"):
+        n, v = 8192 // div, 128256
+        logits = (2 * rn(n, v)).bfloat16()
+        t = torch.randint(0, v, (n,), device=device, generator=g)
+        t[torch.randperm(n, device=device, generator=g)[: n // 10]] = -100
+        nvalid = int((t != -100).sum())
+        add("cross_entropy_bf16_fwd+bwd", timed(lambda: CE.cross_entropy_forward(logits, t, -100, "mean", True)),
+            (nvalid + n) * v * 2, n)
+        del logits
     # config 5: GRPO bf16 logits [16, 1024, 151936] (L = 1023), beta 0.1
-    B, Lc, v = 16, 1023, 151936
+    if not want("grpo"):
+        return out
+    B, Lc, v = 16 // div, 1023, 151936
     logits = (2 * rn(B, Lc + 1, v)).bfloat16()
     ids = torch.randint(0, v, (B, Lc), device=device, generator=g)
     adv = rn(B)
@@ -255,6 +267,10 @@ def run_ours(args):
     from hilda_kernel_b200.parallel import VocabParallelFLCE, shard_bounds
     lib = L.lib()
     pk = peaks()
+    if args.only_op:
+        if rank == 0:
+            print(json.dumps({"ops": per_op_table(device, pk, only=args.only_op, small=args.small)}))
+        return
 
     hidden, weight, targets = make_inputs(device)
     v0, v1 = shard_bounds(V, world, rank, 8)
@@ -389,7 +405,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-ops", action="store_true", help="skip the per-operator table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--bt", type=int, default=BT, help="tokens (default: the BASELINE workload)")
+    ap.add_argument("--vocab", type=int, default=V, help="vocabulary size (default: the BASELINE workload)")
+    ap.add_argument("--hidden", type=int, default=H)
+    ap.add_argument("--only-op", default=None, help="time one operator of the per-op table and exit")
+    ap.add_argument("--small", action="store_true", help="with --only-op: 1/8 of the rows (profiler captures)")
     args = ap.parse_args()
+    global BT, V, H
+    BT, V, H = args.bt, args.vocab, args.hidden
     if args.impl == "reference":
         run_reference(args)
     else:

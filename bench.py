@@ -398,6 +398,7 @@ def run_ours(args):
 
 
 def main():
+    global BT, V, H
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
@@ -411,7 +412,6 @@ def main():
     ap.add_argument("--only-op", default=None, help="time one operator of the per-op table and exit")
     ap.add_argument("--small", action="store_true", help="with --only-op: 1/8 of the rows (profiler captures)")
     args = ap.parse_args()
-    global BT, V, H
     BT, V, H = args.bt, args.vocab, args.hidden
     if args.impl == "reference":
         run_reference(args)

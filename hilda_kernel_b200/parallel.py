@@ -160,9 +160,9 @@ class VocabParallelFLCE:
                 L.check(lib.hilda_flce_row_stats(L.ptr(stats), L.ptr(scratch), L.ptr(tc), L.ptr(rs), rows, V,
                                                  int(vocab_start), dt, st), "flce_row_stats")
                 if world > 1:
-                    gathered = torch.empty(world, 3, rows, dtype=torch.float32, device=dev)
+                    gathered = torch.empty(world * 3, rows, dtype=torch.float32, device=dev)
                     dist.all_gather_into_tensor(gathered, rs, group=self.group)
-                    rs = combine_rowstats(gathered).contiguous()
+                    rs = combine_rowstats(gathered.view(world, 3, rows)).contiguous()
                 L.check(lib.hilda_flce_finalize(L.ptr(rs), L.ptr(tc), int(ignore_index), L.ptr(lse),
                                                 loss_rows.data_ptr() + 4 * r0, rows, st), "flce_finalize")
                 if not compute_grad:

@@ -1,0 +1,118 @@
+"""CPU tests of the multi-GPU host logic: partitioning and the vocab-parallel statistics exchange,
+run as two gloo ranks. What a rank's kernels would produce (per-shard max / sum-exp / target
+logit) is emulated with torch on CPU; the exchange and the combination are the product code."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from hilda_kernel_b200.parallel import combine_rowstats, shard_bounds
+
+
+def test_shard_bounds_cover_and_align():
+    for n, world, mult in [(128256, 8, 8), (128256, 4, 8), (128256, 2, 8), (1000, 3, 8), (7, 4, 1), (16, 8, 1), (5, 8, 8)]:
+        prev = 0
+        sizes = []
+        for r in range(world):
+            a, b = shard_bounds(n, world, r, mult)
+            assert a == prev and a <= b <= n
+            if b < n:
+                assert b % mult == 0
+            sizes.append(b - a)
+            prev = b
+        assert prev == n
+        assert max(sizes) - min(s for s in sizes if s or True) <= mult * 1 + (n % mult)
+    assert shard_bounds(128256, 8, 0, 8) == (0, 16032)
+    with pytest.raises(ValueError):
+        shard_bounds(10, 2, 2)
+
+
+def _shard_stats(logits, targets, v0, v1):
+    x = logits[:, v0:v1]
+    m = x.max(dim=1).values
+    s = torch.exp(x - m[:, None]).sum(dim=1)
+    t = targets - v0
+    inside = (t >= 0) & (t < v1 - v0)
+    xt = torch.where(inside, x.gather(1, t.clamp(0, v1 - v0 - 1)[:, None])[:, 0], torch.zeros_like(m))
+    return torch.stack([m, s, xt])
+
+
+def test_combine_rowstats_matches_full_logsumexp():
+    g = torch.Generator().manual_seed(0)
+    logits = 3 * torch.randn(37, 1003, generator=g)
+    targets = torch.randint(0, 1003, (37,), generator=g)
+    for world in (1, 2, 3, 8):
+        parts = [_shard_stats(logits, targets, *shard_bounds(1003, world, r, 8)) for r in range(world)]
+        m, s, xt = combine_rowstats(torch.stack(parts))
+        torch.testing.assert_close(m + torch.log(s), torch.logsumexp(logits, dim=1), rtol=1e-6, atol=1e-6)
+        torch.testing.assert_close(xt, logits.gather(1, targets[:, None])[:, 0])
+    # an empty shard (max = -inf, sum = 0) contributes nothing
+    parts = [_shard_stats(logits, targets, 0, 1003), torch.stack([torch.full((37,), -float("inf")), torch.zeros(37), torch.zeros(37)])]
+    m, s, _ = combine_rowstats(torch.stack(parts))
+    torch.testing.assert_close(m + torch.log(s), torch.logsumexp(logits, dim=1), rtol=1e-6, atol=1e-6)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(1)  # same inputs on every rank (hidden/targets are replicated)
+        rows, H, V = 24, 16, 203
+        hidden = torch.randn(rows, H, generator=g)
+        weight = torch.randn(V, H, generator=g)
+        targets = torch.randint(0, V, (rows,), generator=g)
+        targets[5] = -100
+        v0, v1 = shard_bounds(V, world, rank, 8)
+        local_logits = hidden @ weight[v0:v1].T
+        full = torch.zeros(rows, V)
+        full[:, v0:v1] = local_logits
+        mine = _shard_stats(full, targets.clamp_min(0), v0, v1)
+        gathered = torch.empty(world * 3, rows)
+        dist.all_gather_into_tensor(gathered, mine)
+        m, s, xt = combine_rowstats(gathered.view(world, 3, rows))
+        lse = m + torch.log(s)
+        valid = targets != -100
+        loss = ((lse - xt) * valid).sum() / valid.sum()
+        ref = torch.nn.functional.cross_entropy(hidden @ weight.T, targets, ignore_index=-100)
+        # d(hidden) partial of this shard, summed over ranks
+        p = torch.exp(local_logits - lse[:, None])
+        onehot = torch.zeros_like(p)
+        t = targets - v0
+        inside = (t >= 0) & (t < v1 - v0) & valid
+        onehot[inside, t[inside]] = 1
+        d = (p - onehot) * valid[:, None] / valid.sum()
+        dh = d @ weight[v0:v1]
+        dist.all_reduce(dh)
+        hr = hidden.clone().requires_grad_(True)
+        torch.nn.functional.cross_entropy(hr @ weight.T, targets, ignore_index=-100).backward()
+        ok = bool(torch.allclose(loss, ref, rtol=1e-5, atol=1e-6)) and bool(torch.allclose(dh, hr.grad, rtol=1e-4, atol=1e-6))
+        # row-sharded weight-gradient reduction helper
+        from hilda_kernel_b200.parallel import allreduce_weight_grad
+        dw = allreduce_weight_grad(torch.full((8,), float(rank + 1)))
+        ok = ok and bool(torch.equal(dw, torch.full((8,), float(sum(range(1, world + 1))))))
+        q.put((rank, ok))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_vocab_parallel_exchange_gloo_world2():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    results = dict(q.get(timeout=5) for _ in range(2))
+    assert results == {0: True, 1: True}

@@ -364,6 +364,27 @@ static int norm_bwd_t(const void* dy, const void* ds, const void* x, const void*
   return HILDA_OK;
 }
 
+// ---- scratch for the entry point that allocates nothing ------------------------------------
+// One fixed array per GPU that loads the library (it stays resident until the process exits).
+// 4 Mi floats = 16 MiB: room for e.g. 444 partial rows of 8192 columns or 592 rows of 4096.
+constexpr int64_t NOALLOC_SCRATCH_FLOATS = 4ll * 1024 * 1024;
+static __device__ __align__(256) float g_norm_bwd_scratch[NOALLOC_SCRATCH_FLOATS];
+
+// In host code `g_norm_bwd_scratch` is only a handle; the device address has to be asked for,
+// once per device, while that device is current.
+static float* noalloc_scratch_ptr(int* rc) {
+  static float* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { *rc = HILDA_ERR_CUDA; return nullptr; }
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_norm_bwd_scratch) != cudaSuccess || p == nullptr) { *rc = HILDA_ERR_CUDA; return nullptr; }
+    cached[dev] = reinterpret_cast<float*>(p);
+  }
+  *rc = HILDA_OK;
+  return cached[dev];
+}
+
 }  // namespace hilda
 
 using namespace hilda;
@@ -432,6 +453,33 @@ int hilda_norm_bwd(const void* dy, const void* ds, const void* x, const void* w,
     case HILDA_F16: return norm_bwd_t<__half>(dy, ds, x, w, w_dtype, rstd, dx, dw, workspace, n_rows, n_cols, st);
   }
   return HILDA_ERR_DTYPE;
+}
+
+int64_t hilda_norm_bwd_noalloc_max_bytes(void) { return NOALLOC_SCRATCH_FLOATS * 4; }
+
+// hilda_norm_bwd for hosts that cannot hand over a workspace: same arguments minus `workspace`, same
+// kernels, same results. The per-CTA dW partial sums go to a 16 MiB array that lives inside the
+// library (one copy on every GPU that loads it). Meant for callers that have no allocator to ask:
+// a C/FFI host without torch's caching allocator, or a server that gave all device memory to its
+// own pool at start-up and must not call cudaMalloc afterwards.
+//  * Sizes whose partial sums need more than hilda_norm_bwd_noalloc_max_bytes() are refused with
+//    HILDA_ERR_SIZE (use hilda_norm_bwd with your own workspace for those).
+//  * The first call on each device looks up the array's device address (cudaGetSymbolAddress);
+//    make that first call during set-up, before any stream capture begins.
+//  * Nothing in the array has to start at zero (each CTA overwrites its whole partial row before
+//    the reduce pass reads it), so the contents left by an earlier call are harmless. But every
+//    call uses the SAME array: two calls that can overlap on the GPU (different streams, or the
+//    same stream from two host threads without ordering) race on it. Keep them ordered.
+//  * Calls no cudaMalloc / cudaFree and no allocating library routine.
+int hilda_norm_bwd_noalloc(const void* dy, const void* ds, const void* x, const void* w, const float* rstd, void* dx,
+                           void* dw, int64_t n_rows, int64_t n_cols, int dtype, int w_dtype, void* stream) {
+  const int64_t need = hilda_norm_bwd_workspace_bytes(n_rows, n_cols, dtype);
+  if (need < 0) return (int)need;
+  if (need > NOALLOC_SCRATCH_FLOATS * 4) return HILDA_ERR_SIZE;
+  int rc = HILDA_OK;
+  float* scratch = noalloc_scratch_ptr(&rc);
+  if (rc != HILDA_OK) return rc;
+  return hilda_norm_bwd(dy, ds, x, w, rstd, dx, dw, scratch, n_rows, n_cols, dtype, w_dtype, stream);
 }
 
 }  // extern "C"

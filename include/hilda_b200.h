@@ -59,6 +59,18 @@ int hilda_norm_bwd(const void* dy, const void* ds, const void* x, const void* w,
                    void* dw, float* workspace, int64_t n_rows, int64_t n_cols, int dtype, int w_dtype,
                    void* stream);
 
+/* No counterpart in the reference. hilda_norm_bwd without the workspace argument, for hosts that
+ * cannot supply one (a C/FFI caller with no allocator to borrow from, or a server whose memory was
+ * all handed to its own pool at start-up and which must not call cudaMalloc afterwards). The dW
+ * partial sums use a 16 MiB array inside the library, one copy per GPU that loads it. Sizes whose
+ * partial sums exceed hilda_norm_bwd_noalloc_max_bytes() return HILDA_ERR_SIZE. The first call on
+ * a device resolves the array's address: make it before any stream capture. All calls share the
+ * array, so calls that may overlap on the GPU race; keep them ordered. Allocates nothing. */
+int64_t hilda_norm_bwd_noalloc_max_bytes(void);
+int hilda_norm_bwd_noalloc(const void* dy, const void* ds, const void* x, const void* w, const float* rstd,
+                           void* dx, void* dw, int64_t n_rows, int64_t n_cols, int dtype, int w_dtype,
+                           void* stream);
+
 /* ---- RoPE --------------------------------------------------------------------------------- */
 /* Replaces rope_forward / rope_backward (kernels/rope.py:113-136, :139-172) for q and k in one
  * launch. Tensors are indexed (batch, head, seq, head_dim) with a contiguous last dim;

@@ -1,0 +1,60 @@
+"""GPU test of hilda_norm_bwd_noalloc, the one entry point that brings its own scratch memory.
+
+It exists for hosts that have no workspace to pass: a plain C/FFI caller without an allocator, or
+a server that gave the whole device to its own memory pool and may not call cudaMalloc any more.
+The test calls it through the C ABI twice in a row (the second time on different data and a
+different shape, so anything left in the shared scratch array by the first call would show) and
+requires bit-identical results to hilda_norm_bwd with a caller-supplied workspace. This file is
+named so that pytest collects it last."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _run_pair(L, n_rows, n_cols, dtype, seed, with_ds):
+    lib = L.lib()
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(n_rows, n_cols, generator=g).to(dtype).to(DEV)
+    dy = torch.randn(n_rows, n_cols, generator=g).to(dtype).to(DEV)
+    ds = torch.randn(n_rows, n_cols, generator=g).to(dtype).to(DEV) if with_ds else None
+    w = (1 + 0.1 * torch.randn(n_cols, generator=g)).to(dtype).to(DEV)
+    y = torch.empty_like(x)
+    rstd = torch.empty(n_rows, dtype=torch.float32, device=DEV)
+    st = L.stream(x.device)
+    assert lib.hilda_rms_norm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(), n_rows, n_cols, 1e-6,
+                                  L.dt(x), L.dt(w), st) == 0
+    # existing entry point, caller-owned workspace
+    ws = torch.empty(lib.hilda_norm_bwd_workspace_bytes(n_rows, n_cols, L.dt(x)) // 4, dtype=torch.float32, device=DEV)
+    dx_a, dw_a = torch.empty_like(x), torch.empty_like(w)
+    assert lib.hilda_norm_bwd(dy.data_ptr(), L.ptr(ds), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx_a.data_ptr(),
+                              dw_a.data_ptr(), ws.data_ptr(), n_rows, n_cols, L.dt(x), L.dt(w), st) == 0
+    # the entry point under test: no workspace argument
+    dx_b, dw_b = torch.empty_like(x), torch.empty_like(w)
+    assert lib.hilda_norm_bwd_noalloc(dy.data_ptr(), L.ptr(ds), x.data_ptr(), w.data_ptr(), rstd.data_ptr(),
+                                      dx_b.data_ptr(), dw_b.data_ptr(), n_rows, n_cols, L.dt(x), L.dt(w), st) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(dx_a, dx_b), "dx differs"
+    assert torch.equal(dw_a, dw_b), "dw differs"
+    assert bool(torch.isfinite(dw_b.float()).all())
+
+
+def test_norm_bwd_noalloc_matches_workspace_version_twice():
+    import hilda_kernel_b200._lib as L
+    _run_pair(L, 3000, 4096, torch.bfloat16, seed=21, with_ds=False)
+    _run_pair(L, 777, 2048, torch.float32, seed=22, with_ds=True)   # second call: other shape, dtype and data
+    _run_pair(L, 3000, 4096, torch.bfloat16, seed=23, with_ds=True)
+
+
+def test_norm_bwd_noalloc_rejects_oversize():
+    import hilda_kernel_b200._lib as L
+    lib = L.lib()
+    cap = lib.hilda_norm_bwd_noalloc_max_bytes()
+    assert cap == 16 * 1024 * 1024
+    n_rows, n_cols = 100000, 32768   # partial sums need far more than the built-in array holds
+    assert lib.hilda_norm_bwd_workspace_bytes(n_rows, n_cols, 0) > cap
+    one = torch.zeros(8, device=DEV)
+    rc = lib.hilda_norm_bwd_noalloc(one.data_ptr(), None, one.data_ptr(), one.data_ptr(), one.data_ptr(), one.data_ptr(),
+                                    one.data_ptr(), n_rows, n_cols, 0, 0, L.stream(one.device))
+    assert rc == -3  # HILDA_ERR_SIZE, nothing launched

@@ -279,16 +279,32 @@ int hilda_flce_grad_weight(const void* dlogits, const void* hidden, float* dw32,
                           (cudaStream_t)stream);
 }
 
-// Default rows per chunk: the scratch [chunk, pitch(V)] stays at or below 1 GiB (so at most a
-// quarter of the full logits for the 16384 x 128256 benchmark shape), in multiples of 128 rows.
+// Default rows per chunk. The scratch [chunk, pitch(V)] is kept at or below 1.25 GiB (about a
+// quarter of the full logits at the 16384 x 128256 benchmark shape). Within [half of that, that]
+// the chunk is chosen so that the d(hidden) GEMM, the one with few output tiles
+// (chunk/128 x H/256), fills whole waves of SMs: e.g. 37 x 16 = 592 tiles = 4 x 148.
 int64_t hilda_flce_default_chunk_rows(int64_t BT, int64_t H, int64_t V) {
-  (void)H;
   const int64_t pitch = round_up(V > 0 ? V : 1, BN);
-  int64_t rows = ((int64_t)1 << 30) / (pitch * 2);
-  rows = rows / BM * BM;
-  if (rows < BM) rows = BM;
-  if (rows > BT) rows = BT;
-  return rows > 0 ? rows : 1;
+  int64_t cap = (((int64_t)5 << 28)) / (pitch * 2);
+  cap = cap / BM * BM;
+  if (cap < BM) cap = BM;
+  if (BT <= cap) return BT > 0 ? BT : 1;
+  const int64_t n_tiles = (H + BN - 1) / BN;
+  const int64_t sms = 148;
+  int64_t best = cap;
+  double best_eff = -1.0;
+  for (int64_t c = cap; c >= cap / 2 && c >= BM; c -= BM) {
+    int64_t waves = 0, tiles = 0;
+    for (int64_t r0 = 0; r0 < BT; r0 += c) {
+      const int64_t rows = (BT - r0 < c) ? BT - r0 : c;
+      const int64_t t = ((rows + BM - 1) / BM) * n_tiles;
+      tiles += t;
+      waves += (t + sms - 1) / sms;
+    }
+    const double eff = (double)tiles / (double)(waves * sms);
+    if (eff > best_eff + 1e-9) { best_eff = eff; best = c; }
+  }
+  return best;
 }
 
 // Workspace layout (all offsets 256-byte aligned), for chunk_rows rows per chunk:

@@ -274,7 +274,7 @@ int hilda_grpo_loss_fwd(const void* logits, const int64_t* ids, const float* adv
                         float temperature, float beta, float eps_low, float eps_high, int dtype, void* stream) {
   if (!logits || !ids || !advantages || !loss || !clipped || !lse || !scalars_out || !workspace) return HILDA_ERR_NULL;
   if (beta != 0.f && (!ref_logp || !kl)) return HILDA_ERR_NULL;
-  if (B < 0 || L < 0 || V <= 0 || temperature == 0.f) return HILDA_ERR_SIZE;
+  if (B < 0 || L < 0 || V <= 0 || !(temperature > 0.f)) return HILDA_ERR_SIZE;
   cudaStream_t st = (cudaStream_t)stream;
   float* seq_len = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 16);
   if (B > 0) {
@@ -304,7 +304,7 @@ int hilda_grpo_loss_fwd(const void* logits, const int64_t* ids, const float* adv
 int hilda_selective_log_softmax(const void* logits, const int64_t* ids, const int32_t* mask, float* logp, int64_t B,
                                 int64_t L, int64_t V, float temperature, int dtype, void* stream) {
   if (!logits || !ids || !logp) return HILDA_ERR_NULL;
-  if (B < 0 || L < 0 || V <= 0 || temperature == 0.f) return HILDA_ERR_SIZE;
+  if (B < 0 || L < 0 || V <= 0 || !(temperature > 0.f)) return HILDA_ERR_SIZE;
   cudaStream_t st = (cudaStream_t)stream;
   GRPOOp op = {};
   op.ids = ids; op.mask = mask; op.logp_out = logp; op.B = B; op.L = L; op.inv_t = 1.0f / temperature;

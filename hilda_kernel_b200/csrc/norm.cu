@@ -39,6 +39,8 @@ __device__ __forceinline__ void load_w_vec(const void* W, int w_dt, int e0, floa
   }
 }
 
+// Persistent CTAs; the next row's loads are issued before the current row is reduced, so every SM
+// always has loads in flight (software prefetch in registers).
 template <typename T, int THREADS, int VPT>
 __global__ void __launch_bounds__(THREADS)
 norm_fwd_kernel(const T* __restrict__ X, const T* __restrict__ R, const void* __restrict__ W, int w_dt,
@@ -48,24 +50,34 @@ norm_fwd_kernel(const T* __restrict__ X, const T* __restrict__ R, const void* __
   const int n_vec = n_cols / VEC;
   __shared__ float red[33];
   const int tid = threadIdx.x;
+  const bool has_r = (R != nullptr);
 
-  for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
-    const T* xr = X + row * n_cols;
-    uint4 xv[VPT];
+  uint4 xv[VPT], rv[VPT], xn[VPT], rn[VPT];
+  int64_t row = blockIdx.x;
+  if (row < n_rows) {
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = tid + i * THREADS;
-      xv[i] = (v < n_vec) ? ld16_stream(xr + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
+      const bool ok = v < n_vec;
+      xn[i] = ok ? ld16_stream(X + row * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
+      rn[i] = (ok && has_r) ? ld16_stream(R + row * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
     }
-    if (R != nullptr) {
-      const T* rr = R + row * n_cols;
-      T* sr = S + row * n_cols;
-      uint4 rv[VPT];
+  }
+  for (; row < n_rows; row += gridDim.x) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) { xv[i] = xn[i]; rv[i] = rn[i]; }
+    const int64_t nrow = row + gridDim.x;
+    if (nrow < n_rows) {
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int v = tid + i * THREADS;
-        rv[i] = (v < n_vec) ? ld16_stream(rr + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
+        const bool ok = v < n_vec;
+        xn[i] = ok ? ld16_stream(X + nrow * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
+        rn[i] = (ok && has_r) ? ld16_stream(R + nrow * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
       }
+    }
+    if (has_r) {
+      T* sr = S + row * n_cols;
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int v = tid + i * THREADS;
@@ -147,6 +159,7 @@ norm_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __r
   __shared__ float red[33];
   const int tid = threadIdx.x;
   const float inv_n = 1.0f / (float)n_cols;
+  const bool has_dy = (dY != nullptr), has_ds = (dS != nullptr);
 
   // w is re-read per row (an L1 hit after the first row) rather than held in registers.
   float dw[VPT][VEC];
@@ -155,14 +168,35 @@ norm_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __r
 #pragma unroll
     for (int j = 0; j < VEC; ++j) dw[i][j] = 0.f;
 
-  for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
-    uint4 dyv[VPT], xv[VPT];
+  uint4 dyv[VPT], xv[VPT], dyn[VPT], xn[VPT], dsv[VPT];
+  int64_t row = blockIdx.x;
+  if (row < n_rows) {
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = tid + i * THREADS;
       const bool ok = v < n_vec;
-      dyv[i] = (ok && dY) ? ld16_stream(dY + row * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
-      xv[i] = ok ? ld16_stream(X + row * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
+      dyn[i] = (ok && has_dy) ? ld16_stream(dY + row * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
+      xn[i] = ok ? ld16_stream(X + row * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
+    }
+  }
+  for (; row < n_rows; row += gridDim.x) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) { dyv[i] = dyn[i]; xv[i] = xn[i]; }
+    // this row's dS and the next row's dY / X go in flight before the reduction below
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = tid + i * THREADS;
+      dsv[i] = (has_ds && v < n_vec) ? ld16_stream(dS + row * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
+    }
+    const int64_t nrow = row + gridDim.x;
+    if (nrow < n_rows) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int v = tid + i * THREADS;
+        const bool ok = v < n_vec;
+        dyn[i] = (ok && has_dy) ? ld16_stream(dY + nrow * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
+        xn[i] = ok ? ld16_stream(X + nrow * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
+      }
     }
     const float rstd = RSTD[row];
     float acc = 0.f;
@@ -183,21 +217,16 @@ norm_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __r
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = tid + i * THREADS;
-      float dy[VEC], x[VEC], dx[VEC], w[VEC];
+      float dy[VEC], x[VEC], dx[VEC], w[VEC], ds[VEC];
       VT<T>::unpack(dyv[i], dy);
       VT<T>::unpack(xv[i], x);
+      VT<T>::unpack(dsv[i], ds);
       if (v < n_vec) {
         load_w_vec<VEC>(W, w_dt, v * VEC, w);
 #pragma unroll
         for (int j = 0; j < VEC; ++j) {
-          dx[j] = rstd * (dy[j] * w[j]) - coef * x[j];
+          dx[j] = rstd * (dy[j] * w[j]) - coef * x[j] + ds[j];
           dw[i][j] = fmaf(dy[j], x[j] * rstd, dw[i][j]);
-        }
-        if (dS != nullptr) {
-          float ds[VEC];
-          VT<T>::unpack(ld16_stream(dS + row * n_cols + (int64_t)v * VEC), ds);
-#pragma unroll
-          for (int j = 0; j < VEC; ++j) dx[j] += ds[j];
         }
         st16(dX + row * n_cols + (int64_t)v * VEC, VT<T>::pack(dx));
       }
@@ -308,7 +337,13 @@ static int norm_fwd_t(const void* x, const void* r, const void* w, int w_dt, voi
     HILDA_LAUNCH_CHECK();
     return HILDA_OK;
   }
-  int grid = (int)(n_rows < max_grid ? n_rows : max_grid);
+  int per_sm = 4;
+#define FWD_OCC(TT, TH, VP) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, norm_fwd_kernel<TT, TH, VP>, TH, 0)
+  NORM_DISPATCH_TV(T, FWD_OCC)
+#undef FWD_OCC
+  if (per_sm < 1) per_sm = 1;
+  int64_t want = (int64_t)sm_count() * per_sm;
+  int grid = (int)(n_rows < want ? n_rows : want);
 #define FWD_CALL(TT, TH, VP)                                                                            \
   norm_fwd_kernel<TT, TH, VP><<<grid, TH, 0, st>>>((const TT*)x, (const TT*)r, w, w_dt, (TT*)y, (TT*)s, rstd, \
                                                     n_rows, (int)n_cols, eps)

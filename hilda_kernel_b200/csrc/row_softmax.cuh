@@ -66,8 +66,11 @@ __device__ __forceinline__ void opaque(uint4& v) {
 constexpr int ROW_THREADS = 256;
 
 // Register-resident, cluster-per-row kernel. Requires V % VEC == 0 and 16-byte aligned rows.
+// CTAs per SM the register budget is held to (the row slice itself takes 4*NV registers).
+constexpr int row_min_blocks(int nv) { return nv <= 8 ? 4 : (nv <= 10 ? 3 : 2); }
+
 template <typename T, int NV, int CLUSTER, class Op>
-__global__ void __launch_bounds__(ROW_THREADS)
+__global__ void __launch_bounds__(ROW_THREADS, row_min_blocks(NV))
 row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V, Op op) {
   constexpr int VEC = VT<T>::N;
   __shared__ float red[33];
@@ -106,16 +109,20 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
   float x_t = 0.f;
   if (target >= 0 && target < V) x_t = VT<T>::load1(xr + target) * inv_t;
 
-  float m = -INFINITY;
+  // pass 1: max of the raw logits (k > 0, so the scale is applied once to the maximum)
+  float m_raw = -INFINITY;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     float f[VEC];
     VT<T>::unpack(xv[i], f);
 #pragma unroll
-    for (int j = 0; j < VEC; ++j) m = fmaxf(m, f[j] * k);
+    for (int j = 0; j < VEC; ++j) m_raw = fmaxf(m_raw, f[j]);
   }
-  m = block_max<ROW_THREADS>(m, red);
+  float m = block_max<ROW_THREADS>(m_raw, red) * k;
   const float m_safe = (m == -INFINITY) ? 0.f : m;
+  // pass 2: e = 2^(x*k - m) summed in fp32, and kept IN PLACE of x (rounded to T): the gradient
+  // pass then needs one multiply per element instead of a second exponential (the SFU would
+  // otherwise be the bottleneck at HBM speed).
   float s = 0.f;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
@@ -123,7 +130,12 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
     opaque(xv[i]);
     VT<T>::unpack(xv[i], f);
 #pragma unroll
-    for (int j = 0; j < VEC; ++j) s += ex2_approx(fmaf(f[j], k, -m_safe));
+    for (int j = 0; j < VEC; ++j) {
+      f[j] = ex2_approx(fmaf(f[j], k, -m_safe));
+      s += f[j];
+    }
+    xv[i] = VT<T>::pack(f);
+    opaque(xv[i]);  // orders the iterations: at most one vector is unpacked to fp32 at a time
   }
   s = block_sum<ROW_THREADS>(s, red);
 
@@ -155,6 +167,8 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
 
   const int64_t tvec = (target >= 0 && target < V) ? target / VEC : -1;
   const int tsub = (int)(target - tvec * VEC);
+  // softmax_j = e_j * 2^(m_cta - lse2)
+  const float coef = (m == -INFINITY) ? 0.f : co.alpha * exp2f(m - lse2);
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int v = v0 + tid + i * ROW_THREADS;
@@ -162,7 +176,7 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
     opaque(xv[i]);
     VT<T>::unpack(xv[i], f);
 #pragma unroll
-    for (int j = 0; j < VEC; ++j) f[j] = co.alpha * ex2_approx(fmaf(f[j], k, -lse2));
+    for (int j = 0; j < VEC; ++j) f[j] *= coef;
     if (v == tvec) {
 #pragma unroll
       for (int j = 0; j < VEC; ++j)

@@ -42,8 +42,9 @@ def test_size_queries_need_no_gpu(libpath):
     assert lib.hilda_flce_logits_pitch(16032) == 16128
     assert lib.hilda_flce_padded_rows(100) == 128
     assert lib.hilda_flce_stat_tiles(128256) == 501
-    assert lib.hilda_flce_default_chunk_rows(16384, 4096, 128256) == 4096
+    assert lib.hilda_flce_default_chunk_rows(16384, 4096, 128256) == 4736  # 37 x 16 tiles = 4 waves of 148 SMs
     assert lib.hilda_flce_default_chunk_rows(100, 64, 1000) == 100
+    assert lib.hilda_flce_default_chunk_rows(4096, 4096, 128256) == 4096
     one = lib.hilda_flce_workspace_bytes(4096, 4096, 128256, 4096, 1)
     four = lib.hilda_flce_workspace_bytes(16384, 4096, 128256, 4096, 1)
     assert four - one >= 128256 * 4096 * 4  # the fp32 dW accumulator appears only with > 1 chunk

@@ -6,12 +6,24 @@
 // GRPO follows kernels/grpo_loss.py:87-159 (forward), :166-234 (backward) and :290-295, :309-310
 // (reductions and the per-token upstream scale); here forward and backward are one kernel that
 // writes dlogits for a unit upstream gradient, so the logits are read once.
+#include <cstdio>
+#include <cstdlib>
 #include "row_softmax.cuh"
 #include "reduce_kernels.cuh"
 
 namespace hilda {
 
 int g_row_force_nv = 0, g_row_force_cluster = 0;
+
+// Tuning runs may preset the plan through the environment: HILDA_ROW_ENGINE="nv,cluster".
+static const bool g_row_env_applied = []() {
+  const char* e = getenv("HILDA_ROW_ENGINE");
+  if (e) {
+    int a = 0, b = 0;
+    if (sscanf(e, "%d,%d", &a, &b) == 2) { g_row_force_nv = a; g_row_force_cluster = b; }
+  }
+  return true;
+}();
 
 // ---------------------------------------------------------------- CrossEntropy
 struct CEOp {
@@ -206,10 +218,9 @@ extern "C" {
 
 // Tuning hook: force (vectors per thread, cluster size) of the row engine; (0,0) restores automatic.
 void hilda_row_engine_force(int nv, int cluster) { g_row_force_nv = nv; g_row_force_cluster = cluster; }
-
 int64_t hilda_cross_entropy_workspace_bytes(int64_t n_rows) { return 16 + (n_rows > 0 ? n_rows : 0) * 4; }
 
-// workspace layout: int n_valid at byte 0, float loss_rows[n_rows] at byte 16 (only used when the
+// workspace layout: int n_valid at byte 0, int status at byte 8, float loss_rows[n_rows] at byte 16 (only used when the
 // caller passes loss_rows == null).
 // reduction: 0 none, 1 mean, 2 sum. grad may be null (inference path: loss only).
 // loss_out: scalar for mean/sum; unused for none (per-row loss is in loss_rows).
@@ -222,6 +233,8 @@ int hilda_cross_entropy_fwd(const void* logits, const int64_t* targets, void* gr
   if (reduction != 0 && !loss_out) return HILDA_ERR_NULL;
   cudaStream_t st = (cudaStream_t)stream;
   int* n_valid = reinterpret_cast<int*>(workspace);
+  int* status = n_valid + 2;  // byte 8 of the workspace: non-zero if a bounded device-side wait ran out
+  if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) return HILDA_ERR_CUDA;
   float* rows = loss_rows ? loss_rows : reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 16);
   count_valid_kernel<<<1, 1024, 0, st>>>(targets, n_rows, ignore_index, n_valid);
   HILDA_LAUNCH_CHECK();
@@ -233,9 +246,9 @@ int hilda_cross_entropy_fwd(const void* logits, const int64_t* targets, void* gr
   op.loss_rows = rows; op.lse_rows = lse_rows;
   int rc;
   switch (dtype) {
-    case HILDA_F32: rc = launch_rows<float, CEOp>(logits, grad, n_rows, V, op, st); break;
-    case HILDA_BF16: rc = launch_rows<__nv_bfloat16, CEOp>(logits, grad, n_rows, V, op, st); break;
-    case HILDA_F16: rc = launch_rows<__half, CEOp>(logits, grad, n_rows, V, op, st); break;
+    case HILDA_F32: rc = launch_rows<float, CEOp>(logits, grad, n_rows, V, op, status, st); break;
+    case HILDA_BF16: rc = launch_rows<__nv_bfloat16, CEOp>(logits, grad, n_rows, V, op, status, st); break;
+    case HILDA_F16: rc = launch_rows<__half, CEOp>(logits, grad, n_rows, V, op, status, st); break;
     default: return HILDA_ERR_DTYPE;
   }
   if (rc != HILDA_OK) return rc;
@@ -277,6 +290,8 @@ int hilda_grpo_loss_fwd(const void* logits, const int64_t* ids, const float* adv
   if (B < 0 || L < 0 || V <= 0 || !(temperature > 0.f)) return HILDA_ERR_SIZE;
   cudaStream_t st = (cudaStream_t)stream;
   float* seq_len = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 16);
+  int* status = reinterpret_cast<int*>(workspace);  // byte 0: non-zero if a bounded device-side wait ran out
+  if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) return HILDA_ERR_CUDA;
   if (B > 0) {
     grpo_seq_len_kernel<<<(unsigned)B, 256, 0, st>>>(mask, L, seq_len);
     HILDA_LAUNCH_CHECK();
@@ -289,9 +304,9 @@ int hilda_grpo_loss_fwd(const void* logits, const int64_t* ids, const float* adv
   const int64_t n_rows = B * (L + 1);
   int rc;
   switch (dtype) {
-    case HILDA_F32: rc = launch_rows<float, GRPOOp>(logits, grad, n_rows, V, op, st); break;
-    case HILDA_BF16: rc = launch_rows<__nv_bfloat16, GRPOOp>(logits, grad, n_rows, V, op, st); break;
-    case HILDA_F16: rc = launch_rows<__half, GRPOOp>(logits, grad, n_rows, V, op, st); break;
+    case HILDA_F32: rc = launch_rows<float, GRPOOp>(logits, grad, n_rows, V, op, status, st); break;
+    case HILDA_BF16: rc = launch_rows<__nv_bfloat16, GRPOOp>(logits, grad, n_rows, V, op, status, st); break;
+    case HILDA_F16: rc = launch_rows<__half, GRPOOp>(logits, grad, n_rows, V, op, status, st); break;
     default: return HILDA_ERR_DTYPE;
   }
   if (rc != HILDA_OK) return rc;
@@ -311,9 +326,9 @@ int hilda_selective_log_softmax(const void* logits, const int64_t* ids, const in
   op.logp_only = 1;
   const int64_t n_rows = B * (L + 1);
   switch (dtype) {
-    case HILDA_F32: return launch_rows<float, GRPOOp>(logits, nullptr, n_rows, V, op, st);
-    case HILDA_BF16: return launch_rows<__nv_bfloat16, GRPOOp>(logits, nullptr, n_rows, V, op, st);
-    case HILDA_F16: return launch_rows<__half, GRPOOp>(logits, nullptr, n_rows, V, op, st);
+    case HILDA_F32: return launch_rows<float, GRPOOp>(logits, nullptr, n_rows, V, op, nullptr, st);
+    case HILDA_BF16: return launch_rows<__nv_bfloat16, GRPOOp>(logits, nullptr, n_rows, V, op, nullptr, st);
+    case HILDA_F16: return launch_rows<__half, GRPOOp>(logits, nullptr, n_rows, V, op, nullptr, st);
   }
   return HILDA_ERR_DTYPE;
 }

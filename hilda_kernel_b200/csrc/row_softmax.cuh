@@ -63,14 +63,88 @@ __device__ __forceinline__ void opaque(uint4& v) {
   asm volatile("" : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w));
 }
 
-constexpr int ROW_THREADS = 256;
+
+// ---- per-vector math, specialised per dtype to keep the instruction count per element low ------
+// vmax : running maximum over a packed vector (packed 16-bit max for bf16/fp16, no unpacking)
+// scale: v * coef in place. For 16-bit types coef is split into hi + lo parts in T so that the
+//        packed fused multiply-add e*hi + (e*lo) rounds like one fp32 multiply followed by a
+//        rounding to T.
+template <typename T> struct RowMath;
+
+template <> struct RowMath<float> {
+  struct MaxAcc { float m; };
+  struct Coef { float c; };
+  static __device__ __forceinline__ MaxAcc max_init() { return MaxAcc{-INFINITY}; }
+  static __device__ __forceinline__ void vmax(MaxAcc& a, const uint4& v) {
+    a.m = fmaxf(fmaxf(a.m, __uint_as_float(v.x)), fmaxf(__uint_as_float(v.y), fmaxf(__uint_as_float(v.z), __uint_as_float(v.w))));
+  }
+  static __device__ __forceinline__ float max_final(const MaxAcc& a) { return a.m; }
+  static __device__ __forceinline__ Coef make_coef(float c) { return Coef{c}; }
+  static __device__ __forceinline__ void scale(uint4& v, const Coef& c) {
+    v.x = __float_as_uint(__uint_as_float(v.x) * c.c); v.y = __float_as_uint(__uint_as_float(v.y) * c.c);
+    v.z = __float_as_uint(__uint_as_float(v.z) * c.c); v.w = __float_as_uint(__uint_as_float(v.w) * c.c);
+  }
+};
+
+template <typename P2, typename T> struct RowMath16 {
+  struct MaxAcc { P2 m; };
+  struct Coef { P2 hi, lo; };
+  static __device__ __forceinline__ MaxAcc max_init() {
+    const uint4 n = neg_inf_vec<T>();
+    return MaxAcc{*reinterpret_cast<const P2*>(&n.x)};
+  }
+  static __device__ __forceinline__ void vmax(MaxAcc& a, const uint4& v) {
+    const P2* p = reinterpret_cast<const P2*>(&v);
+    a.m = __hmax2(__hmax2(a.m, p[0]), __hmax2(p[1], __hmax2(p[2], p[3])));
+  }
+  static __device__ __forceinline__ float max_final(const MaxAcc& a) {
+    return fmaxf(VT<T>::load1(reinterpret_cast<const T*>(&a.m)), VT<T>::load1(reinterpret_cast<const T*>(&a.m) + 1));
+  }
+  static __device__ __forceinline__ Coef make_coef(float c) {
+    T hi, lo;
+    VT<T>::store1(&hi, c);
+    VT<T>::store1(&lo, c - VT<T>::load1(&hi));
+    Coef r;
+    T* ph = reinterpret_cast<T*>(&r.hi);
+    T* pl = reinterpret_cast<T*>(&r.lo);
+    ph[0] = hi; ph[1] = hi; pl[0] = lo; pl[1] = lo;
+    return r;
+  }
+  static __device__ __forceinline__ void scale(uint4& v, const Coef& c) {
+    P2* p = reinterpret_cast<P2*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) p[j] = __hfma2(p[j], c.hi, __hmul2(p[j], c.lo));
+  }
+};
+template <> struct RowMath<__nv_bfloat16> : RowMath16<__nv_bfloat162, __nv_bfloat16> {};
+template <> struct RowMath<__half> : RowMath16<__half2, __half> {};
+
+// v <- 2^(v*k - m) (rounded to T), returns the fp32 sum of the eight/four exponentials
+template <typename T>
+__device__ __forceinline__ float vec_exp_inplace(uint4& v, float k, float m) {
+  constexpr int VEC = VT<T>::N;
+  float f[VEC];
+  VT<T>::unpack(v, f);
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) {
+    f[j] = ex2_approx(fmaf(f[j], k, -m));
+    s += f[j];
+  }
+  v = VT<T>::pack(f);
+  return s;
+}
+
+constexpr int ROW_THREADS_DEFAULT = 256;
 
 // Register-resident, cluster-per-row kernel. Requires V % VEC == 0 and 16-byte aligned rows.
 // CTAs per SM the register budget is held to (the row slice itself takes 4*NV registers).
-constexpr int row_min_blocks(int nv) { return nv <= 8 ? 4 : (nv <= 10 ? 3 : 2); }
+constexpr int row_min_blocks(int threads, int nv) {
+  return nv <= 8 ? (threads <= 256 ? 4 : (threads <= 320 ? 3 : 2)) : (nv <= 10 ? 3 : 2);
+}
 
-template <typename T, int NV, int CLUSTER, class Op>
-__global__ void __launch_bounds__(ROW_THREADS, row_min_blocks(NV))
+template <typename T, int ROW_THREADS, int NV, int CLUSTER, class Op>
+__global__ void __launch_bounds__(ROW_THREADS, row_min_blocks(ROW_THREADS, NV))
 row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V, Op op) {
   constexpr int VEC = VT<T>::N;
   __shared__ float red[33];
@@ -98,27 +172,23 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
     return;
   }
 
+  // per-thread base pointers: vector i of this thread sits at a compile-time offset from them
+  const int my_vec = v1 - v0;  // vectors in this CTA's slice
+  const uint4* src = reinterpret_cast<const uint4*>(xr) + v0 + tid;
   uint4 xv[NV];
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int v = v0 + tid + i * ROW_THREADS;
-    xv[i] = (v < v1) ? ld16_stream(xr + (int64_t)v * VEC) : neg_inf_vec<T>();
-  }
+  for (int i = 0; i < NV; ++i)
+    xv[i] = (tid + i * ROW_THREADS < my_vec) ? ld16_stream(src + i * ROW_THREADS) : neg_inf_vec<T>();
   const float inv_t = op.inv_temperature();
   const float k = inv_t * LOG2E;  // logits -> log2 domain
   float x_t = 0.f;
   if (target >= 0 && target < V) x_t = VT<T>::load1(xr + target) * inv_t;
 
   // pass 1: max of the raw logits (k > 0, so the scale is applied once to the maximum)
-  float m_raw = -INFINITY;
+  typename RowMath<T>::MaxAcc macc = RowMath<T>::max_init();
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    float f[VEC];
-    VT<T>::unpack(xv[i], f);
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) m_raw = fmaxf(m_raw, f[j]);
-  }
-  float m = block_max<ROW_THREADS>(m_raw, red) * k;
+  for (int i = 0; i < NV; ++i) RowMath<T>::vmax(macc, xv[i]);
+  float m = block_max<ROW_THREADS>(RowMath<T>::max_final(macc), red) * k;
   const float m_safe = (m == -INFINITY) ? 0.f : m;
   // pass 2: e = 2^(x*k - m) summed in fp32, and kept IN PLACE of x (rounded to T): the gradient
   // pass then needs one multiply per element instead of a second exponential (the SFU would
@@ -126,15 +196,8 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
   float s = 0.f;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
-    float f[VEC];
     opaque(xv[i]);
-    VT<T>::unpack(xv[i], f);
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) {
-      f[j] = ex2_approx(fmaf(f[j], k, -m_safe));
-      s += f[j];
-    }
-    xv[i] = VT<T>::pack(f);
+    s += vec_exp_inplace<T>(xv[i], k, m_safe);
     opaque(xv[i]);  // orders the iterations: at most one vector is unpacked to fp32 at a time
   }
   s = block_sum<ROW_THREADS>(s, red);
@@ -154,10 +217,7 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
     for (int c = 0; c < CLUSTER; ++c) M = fmaxf(M, xchg[2 * c]);
     S = 0.f;
 #pragma unroll
-    for (int c = 0; c < CLUSTER; ++c) {
-      const float mc = xchg[2 * c];
-      S += (mc == -INFINITY) ? 0.f : xchg[2 * c + 1] * exp2f(mc - M);
-    }
+    for (int c = 0; c < CLUSTER; ++c) S = fmaf(xchg[2 * c + 1], ex2_approx(xchg[2 * c] - M), S);  // empty slice: 0 * 2^-inf
   }
   const float lse2 = M + log2f(S);
   const float lse = lse2 * LN2;  // natural-log logsumexp of logits/T
@@ -165,24 +225,21 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
   const RowCoef co = op.finish(row, lse, x_t, writer);
   if (!gr) return;
 
-  const int64_t tvec = (target >= 0 && target < V) ? target / VEC : -1;
-  const int tsub = (int)(target - tvec * VEC);
   // softmax_j = e_j * 2^(m_cta - lse2)
-  const float coef = (m == -INFINITY) ? 0.f : co.alpha * exp2f(m - lse2);
+  const float coef = (m == -INFINITY) ? 0.f : co.alpha * ex2_approx(m - lse2);
+  const typename RowMath<T>::Coef pc = RowMath<T>::make_coef(coef);
+  uint4* dst = reinterpret_cast<uint4*>(gr) + v0 + tid;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
-    const int v = v0 + tid + i * ROW_THREADS;
-    float f[VEC];
-    opaque(xv[i]);
-    VT<T>::unpack(xv[i], f);
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) f[j] *= coef;
-    if (v == tvec) {
-#pragma unroll
-      for (int j = 0; j < VEC; ++j)
-        if (j == tsub) f[j] += co.beta;
-    }
-    if (v < v1) st16_stream(gr + (int64_t)v * VEC, VT<T>::pack(f));
+    RowMath<T>::scale(xv[i], pc);
+    if (tid + i * ROW_THREADS < my_vec) st16_stream(dst + i * ROW_THREADS, xv[i]);
+  }
+  // The target column gets alpha*softmax + beta: the thread that stored its vector overwrites that
+  // one element afterwards (same thread, same address: program order holds).
+  if (target >= 0 && target < V) {
+    const int tv = (int)(target / VEC) - v0;
+    if (tv >= 0 && tv < my_vec && (tv % ROW_THREADS) == tid)
+      VT<T>::store1(gr + target, co.alpha * ex2_approx((x_t - lse) * LOG2E) + co.beta);
   }
 }
 
@@ -227,18 +284,21 @@ row_softmax_generic_kernel(const T* __restrict__ logits, T* __restrict__ grad, i
   }
 }
 
-struct RowPlan { int nv; int cluster; bool generic; };
+struct RowPlan { int threads; int nv; int cluster; bool generic; };
 
-// Pick (vectors per thread, cluster size) so that cluster * 256 * nv vectors cover the row.
+// Pick (threads, vectors per thread, cluster size) so that cluster * threads * nv vectors cover the
+// row with as few idle slots as possible. force_nv may carry the thread count as threads*100 + nv.
 static inline RowPlan plan_row(int64_t V, int vec, bool aligned, int force_nv, int force_cluster) {
-  RowPlan p{0, 1, true};
+  RowPlan p{ROW_THREADS_DEFAULT, 0, 1, true};
   if (!aligned || V % vec != 0 || V / vec > 0x7fffffff) return p;
   const int64_t n_vec = V / vec;
   if (force_nv > 0 && force_cluster > 0) {
-    if ((int64_t)force_nv * force_cluster * ROW_THREADS >= n_vec) { p.nv = force_nv; p.cluster = force_cluster; p.generic = false; }
+    const int th = force_nv >= 100 ? force_nv / 100 : ROW_THREADS_DEFAULT;
+    const int nv = force_nv % 100;
+    if ((int64_t)nv * force_cluster * th >= n_vec) { p.threads = th; p.nv = nv; p.cluster = force_cluster; p.generic = false; }
     return p;
   }
-  const int64_t per = ROW_THREADS;
+  const int64_t per = ROW_THREADS_DEFAULT;
   if (n_vec <= per * 1) { p.nv = 1; }
   else if (n_vec <= per * 2) { p.nv = 2; }
   else if (n_vec <= per * 4) { p.nv = 4; }
@@ -246,19 +306,19 @@ static inline RowPlan plan_row(int64_t V, int vec, bool aligned, int force_nv, i
   else if (n_vec <= per * 8 * 2) { p.nv = 8; p.cluster = 2; }
   else if (n_vec <= per * 8 * 4) { p.nv = 8; p.cluster = 4; }
   else if (n_vec <= per * 8 * 8) { p.nv = 8; p.cluster = 8; }
-  else if (n_vec <= per * 10 * 8) { p.nv = 10; p.cluster = 8; }
-  else if (n_vec <= per * 12 * 8) { p.nv = 12; p.cluster = 8; }
-  else if (n_vec <= per * 16 * 8) { p.nv = 16; p.cluster = 8; }
+  else if (n_vec <= 320 * 8 * 8) { p.threads = 320; p.nv = 8; p.cluster = 8; }
+  else if (n_vec <= 384 * 8 * 8) { p.threads = 384; p.nv = 8; p.cluster = 8; }
+  else if (n_vec <= 512 * 8 * 8) { p.threads = 512; p.nv = 8; p.cluster = 8; }
   else return p;
   p.generic = false;
   return p;
 }
 
-template <typename T, int NV, int CLUSTER, class Op>
+template <typename T, int THREADS, int NV, int CLUSTER, class Op>
 static int launch_row_cfg(const T* logits, T* grad, int64_t n_rows, int64_t V, const Op& op, cudaStream_t st) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(n_rows * CLUSTER), 1, 1);
-  cfg.blockDim = dim3(ROW_THREADS, 1, 1);
+  cfg.blockDim = dim3(THREADS, 1, 1);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -268,7 +328,7 @@ static int launch_row_cfg(const T* logits, T* grad, int64_t n_rows, int64_t V, c
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, row_softmax_kernel<T, NV, CLUSTER, Op>, logits, grad, V, op);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, row_softmax_kernel<T, THREADS, NV, CLUSTER, Op>, logits, grad, V, op);
   return e == cudaSuccess ? HILDA_OK : HILDA_ERR_CUDA;
 }
 
@@ -276,22 +336,26 @@ static int launch_row_cfg(const T* logits, T* grad, int64_t n_rows, int64_t V, c
 extern int g_row_force_nv, g_row_force_cluster;
 
 template <typename T, class Op>
-static int launch_rows(const void* logits_v, void* grad_v, int64_t n_rows, int64_t V, const Op& op, cudaStream_t st) {
+static int launch_rows(const void* logits_v, void* grad_v, int64_t n_rows, int64_t V, const Op& op, int* status,
+                       cudaStream_t st) {
   const T* logits = (const T*)logits_v;
   T* grad = (T*)grad_v;
   if (n_rows == 0) return HILDA_OK;
   if (n_rows * 8 > 0x7fffffffLL) return HILDA_ERR_SIZE;
   const bool al = aligned16(logits) && (!grad || aligned16(grad)) && op.rows_aligned(V, VT<T>::N);
+  (void)status;
   const RowPlan p = plan_row(V, VT<T>::N, al, g_row_force_nv, g_row_force_cluster);
   if (p.generic) {
     row_softmax_generic_kernel<T, Op><<<(unsigned)n_rows, 512, 0, st>>>(logits, grad, V, op);
     HILDA_LAUNCH_CHECK();
     return HILDA_OK;
   }
-#define ROW_CFG(NV_, CL_) \
-  if (p.nv == NV_ && p.cluster == CL_) return launch_row_cfg<T, NV_, CL_, Op>(logits, grad, n_rows, V, op, st);
-  ROW_CFG(1, 1) ROW_CFG(2, 1) ROW_CFG(4, 1) ROW_CFG(8, 1) ROW_CFG(8, 2) ROW_CFG(8, 4) ROW_CFG(8, 8)
-  ROW_CFG(10, 8) ROW_CFG(12, 8) ROW_CFG(16, 8) ROW_CFG(16, 4) ROW_CFG(16, 2)
+#define ROW_CFG(TH_, NV_, CL_) \
+  if (p.threads == TH_ && p.nv == NV_ && p.cluster == CL_)  \
+    return launch_row_cfg<T, TH_, NV_, CL_, Op>(logits, grad, n_rows, V, op, st);
+  ROW_CFG(256, 1, 1) ROW_CFG(256, 2, 1) ROW_CFG(256, 4, 1) ROW_CFG(256, 8, 1) ROW_CFG(256, 8, 2) ROW_CFG(256, 8, 4)
+  ROW_CFG(256, 8, 8) ROW_CFG(256, 10, 8) ROW_CFG(256, 12, 8) ROW_CFG(256, 16, 8) ROW_CFG(256, 16, 4)
+  ROW_CFG(256, 16, 2) ROW_CFG(320, 8, 8) ROW_CFG(384, 8, 8) ROW_CFG(512, 8, 8) ROW_CFG(512, 4, 8)
 #undef ROW_CFG
   return HILDA_ERR_SIZE;
 }

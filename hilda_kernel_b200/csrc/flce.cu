@@ -13,7 +13,8 @@
 //   4. dHidden = dlogits @ W and dW += dlogits^T @ hidden run on the same tcgen05 kernel with
 //      MN-major operands (no transposed copies); dW is accumulated across chunks in fp32 and
 //      rounded once at the end (the reference accumulates in the 16-bit dtype).
-#include "tcgen05_gemm.cuh"
+#include <cstdlib>
+#include "tcgen05_gemm2.cuh"
 #include "reduce_kernels.cuh"
 
 namespace hilda {
@@ -113,6 +114,19 @@ flce_dlogits_kernel(T* __restrict__ logits, int64_t pitch, const float* __restri
 
 static inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
 
+// 1: GEMMs run as CTA pairs (256 x 256 tiles, cta_group::2); 0: one CTA per 128 x 256 tile.
+// HILDA_GEMM_PAIR in the environment presets it.
+static int g_gemm_pair = []() {
+  const char* e = getenv("HILDA_GEMM_PAIR");
+  return e ? atoi(e) : 0;
+}();
+
+template <bool A_MN, bool B_MN, int EPI>
+static int run_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, const GemmParams& p, cudaStream_t st) {
+  if (g_gemm_pair) return launch_gemm2<A_MN, B_MN, EPI>(A, lda, B, ldb, p, st);
+  return run_gemm<A_MN, B_MN, EPI>(A, lda, B, ldb, p, st);
+}
+
 // Optional timing of the GEMM launches with CUDA events on the launching stream (off by default).
 // kind 0 = logits GEMM, 1 = d(hidden) GEMM, 2 = d(W) GEMM.
 constexpr int PROF_MAX = 4096;
@@ -149,21 +163,22 @@ static int flce_logits(const void* hidden, const void* W, void* logits, float* s
   p.stats = reinterpret_cast<float2*>(stats); p.stats_ld = (V + BN - 1) / BN;
   p.status = status;
   ProfScope prof(0, st);
-  return launch_gemm<false, false, EPI_LOGITS_STATS>(hidden, H, W, H, p, st);
+  return run_gemm<false, false, EPI_LOGITS_STATS>(hidden, H, W, H, p, st);
 }
 
 static int flce_grad_hidden(const void* dlogits, const void* W, void* dh16, float* dh32, int64_t rows, int64_t H,
                             int64_t V, int is_bf16, int* status, cudaStream_t st) {
   GemmParams p = {};
-  p.M = (int)rows; p.N = (int)H; p.K = (int)V; p.m_fast = 1; p.is_bf16 = is_bf16; p.status = status;
+  static const int mfast = []() { const char* e = getenv("HILDA_GEMM2_MFAST"); return e ? atoi(e) : 1; }();
+  p.M = (int)rows; p.N = (int)H; p.K = (int)V; p.m_fast = mfast; p.is_bf16 = is_bf16; p.status = status;
   const int64_t pitch = round_up(V, BN);
   ProfScope prof(1, st);
   if (dh16) {
     p.C16 = dh16; p.ldc16 = H;
-    return launch_gemm<false, true, EPI_STORE16>(dlogits, pitch, W, H, p, st);
+    return run_gemm<false, true, EPI_STORE16>(dlogits, pitch, W, H, p, st);
   }
   p.C32 = dh32; p.ldc32 = H;
-  return launch_gemm<false, true, EPI_STORE32>(dlogits, pitch, W, H, p, st);
+  return run_gemm<false, true, EPI_STORE32>(dlogits, pitch, W, H, p, st);
 }
 
 // mode 0: dw32 = D^T h; 1: dw32 += D^T h; 2: dw16 = dw32 + D^T h; 3: dw16 = D^T h
@@ -175,10 +190,10 @@ static int flce_grad_weight(const void* dlogits, const void* hidden, float* dw32
   const int64_t pitch = round_up(V, BN);
   ProfScope prof(2, st);
   switch (mode) {
-    case 0: return launch_gemm<true, true, EPI_STORE32>(dlogits, pitch, hidden, H, p, st);
-    case 1: return launch_gemm<true, true, EPI_ACCUM32>(dlogits, pitch, hidden, H, p, st);
-    case 2: return launch_gemm<true, true, EPI_ACCUM_FINAL16>(dlogits, pitch, hidden, H, p, st);
-    case 3: return launch_gemm<true, true, EPI_STORE16>(dlogits, pitch, hidden, H, p, st);
+    case 0: return run_gemm<true, true, EPI_STORE32>(dlogits, pitch, hidden, H, p, st);
+    case 1: return run_gemm<true, true, EPI_ACCUM32>(dlogits, pitch, hidden, H, p, st);
+    case 2: return run_gemm<true, true, EPI_ACCUM_FINAL16>(dlogits, pitch, hidden, H, p, st);
+    case 3: return run_gemm<true, true, EPI_STORE16>(dlogits, pitch, hidden, H, p, st);
   }
   return HILDA_ERR_ARG;
 }
@@ -197,7 +212,7 @@ using namespace hilda;
 extern "C" {
 
 int64_t hilda_flce_logits_pitch(int64_t V) { return round_up(V, BN); }
-int64_t hilda_flce_padded_rows(int64_t rows) { return round_up(rows, BM); }
+int64_t hilda_flce_padded_rows(int64_t rows) { return round_up(rows, 2 * BM); }
 int64_t hilda_flce_stat_tiles(int64_t V) { return (V + BN - 1) / BN; }
 
 int hilda_count_valid(const int64_t* targets, int64_t n, int64_t ignore_index, int* out, void* stream) {
@@ -317,7 +332,7 @@ int64_t hilda_flce_default_chunk_rows(int64_t BT, int64_t H, int64_t V) {
 //   dw32     float [V, H]          (only when BT > chunk_rows and gradients are requested)
 static int64_t flce_ws_layout(int64_t BT, int64_t H, int64_t V, int64_t chunk, int with_grad, int64_t* off) {
   int64_t o = 256;
-  off[0] = o; o = round_up(o + round_up(chunk, BM) * round_up(V, BN) * 2, 256);
+  off[0] = o; o = round_up(o + round_up(chunk, 2 * BM) * round_up(V, BN) * 2, 256);
   off[1] = o; o = round_up(o + chunk * ((V + BN - 1) / BN) * 8, 256);
   off[2] = o; o = round_up(o + 3 * chunk * 4, 256);
   off[3] = o; o = round_up(o + chunk * 4, 256);
@@ -427,6 +442,10 @@ int hilda_flce_profile_collect(float* ms_per_kind, int* launches_per_kind) {
   return HILDA_OK;
 }
 
+// Select the GEMM variant: 1 = CTA pairs (cta_group::2, 256 x 256 tiles), 0 = single CTAs.
+void hilda_gemm_set_pair(int enable) { g_gemm_pair = enable ? 1 : 0; }
+int hilda_gemm_get_pair(void) { return g_gemm_pair; }
+
 // Plain GEMM through the same kernel, for validating operand layouts against a library matmul.
 // A is [M,K] (a_mn=0) or stored [K,M] (a_mn=1); B is [N,K] (b_mn=0) or stored [K,N] (b_mn=1);
 // exactly one of c16 / c32 is written. mn_lbo/mn_sbo = 0 selects the defaults.
@@ -444,17 +463,17 @@ int hilda_debug_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, voi
   const int key = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
   if (c16) {
     switch (key) {
-      case 0: return launch_gemm<false, false, EPI_STORE16>(A, lda, B, ldb, p, st);
-      case 1: return launch_gemm<false, true, EPI_STORE16>(A, lda, B, ldb, p, st);
-      case 2: return launch_gemm<true, false, EPI_STORE16>(A, lda, B, ldb, p, st);
-      default: return launch_gemm<true, true, EPI_STORE16>(A, lda, B, ldb, p, st);
+      case 0: return run_gemm<false, false, EPI_STORE16>(A, lda, B, ldb, p, st);
+      case 1: return run_gemm<false, true, EPI_STORE16>(A, lda, B, ldb, p, st);
+      case 2: return run_gemm<true, false, EPI_STORE16>(A, lda, B, ldb, p, st);
+      default: return run_gemm<true, true, EPI_STORE16>(A, lda, B, ldb, p, st);
     }
   }
   switch (key) {
-    case 0: return launch_gemm<false, false, EPI_STORE32>(A, lda, B, ldb, p, st);
-    case 1: return launch_gemm<false, true, EPI_STORE32>(A, lda, B, ldb, p, st);
-    case 2: return launch_gemm<true, false, EPI_STORE32>(A, lda, B, ldb, p, st);
-    default: return launch_gemm<true, true, EPI_STORE32>(A, lda, B, ldb, p, st);
+    case 0: return run_gemm<false, false, EPI_STORE32>(A, lda, B, ldb, p, st);
+    case 1: return run_gemm<false, true, EPI_STORE32>(A, lda, B, ldb, p, st);
+    case 2: return run_gemm<true, false, EPI_STORE32>(A, lda, B, ldb, p, st);
+    default: return run_gemm<true, true, EPI_STORE32>(A, lda, B, ldb, p, st);
   }
 }
 

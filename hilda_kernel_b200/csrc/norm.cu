@@ -159,7 +159,6 @@ norm_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __r
   __shared__ float red[33];
   const int tid = threadIdx.x;
   const float inv_n = 1.0f / (float)n_cols;
-  const bool has_dy = (dY != nullptr), has_ds = (dS != nullptr);
 
   // w is re-read per row (an L1 hit after the first row) rather than held in registers.
   float dw[VPT][VEC];
@@ -168,35 +167,14 @@ norm_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __r
 #pragma unroll
     for (int j = 0; j < VEC; ++j) dw[i][j] = 0.f;
 
-  uint4 dyv[VPT], xv[VPT], dyn[VPT], xn[VPT], dsv[VPT];
-  int64_t row = blockIdx.x;
-  if (row < n_rows) {
+  for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
+    uint4 dyv[VPT], xv[VPT];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = tid + i * THREADS;
       const bool ok = v < n_vec;
-      dyn[i] = (ok && has_dy) ? ld16_stream(dY + row * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
-      xn[i] = ok ? ld16_stream(X + row * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
-    }
-  }
-  for (; row < n_rows; row += gridDim.x) {
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) { dyv[i] = dyn[i]; xv[i] = xn[i]; }
-    // this row's dS and the next row's dY / X go in flight before the reduction below
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int v = tid + i * THREADS;
-      dsv[i] = (has_ds && v < n_vec) ? ld16_stream(dS + row * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
-    }
-    const int64_t nrow = row + gridDim.x;
-    if (nrow < n_rows) {
-#pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        const int v = tid + i * THREADS;
-        const bool ok = v < n_vec;
-        dyn[i] = (ok && has_dy) ? ld16_stream(dY + nrow * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
-        xn[i] = ok ? ld16_stream(X + nrow * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
-      }
+      dyv[i] = (ok && dY) ? ld16_stream(dY + row * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
+      xv[i] = ok ? ld16_stream(X + row * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
     }
     const float rstd = RSTD[row];
     float acc = 0.f;
@@ -217,16 +195,21 @@ norm_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __r
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = tid + i * THREADS;
-      float dy[VEC], x[VEC], dx[VEC], w[VEC], ds[VEC];
+      float dy[VEC], x[VEC], dx[VEC], w[VEC];
       VT<T>::unpack(dyv[i], dy);
       VT<T>::unpack(xv[i], x);
-      VT<T>::unpack(dsv[i], ds);
       if (v < n_vec) {
         load_w_vec<VEC>(W, w_dt, v * VEC, w);
 #pragma unroll
         for (int j = 0; j < VEC; ++j) {
-          dx[j] = rstd * (dy[j] * w[j]) - coef * x[j] + ds[j];
+          dx[j] = rstd * (dy[j] * w[j]) - coef * x[j];
           dw[i][j] = fmaf(dy[j], x[j] * rstd, dw[i][j]);
+        }
+        if (dS != nullptr) {
+          float ds[VEC];
+          VT<T>::unpack(ld16_stream(dS + row * n_cols + (int64_t)v * VEC), ds);
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) dx[j] += ds[j];
         }
         st16(dX + row * n_cols + (int64_t)v * VEC, VT<T>::pack(dx));
       }

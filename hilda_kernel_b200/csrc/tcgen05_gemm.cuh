@@ -155,6 +155,96 @@ __device__ __forceinline__ float ex2_fast(float x) {
   return y;
 }
 
+// Epilogue of one 128 x 256 accumulator tile for the calling thread (thread = TMEM lane = row).
+// taddr0: TMEM address of column 0 of the accumulator in this warp's lane quadrant.
+template <int EPI>
+__device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t taddr0, int64_t row, int col0, int nt) {
+  float run_m = -INFINITY, run_s = 0.f;
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld32(taddr0 + c * 32, r);
+    tmem_ld_wait();
+    const int cbase = col0 + c * 32;
+    if constexpr (EPI == EPI_STORE16 || EPI == EPI_LOGITS_STATS) {
+      uint32_t h[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) h[j] = pack16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]), p.is_bf16);
+      if constexpr (EPI == EPI_LOGITS_STATS) {
+        // scratch is padded to whole tiles: unmasked stores
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.C16) + row * p.ldc16 + cbase);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dst[j] = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
+        // online (max, sum-exp) in the log2 domain over the ROUNDED values, columns >= N masked
+        float y[32];
+        float cm = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float lo = unpack16_lo(h[j], p.is_bf16) * 1.4426950408889634f;
+          const float hi = unpack16_hi(h[j], p.is_bf16) * 1.4426950408889634f;
+          y[2 * j] = (cbase + 2 * j < p.N) ? lo : -INFINITY;
+          y[2 * j + 1] = (cbase + 2 * j + 1 < p.N) ? hi : -INFINITY;
+          cm = fmaxf(cm, fmaxf(y[2 * j], y[2 * j + 1]));
+        }
+        const float m_new = fmaxf(run_m, cm);
+        if (m_new != -INFINITY) {
+          float s = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) s += ex2_fast(y[j] - m_new);
+          run_s = run_s * ex2_fast(run_m - m_new) + s;
+          run_m = m_new;
+        }
+      } else {
+        if (row < p.M) {
+          uint16_t* dst = reinterpret_cast<uint16_t*>(p.C16) + row * p.ldc16 + cbase;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (cbase + 8 * j + 8 <= p.N)
+              *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
+        }
+      }
+    } else {
+      if (row < p.M) {
+        float* c32 = p.C32 + row * p.ldc32 + cbase;
+        if constexpr (EPI == EPI_STORE32) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (cbase + 4 * j + 4 <= p.N)
+              *reinterpret_cast<uint4*>(c32 + 4 * j) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        } else {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (cbase + 4 * j + 4 <= p.N) o = *reinterpret_cast<const float4*>(c32 + 4 * j);
+            v[4 * j] = o.x + __uint_as_float(r[4 * j]);
+            v[4 * j + 1] = o.y + __uint_as_float(r[4 * j + 1]);
+            v[4 * j + 2] = o.z + __uint_as_float(r[4 * j + 2]);
+            v[4 * j + 3] = o.w + __uint_as_float(r[4 * j + 3]);
+          }
+          if constexpr (EPI == EPI_ACCUM32) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (cbase + 4 * j + 4 <= p.N)
+                *reinterpret_cast<float4*>(c32 + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else {
+            uint16_t* dst = reinterpret_cast<uint16_t*>(p.C16) + row * p.ldc16 + cbase;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (cbase + 8 * j + 8 <= p.N)
+                *reinterpret_cast<uint4*>(dst + 8 * j) =
+                    make_uint4(pack16(v[8 * j], v[8 * j + 1], p.is_bf16), pack16(v[8 * j + 2], v[8 * j + 3], p.is_bf16),
+                               pack16(v[8 * j + 4], v[8 * j + 5], p.is_bf16), pack16(v[8 * j + 6], v[8 * j + 7], p.is_bf16));
+          }
+        }
+      }
+    }
+  }
+  if constexpr (EPI == EPI_LOGITS_STATS) {
+    if (row < p.M) p.stats[row * p.stats_ld + nt] = make_float2(run_m, run_s);
+  }
+}
+
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 tcgen05_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
@@ -259,90 +349,7 @@ tcgen05_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int64_t row = (int64_t)mt * BM + row_in_tile;
       const int col0 = nt * BN;
       const uint32_t taddr0 = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
-      float run_m = -INFINITY, run_s = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(taddr0 + c * 32, r);
-        tmem_ld_wait();
-        const int cbase = col0 + c * 32;
-        if constexpr (EPI == EPI_STORE16 || EPI == EPI_LOGITS_STATS) {
-          uint32_t h[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) h[j] = pack16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]), p.is_bf16);
-          if constexpr (EPI == EPI_LOGITS_STATS) {
-            // scratch is padded to whole tiles: unmasked stores
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.C16) + row * p.ldc16 + cbase);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) dst[j] = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
-            // online (max, sum-exp) in the log2 domain over the ROUNDED values, columns >= N masked
-            float y[32];
-            float cm = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float lo = unpack16_lo(h[j], p.is_bf16) * 1.4426950408889634f;
-              const float hi = unpack16_hi(h[j], p.is_bf16) * 1.4426950408889634f;
-              y[2 * j] = (cbase + 2 * j < p.N) ? lo : -INFINITY;
-              y[2 * j + 1] = (cbase + 2 * j + 1 < p.N) ? hi : -INFINITY;
-              cm = fmaxf(cm, fmaxf(y[2 * j], y[2 * j + 1]));
-            }
-            const float m_new = fmaxf(run_m, cm);
-            if (m_new != -INFINITY) {
-              float s = 0.f;
-#pragma unroll
-              for (int j = 0; j < 32; ++j) s += ex2_fast(y[j] - m_new);
-              run_s = run_s * ex2_fast(run_m - m_new) + s;
-              run_m = m_new;
-            }
-          } else {
-            if (row < p.M) {
-              uint16_t* dst = reinterpret_cast<uint16_t*>(p.C16) + row * p.ldc16 + cbase;
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                if (cbase + 8 * j + 8 <= p.N)
-                  *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
-            }
-          }
-        } else {
-          if (row < p.M) {
-            float* c32 = p.C32 + row * p.ldc32 + cbase;
-            if constexpr (EPI == EPI_STORE32) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                if (cbase + 4 * j + 4 <= p.N)
-                  *reinterpret_cast<uint4*>(c32 + 4 * j) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-            } else {
-              float v[32];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (cbase + 4 * j + 4 <= p.N) o = *reinterpret_cast<const float4*>(c32 + 4 * j);
-                v[4 * j] = o.x + __uint_as_float(r[4 * j]);
-                v[4 * j + 1] = o.y + __uint_as_float(r[4 * j + 1]);
-                v[4 * j + 2] = o.z + __uint_as_float(r[4 * j + 2]);
-                v[4 * j + 3] = o.w + __uint_as_float(r[4 * j + 3]);
-              }
-              if constexpr (EPI == EPI_ACCUM32) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  if (cbase + 4 * j + 4 <= p.N)
-                    *reinterpret_cast<float4*>(c32 + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-              } else {
-                uint16_t* dst = reinterpret_cast<uint16_t*>(p.C16) + row * p.ldc16 + cbase;
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                  if (cbase + 8 * j + 8 <= p.N)
-                    *reinterpret_cast<uint4*>(dst + 8 * j) =
-                        make_uint4(pack16(v[8 * j], v[8 * j + 1], p.is_bf16), pack16(v[8 * j + 2], v[8 * j + 3], p.is_bf16),
-                                   pack16(v[8 * j + 4], v[8 * j + 5], p.is_bf16), pack16(v[8 * j + 6], v[8 * j + 7], p.is_bf16));
-              }
-            }
-          }
-        }
-      }
-      if constexpr (EPI == EPI_LOGITS_STATS) {
-        if (row < p.M) p.stats[row * p.stats_ld + nt] = make_float2(run_m, run_s);
-      }
+      gemm_epilogue_tile<EPI>(p, taddr0, row, col0, nt);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));

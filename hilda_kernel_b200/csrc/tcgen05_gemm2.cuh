@@ -1,0 +1,245 @@
+// CTA-pair variant of the tcgen05 GEMM: two CTAs of a cluster (two SMs) work on one 256 x 256 tile
+// with `tcgen05.mma.cta_group::2`. Each CTA stages its own 128 rows of A and 128 of the 256 columns
+// of B (32 KB per stage instead of 48 KB, so 6 stages fit and the shared-memory operand traffic
+// per SM drops by a third); the leader CTA (cluster rank 0) issues the MMAs, which read both CTAs'
+// shared memory and write each CTA's half of the accumulator into that CTA's TMEM.
+//
+// Barriers (all mbarriers; every wait bounded):
+//   full[s]    in the leader only: 1 arrival (leader's expect_tx of both CTAs' bytes) + the bytes of
+//              both CTAs' TMA loads (the peer's loads signal the leader's barrier);
+//   empty[s]   in each CTA: released by the leader's commit, delivered to both CTAs of the pair;
+//   tfull[a]   in each CTA: accumulator a complete (same commit mechanism);
+//   tempty[a]  in the leader only: 8 arrivals = 4 epilogue warps of each CTA (the peer arrives remotely).
+// No TMA load here is a cluster broadcast: every CTA fetches its own operand tiles.
+#pragma once
+#include "tcgen05_gemm.cuh"
+
+namespace hilda {
+
+constexpr int G2_STAGES = 6;
+constexpr int G2_B_ROWS = BN / 2;                      // B columns staged per CTA
+constexpr int G2_A_BYTES = BM * BK * 2;                // 16 KB
+constexpr int G2_B_BYTES = G2_B_ROWS * BK * 2;         // 16 KB
+constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
+constexpr int G2_SMEM_BYTES = G2_STAGES * G2_STAGE_BYTES + 1024;
+
+__device__ __forceinline__ uint32_t g2_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t g2_map_rank(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void g2_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load whose completion bytes are credited to a barrier that may live in the peer CTA.
+__device__ __forceinline__ void g2_tma_load_2d(uint32_t dst, const CUtensorMap* tmap, uint32_t bar_cluster_addr, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(tmap), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void g2_mbar_arrive_remote(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void g2_tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void g2_tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void g2_tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void g2_umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrive (once all prior MMAs of this thread retired) on the barrier at this shared-memory offset in
+// BOTH CTAs of the pair.
+__device__ __forceinline__ void g2_umma_commit_pair(uint32_t bar) {
+  const uint16_t mask = 0x3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(mask) : "memory");
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+tcgen05_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[G2_STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[G2_STAGES];
+  __shared__ __align__(8) uint64_t tfull_bar[2];
+  __shared__ __align__(8) uint64_t tempty_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = g2_cta_rank();
+  const bool leader = (rank == 0);
+  const uint32_t stage_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  volatile int* abortp = &abort_flag;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < G2_STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull_bar[a]), 1); mbar_init(smem_u32(&tempty_bar[a]), 8); }
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    g2_tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
+    g2_tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  g2_cluster_sync();  // both CTAs' barriers are initialised and their TMEM allocated before any cross-CTA traffic
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  const int total_tiles = p.m_tiles * p.n_tiles;  // m_tiles counts 256-row tiles here
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+        const int mt = p.m_fast ? tile % p.m_tiles : tile / p.n_tiles;
+        const int nt = p.m_fast ? tile / p.m_tiles : tile % p.n_tiles;
+        const int m0 = mt * (2 * BM) + (int)rank * BM;        // this CTA's 128 rows of A
+        const int n0 = nt * BN + (int)rank * G2_B_ROWS;        // this CTA's 128 columns of B
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abortp, p.status, 21)) { ok = false; break; }
+          const uint32_t fb_local = smem_u32(&full_bar[stage]);
+          const uint32_t fb = g2_map_rank(fb_local, 0);  // the leader's barrier
+          const uint32_t sA = stage_base + stage * G2_STAGE_BYTES;
+          const uint32_t sB = sA + G2_A_BYTES;
+          if (leader) mbar_expect_tx(fb_local, 2 * G2_STAGE_BYTES);
+          if constexpr (!A_MN) {
+            g2_tma_load_2d(sA, &tmA, fb, kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) g2_tma_load_2d(sA + j * 8192, &tmA, fb, m0 + j * 64, kb * BK);
+          }
+          if constexpr (!B_MN) {
+            g2_tma_load_2d(sB, &tmB, fb, kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < G2_B_ROWS / 64; ++j) g2_tma_load_2d(sB + j * 8192, &tmB, fb, n0 + j * 64, kb * BK);
+          }
+          if (++stage == G2_STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && leader) {
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+        if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1u, abortp, p.status, 22)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abortp, p.status, 23)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = stage_base + stage * G2_STAGE_BYTES;
+          const uint32_t sB = sA + G2_A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t ad = A_MN ? make_smem_desc(sA + k * 2048, p.mn_lbo, p.mn_sbo) : make_smem_desc(sA + k * 32, 0, 1024);
+            const uint64_t bd = B_MN ? make_smem_desc(sB + k * 2048, p.mn_lbo, p.mn_sbo) : make_smem_desc(sB + k * 32, 0, 1024);
+            g2_umma_f16(d_tmem, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          g2_umma_commit_pair(smem_u32(&empty_bar[stage]));  // frees this stage in both CTAs
+          if (++stage == G2_STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        g2_umma_commit_pair(smem_u32(&tfull_bar[acc]));  // accumulator halves complete in both CTAs
+        acc ^= 1u;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int q = warp & 3;
+    const int row_in_tile = q * 32 + lane;
+    uint32_t acc = 0, acc_phase = 0;
+    for (int tile = pair; tile < total_tiles; tile += n_pairs) {
+      const int mt = p.m_fast ? tile % p.m_tiles : tile / p.n_tiles;
+      const int nt = p.m_fast ? tile / p.m_tiles : tile % p.n_tiles;
+      if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase, abortp, p.status, 24)) break;
+      tc_fence_after();
+      const int64_t row = (int64_t)mt * (2 * BM) + (int64_t)rank * BM + row_in_tile;
+      const uint32_t taddr0 = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+      gemm_epilogue_tile<EPI>(p, taddr0, row, nt * BN, nt);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) g2_mbar_arrive_remote(g2_map_rank(smem_u32(&tempty_bar[acc]), 0));
+      acc ^= 1u;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  __syncwarp();       // lanes of the producer / MMA warps rejoin before the warp-aligned cluster barrier
+  g2_cluster_sync();  // neither CTA frees TMEM or exits while its peer may still touch it
+  if (warp == 1) {
+    tc_fence_after();
+    g2_tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+static int launch_gemm2(const void* A, int64_t lda, const void* B, int64_t ldb, GemmParams p, cudaStream_t st) {
+  if (p.M <= 0 || p.N <= 0 || p.K <= 0) return HILDA_ERR_SIZE;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!A_MN) rc = make_tmap_2d(&tmA, A, p.is_bf16, (uint64_t)p.K, (uint64_t)p.M, (uint64_t)lda, BK, BM);
+  else rc = make_tmap_2d(&tmA, A, p.is_bf16, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)lda, 64, BK);
+  if (rc != HILDA_OK) return rc;
+  if (!B_MN) rc = make_tmap_2d(&tmB, B, p.is_bf16, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)ldb, BK, G2_B_ROWS);
+  else rc = make_tmap_2d(&tmB, B, p.is_bf16, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)ldb, 64, BK);
+  if (rc != HILDA_OK) return rc;
+  p.m_tiles = (p.M + 2 * BM - 1) / (2 * BM);
+  p.n_tiles = (p.N + BN - 1) / BN;
+  p.k_blocks = (p.K + BK - 1) / BK;
+  // instruction descriptor for the pair: M = 256
+  const uint32_t fmt = p.is_bf16 ? 1u : 0u;
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+            ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+  if (p.mn_lbo == 0) { p.mn_lbo = 8192; p.mn_sbo = 1024; }
+  auto kern = tcgen05_gemm2_kernel<A_MN, B_MN, EPI>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_BYTES) != cudaSuccess)
+    return HILDA_ERR_CUDA;
+  const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
+  if (tiles > 0x7fffffffLL) return HILDA_ERR_SIZE;
+  int pairs = sm_count() / 2;
+  if (tiles < pairs) pairs = (int)tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(pairs * 2), 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = G2_SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p);
+  return e == cudaSuccess ? HILDA_OK : HILDA_ERR_CUDA;
+}
+
+}  // namespace hilda

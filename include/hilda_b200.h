@@ -161,6 +161,11 @@ int hilda_flce_grad_weight(const void* dlogits, const void* hidden, float* dw32,
 void hilda_flce_profile(int enable);
 int hilda_flce_profile_collect(float* ms_per_kind, int* launches_per_kind);
 
+/* GEMM variant used by the FLCE entry points (no counterpart in the reference): 1 = CTA pairs
+ * (tcgen05 cta_group::2, 256 x 256 tiles over two SMs), 0 = one CTA per 128 x 256 tile. */
+void hilda_gemm_set_pair(int enable);
+int hilda_gemm_get_pair(void);
+
 /* Validation hook: plain C = A x B through the tcgen05 kernel with either operand K-major
  * ([M,K] / [N,K]) or MN-major (stored [K,M] / [K,N]). No counterpart in the reference. */
 int hilda_debug_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* c16, float* c32, int64_t ldc,

@@ -40,7 +40,7 @@ def test_size_queries_need_no_gpu(libpath):
     lib = _lib.lib()
     assert lib.hilda_flce_logits_pitch(128256) == 128256
     assert lib.hilda_flce_logits_pitch(16032) == 16128
-    assert lib.hilda_flce_padded_rows(100) == 128
+    assert lib.hilda_flce_padded_rows(100) == 256
     assert lib.hilda_flce_stat_tiles(128256) == 501
     assert lib.hilda_flce_default_chunk_rows(16384, 4096, 128256) == 4736  # 37 x 16 tiles = 4 waves of 148 SMs
     assert lib.hilda_flce_default_chunk_rows(100, 64, 1000) == 100

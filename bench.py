@@ -148,7 +148,7 @@ def run_reference(args):
             vals.append(v)
     value = statistics.mean(vals)
     sample = f"{rows_used} of {BT} rows x full V={V}, H={H}; bf16 hidden @ W.T + F.cross_entropy + autograd"
-    print(json.dumps({
+    EMIT(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * rows_used / value,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -282,7 +282,7 @@ def run_ours(args):
     pk = peaks()
     if args.only_op:
         if rank == 0:
-            print(json.dumps({"ops": per_op_table(device, pk, only=args.only_op, small=args.small)}))
+            EMIT(json.dumps({"ops": per_op_table(device, pk, only=args.only_op, small=args.small)}))
         return
 
     hidden, weight, targets = make_inputs(device)
@@ -405,13 +405,30 @@ def run_ours(args):
             result["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port",
                                       "sample": f"{rows} of {BT} rows x full V={V}, H={H}, {dt:.1f} s; PyTorch "
                                                 f"reference (bf16 matmul + F.cross_entropy + autograd) on host cores"}
-    print(json.dumps(result))
+    EMIT(json.dumps(result))
     if world > 1:
         dist.destroy_process_group()
 
 
+def _protect_stdout():
+    """Libraries (NCCL prints its version banner) may write to stdout; the contract is ONE JSON line
+    there. Point fd 1 at stderr for the run and return a writer bound to the real stdout."""
+    sys.stdout.flush()
+    real = os.dup(1)
+    os.dup2(2, 1)
+    out = os.fdopen(real, "w")
+
+    def emit(line):
+        out.write(line + "\n")
+        out.flush()
+    return emit
+
+
+EMIT = print
+
+
 def main():
-    global BT, V, H
+    global BT, V, H, EMIT
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
@@ -426,6 +443,7 @@ def main():
     ap.add_argument("--small", action="store_true", help="with --only-op: 1/8 of the rows (profiler captures)")
     args = ap.parse_args()
     BT, V, H = args.bt, args.vocab, args.hidden
+    EMIT = _protect_stdout()
     if args.impl == "reference":
         run_reference(args)
     else:

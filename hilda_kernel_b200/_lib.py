@@ -34,6 +34,8 @@ SIGNATURES = {
     "hilda_rope": (_i32, [_p, _p, _p, _i32, _p, _p, _p, _i32, _p, _p, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _p]),
     "hilda_swiglu_fwd": (_i32, [_p, _p, _p, _i64, _i32, _p]),
     "hilda_swiglu_bwd": (_i32, [_p, _p, _p, _p, _p, _i64, _i32, _p]),
+    "hilda_geglu_fwd": (_i32, [_p, _p, _p, _i64, _i32, _p]),
+    "hilda_geglu_bwd": (_i32, [_p, _p, _p, _p, _p, _i64, _i32, _p]),
     "hilda_cross_entropy_workspace_bytes": (_i64, [_i64]),
     "hilda_cross_entropy_fwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i32, _i32, _p]),
     "hilda_scale_rows": (_i32, [_p, _p, _p, _i32, _i64, _i64, _i32, _p]),

@@ -1,10 +1,11 @@
 """Operator modules named as in hilda-kernel's ``kernels`` package (kernels/__init__.py:1-12),
 restricted to the token-parallel operator path: RMSNorm, FusedAddRMSNorm, RoPE, SwiGLU,
-CrossEntropy, FusedLinearCrossEntropy and the GRPO loss."""
+CrossEntropy, FusedLinearCrossEntropy and the GRPO loss, plus GeGLU (same kernels as SwiGLU)."""
 from .rms_norm import HildaRMSNormFunction, hilda_rms_norm, RMSNorm
 from .rope import HildaRopeFunction, hilda_rope, RotaryEmbedding
 from .cross_entropy import HildaCrossEntropyFunction, hilda_cross_entropy, CrossEntropyLoss
 from .swiglu import HildaSwiGLUFunction, hilda_swiglu, SwiGLU
+from .geglu import HildaGeGLUFunction, hilda_geglu, GeGLU
 from .fused_add_rms_norm import HildaFusedAddRMSNormFunction, hilda_fused_add_rms_norm, FusedAddRMSNorm
 from .fused_linear_cross_entropy import (HildaFusedLinearCrossEntropyFunction, hilda_fused_linear_cross_entropy,
                                          FusedLinearCrossEntropyLoss)
@@ -15,6 +16,7 @@ __all__ = [
     "HildaRopeFunction", "hilda_rope", "RotaryEmbedding",
     "HildaCrossEntropyFunction", "hilda_cross_entropy", "CrossEntropyLoss",
     "HildaSwiGLUFunction", "hilda_swiglu", "SwiGLU",
+    "HildaGeGLUFunction", "hilda_geglu", "GeGLU",
     "HildaFusedAddRMSNormFunction", "hilda_fused_add_rms_norm", "FusedAddRMSNorm",
     "HildaFusedLinearCrossEntropyFunction", "hilda_fused_linear_cross_entropy", "FusedLinearCrossEntropyLoss",
     "HildaGRPOLossFunction", "hilda_grpo_loss", "GRPOLoss", "fused_selective_log_softmax",

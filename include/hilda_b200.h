@@ -91,6 +91,13 @@ int hilda_swiglu_fwd(const void* a, const void* b, void* c, int64_t n, int dtype
 int hilda_swiglu_bwd(const void* a, const void* b, const void* dc, void* da, void* db, int64_t n, int dtype,
                      void* stream);
 
+/* ---- GeGLU -------------------------------------------------------------------------------- */
+/* Replace geglu_forward / geglu_backward (kernels/geglu.py:131-159): c = gelu_tanh(a) * b; the
+ * backward may write da/db over a/b. */
+int hilda_geglu_fwd(const void* a, const void* b, void* c, int64_t n, int dtype, void* stream);
+int hilda_geglu_bwd(const void* a, const void* b, const void* dc, void* da, void* db, int64_t n, int dtype,
+                    void* stream);
+
 /* ---- CrossEntropy ------------------------------------------------------------------------- */
 int64_t hilda_cross_entropy_workspace_bytes(int64_t n_rows);
 /* Replaces cross_entropy_forward (kernels/cross_entropy.py:206-249). logits [n_rows, V] in dtype,

@@ -84,6 +84,12 @@ def swiglu(a, b):
     return F.silu(a) * b
 
 
+# --------------------------------------------------------------------------- GeGLU
+def geglu(a, b):
+    """benchmarks/bench_geglu.py:41-42 (``pytorch_geglu``)."""
+    return F.gelu(a, approximate="tanh") * b
+
+
 # --------------------------------------------------------------------------- CrossEntropy
 def cross_entropy(logits, targets, ignore_index=-100, reduction="mean"):
     """benchmarks/bench_cross_entropy.py:77-79, :101-104: ``F.cross_entropy`` with ignore_index.

@@ -6,7 +6,7 @@ Run once, in a container where the reference checkout is available:
 
 It imports the reference benchmark modules (``triton-kernels/benchmarks/bench_*.py``; importing them
 needs triton but no GPU) and calls the reference implementations they define
-(``pytorch_rms_norm``, ``pytorch_fused_add_rms_norm``, ``pytorch_rope``, ``pytorch_swiglu``,
+(``pytorch_rms_norm``, ``pytorch_fused_add_rms_norm``, ``pytorch_rope``, ``pytorch_swiglu``, ``pytorch_geglu``,
 ``pytorch_linear_ce``, ``pytorch_grpo_loss``) plus ``torch.nn.functional.cross_entropy`` exactly as
 ``bench_cross_entropy.py:77-79`` calls it, on small seeded CPU inputs, including their autograd
 gradients. Inputs and outputs are stored together so the tests need neither the reference nor
@@ -26,7 +26,7 @@ def _import_reference(root):
     sys.path.insert(0, tk)
     mods = {}
     with contextlib.redirect_stdout(io.StringIO()):
-        for name in ("bench_rms_norm", "bench_fused_add_rms_norm", "bench_rope", "bench_swiglu",
+        for name in ("bench_rms_norm", "bench_fused_add_rms_norm", "bench_rope", "bench_swiglu", "bench_geglu",
                      "bench_fused_linear_ce", "bench_grpo"):
             mods[name] = __import__(name)
     return mods
@@ -92,6 +92,17 @@ def main(root):
         c = m["bench_swiglu"].pytorch_swiglu(ar, br)
         c.backward(dc)
         out[f"swiglu_{tag}"] = dict(a=a, b=b, dc=dc, c=c.detach(), da=ar.grad, db=br.grad)
+
+    # ---- GeGLU
+    for tag, dtype in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        g = _g(7)
+        a = torch.randn(7, 200, generator=g).to(dtype)
+        b = torch.randn(7, 200, generator=g).to(dtype)
+        dc = torch.randn(7, 200, generator=g).to(dtype)
+        ar, br = a.clone().requires_grad_(True), b.clone().requires_grad_(True)
+        c = m["bench_geglu"].pytorch_geglu(ar, br)
+        c.backward(dc)
+        out[f"geglu_{tag}"] = dict(a=a, b=b, dc=dc, c=c.detach(), da=ar.grad, db=br.grad)
 
     # ---- CrossEntropy: F.cross_entropy(ignore_index=-100, reduction='mean') as bench_cross_entropy.py:77-79
     g = _g(4)

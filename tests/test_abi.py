@@ -77,7 +77,8 @@ def test_exported_names_match_reference_api():
     import hilda_kernel_b200 as hk
     for name in ["HildaRMSNormFunction", "hilda_rms_norm", "RMSNorm", "HildaRopeFunction", "hilda_rope",
                  "RotaryEmbedding", "HildaCrossEntropyFunction", "hilda_cross_entropy", "CrossEntropyLoss",
-                 "HildaSwiGLUFunction", "hilda_swiglu", "SwiGLU", "HildaFusedAddRMSNormFunction",
+                 "HildaSwiGLUFunction", "hilda_swiglu", "SwiGLU", "HildaGeGLUFunction", "hilda_geglu", "GeGLU",
+                 "HildaFusedAddRMSNormFunction",
                  "hilda_fused_add_rms_norm", "FusedAddRMSNorm", "HildaFusedLinearCrossEntropyFunction",
                  "hilda_fused_linear_cross_entropy", "FusedLinearCrossEntropyLoss", "HildaGRPOLossFunction",
                  "hilda_grpo_loss", "GRPOLoss", "fused_selective_log_softmax"]:

@@ -309,6 +309,31 @@ def test_swiglu_golden_and_inplace_backward(golden):
         assert_close(db, c["db"], dtype, what="db")
 
 
+# ------------------------------------------------------------------ GeGLU
+@pytest.mark.parametrize("shape", [(64, 11008), (33, 14336), (7, 200), (5, 33), (3, 4, 1000), (512, 4096)])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_geglu(shape, dtype, golden):
+    hk = ops()
+    g = gen(12)
+    a = torch.randn(*shape, generator=g).to(dtype)
+    b = torch.randn(*shape, generator=g).to(dtype)
+    dc = torch.randn(*shape, generator=g).to(dtype)
+    c_ref = R.geglu(a, b)
+    a32, b32 = a.float().clone().requires_grad_(True), b.float().clone().requires_grad_(True)
+    R.geglu(a32, b32).backward(dc.float())
+    ad, bd = a.to(DEV).requires_grad_(True), b.to(DEV).requires_grad_(True)
+    c = hk.hilda_geglu(ad, bd)
+    assert c.dtype == dtype
+    assert_close(c, c_ref, dtype, what="c")
+    c.backward(dc.to(DEV))
+    assert_close(ad.grad, a32.grad, dtype, what="da")
+    assert_close(bd.grad, b32.grad, dtype, what="db")
+    if shape == (7, 200) and dtype != torch.float16:
+        k = golden["geglu_f32" if dtype == torch.float32 else "geglu_bf16"]
+        out = hk.GeGLU()(k["a"].to(DEV), k["b"].to(DEV))
+        assert_close(out, k["c"], dtype, what="golden c")
+
+
 # ------------------------------------------------------------------ CrossEntropy
 def _ce_inputs(n, v, dtype, ignore_frac=0.1, seed=7):
     g = gen(seed)

@@ -39,8 +39,6 @@ __device__ __forceinline__ void load_w_vec(const void* W, int w_dt, int e0, floa
   }
 }
 
-// Persistent CTAs; the next row's loads are issued before the current row is reduced, so every SM
-// always has loads in flight (software prefetch in registers).
 template <typename T, int THREADS, int VPT>
 __global__ void __launch_bounds__(THREADS)
 norm_fwd_kernel(const T* __restrict__ X, const T* __restrict__ R, const void* __restrict__ W, int w_dt,
@@ -50,34 +48,24 @@ norm_fwd_kernel(const T* __restrict__ X, const T* __restrict__ R, const void* __
   const int n_vec = n_cols / VEC;
   __shared__ float red[33];
   const int tid = threadIdx.x;
-  const bool has_r = (R != nullptr);
 
-  uint4 xv[VPT], rv[VPT], xn[VPT], rn[VPT];
-  int64_t row = blockIdx.x;
-  if (row < n_rows) {
+  for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
+    const T* xr = X + row * n_cols;
+    uint4 xv[VPT];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = tid + i * THREADS;
-      const bool ok = v < n_vec;
-      xn[i] = ok ? ld16_stream(X + row * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
-      rn[i] = (ok && has_r) ? ld16_stream(R + row * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
+      xv[i] = (v < n_vec) ? ld16_stream(xr + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
     }
-  }
-  for (; row < n_rows; row += gridDim.x) {
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) { xv[i] = xn[i]; rv[i] = rn[i]; }
-    const int64_t nrow = row + gridDim.x;
-    if (nrow < n_rows) {
+    if (R != nullptr) {
+      const T* rr = R + row * n_cols;
+      T* sr = S + row * n_cols;
+      uint4 rv[VPT];
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int v = tid + i * THREADS;
-        const bool ok = v < n_vec;
-        xn[i] = ok ? ld16_stream(X + nrow * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
-        rn[i] = (ok && has_r) ? ld16_stream(R + nrow * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
+        rv[i] = (v < n_vec) ? ld16_stream(rr + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
       }
-    }
-    if (has_r) {
-      T* sr = S + row * n_cols;
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int v = tid + i * THREADS;
@@ -320,13 +308,7 @@ static int norm_fwd_t(const void* x, const void* r, const void* w, int w_dt, voi
     HILDA_LAUNCH_CHECK();
     return HILDA_OK;
   }
-  int per_sm = 4;
-#define FWD_OCC(TT, TH, VP) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, norm_fwd_kernel<TT, TH, VP>, TH, 0)
-  NORM_DISPATCH_TV(T, FWD_OCC)
-#undef FWD_OCC
-  if (per_sm < 1) per_sm = 1;
-  int64_t want = (int64_t)sm_count() * per_sm;
-  int grid = (int)(n_rows < want ? n_rows : want);
+  int grid = (int)(n_rows < max_grid ? n_rows : max_grid);
 #define FWD_CALL(TT, TH, VP)                                                                            \
   norm_fwd_kernel<TT, TH, VP><<<grid, TH, 0, st>>>((const TT*)x, (const TT*)r, w, w_dt, (TT*)y, (TT*)s, rstd, \
                                                     n_rows, (int)n_cols, eps)

@@ -164,27 +164,44 @@ def run_reference(args):
 def per_op_table(device, pk, only=None, small=False):
     """Device-timed GB/s of the six HBM-bound operators at their BASELINE configs (N = 1).
     `only` restricts to one operator; `small` divides the row counts by 8 (for profiler captures)."""
+    import hilda_kernel_b200._lib as L
     from hilda_kernel_b200.kernels import (cross_entropy as CE, fused_add_rms_norm as FA, grpo_loss as GR,
                                            rms_norm as RN, rope as RP, swiglu as SW)
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
     g = torch.Generator(device=device).manual_seed(1)
 
-    def timed(fn, reps=10, warm=3):
-        for _ in range(warm):
-            fn()
-        ts = []
-        for _ in range(reps):
-            flush.zero_()  # evict L2 between reps
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(); fn(); b.record()
-            torch.cuda.synchronize()
-            ts.append(a.elapsed_time(b))
-        return statistics.median(ts)
+    def timed(fns, iters=8):
+        """Device time per launch of the closures in `fns`. They work on DISTINCT buffer sets whose
+        combined footprint exceeds the 126 MB L2 several times, so every launch starts L2-cold
+        ("inputs larger than L2"). The launch sequence is captured once in a CUDA graph and replayed
+        between two events, which keeps host launch overhead (tens of microseconds per operator call,
+        comparable to the shorter kernels) out of the measurement."""
+        if not isinstance(fns, (list, tuple)):
+            fns = [fns]
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                for f in fns:
+                    f()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for f in fns:
+                f()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (iters * len(fns))
 
-    def timed2(fwd, bwd):
-        """forward and backward timed separately (each after its own L2 flush, so the host has time
-        to enqueue the launch while the flush runs) and summed: device time of the two passes."""
-        a, b = timed(fwd), timed(bwd)
+    def timed2(fwds, bwds):
+        """forward and backward timed separately and summed: device time of the two passes."""
+        a, b = timed(fwds), timed(bwds)
         return a + b, a, b
 
     out = {}
@@ -205,37 +222,61 @@ def per_op_table(device, pk, only=None, small=False):
     rn = lambda *s: torch.randn(*s, device=device, generator=g)
     # config 1: RMSNorm fp32 [4096, 4096] fwd+bwd (5 tensor passes)
     if want("rms_norm_fp32"):
-        x, w, dy = rn(4096, 4096), 1 + 0.1 * rn(4096), rn(4096, 4096)
-        _, xf, rstd = RN.rms_norm_forward(x, w)
-        add("rms_norm_fp32_fwd+bwd", timed2(lambda: RN.rms_norm_forward(x, w), lambda: RN.rms_norm_backward(dy, xf, w, rstd)),
-            5 * x.numel() * 4, 4096)
+        w = 1 + 0.1 * rn(4096)
+        sets = []
+        for _ in range(6):  # 6 x (x, y | dy, x, dx) = 6 x 201 MB per pass
+            x, dy = rn(4096, 4096), rn(4096, 4096)
+            _, xf, rstd = RN.rms_norm_forward(x, w)
+            sets.append((x, dy, xf, rstd))
+        add("rms_norm_fp32_fwd+bwd",
+            timed2([(lambda x=x: RN.rms_norm_forward(x, w)) for x, _, _, _ in sets],
+                   [(lambda dy=dy, xf=xf, rstd=rstd: RN.rms_norm_backward(dy, xf, w, rstd)) for _, dy, xf, rstd in sets]),
+            5 * 4096 * 4096 * 4, 4096)
+        del sets
     # config 2a: FusedAddRMSNorm bf16 [16384, 4096] fwd+bwd with dY and dS (8 passes)
     if want("fused_add_rms_norm"):
-        x, r, w = rn(16384, 4096).bfloat16(), rn(16384, 4096).bfloat16(), (1 + 0.1 * rn(4096)).bfloat16()
-        dy, ds = rn(16384, 4096).bfloat16(), rn(16384, 4096).bfloat16()
-        _, s, rstd = FA.fused_add_rms_norm_forward(x, r, w)
+        w = (1 + 0.1 * rn(4096)).bfloat16()
+        sets = []
+        for _ in range(3):  # 3 x 537 MB per pass
+            x, r = rn(16384, 4096).bfloat16(), rn(16384, 4096).bfloat16()
+            dy, ds = rn(16384, 4096).bfloat16(), rn(16384, 4096).bfloat16()
+            _, s, rstd = FA.fused_add_rms_norm_forward(x, r, w)
+            sets.append((x, r, dy, ds, s, rstd))
         add("fused_add_rms_norm_bf16_fwd+bwd",
-            timed2(lambda: FA.fused_add_rms_norm_forward(x, r, w),
-                   lambda: FA.fused_add_rms_norm_backward(dy, ds, s, w, rstd)),
-            8 * x.numel() * 2, 16384)
-        del x, r, dy, ds, s
+            timed2([(lambda x=x, r=r: FA.fused_add_rms_norm_forward(x, r, w)) for x, r, _, _, _, _ in sets],
+                   [(lambda dy=dy, ds=ds, s=s, rstd=rstd: FA.fused_add_rms_norm_backward(dy, ds, s, w, rstd))
+                    for _, _, dy, ds, s, rstd in sets]),
+            8 * 16384 * 4096 * 2, 16384)
+        del sets
     # config 2b: RoPE bf16 in place, q [4,4096,32,128] k [4,4096,8,128] in (B,S,H,D) memory, theta 5e5
     if want("rope"):
-        q = rn(4, 4096, 32, 128).bfloat16().transpose(1, 2)
-        k = rn(4, 4096, 8, 128).bfloat16().transpose(1, 2)
         inv = 1.0 / (500000.0 ** (torch.arange(0, 128, 2, device=device).float() / 128))
         fr = torch.outer(torch.arange(4096, device=device).float(), inv)
         cos, sin = fr.cos()[None].bfloat16(), fr.sin()[None].bfloat16()
+        sets = [(rn(4, 4096, 32, 128).bfloat16().transpose(1, 2), rn(4, 4096, 8, 128).bfloat16().transpose(1, 2))
+                for _ in range(4)]  # 4 x 168 MB, rotated in place
         add("rope_bf16_fwd+bwd",
-            timed2(lambda: RP.rope_forward(q, k, cos, sin, inplace=True), lambda: RP.rope_backward(q, k, cos, sin)),
-            4 * (q.numel() + k.numel()) * 2, 16384)
-        del q, k
+            timed2([(lambda q=q, k=k: RP.rope_forward(q, k, cos, sin, inplace=True)) for q, k in sets],
+                   [(lambda q=q, k=k: RP.rope_backward(q, k, cos, sin)) for q, k in sets]),
+            4 * (4 * 4096 * 40 * 128) * 2, 16384)
+        del sets
     # config 2c: SwiGLU bf16 [16384, 14336] fwd+bwd (3 + 5 passes)
     if want("swiglu"):
         nr = 16384 // div
         a, b, dc = rn(nr, 14336).bfloat16(), rn(nr, 14336).bfloat16(), rn(nr, 14336).bfloat16()
-        add("swiglu_bf16_fwd+bwd", timed2(lambda: SW.swiglu_forward(a, b), lambda: SW.swiglu_backward(a, b, dc)),
-            8 * a.numel() * 2, nr)
+        c_out = torch.empty_like(a)
+        da, db = torch.empty_like(a), torch.empty_like(a)
+        lib, st_ = L.lib(), L.stream(a.device)
+
+        def sw_fwd():  # the C ABI directly: outputs preallocated, so the timing is the kernel alone
+            L.check(lib.hilda_swiglu_fwd(a.data_ptr(), b.data_ptr(), c_out.data_ptr(), a.numel(), L.dt(a),
+                                         L.stream(a.device)), "swiglu_fwd")
+
+        def sw_bwd():
+            L.check(lib.hilda_swiglu_bwd(a.data_ptr(), b.data_ptr(), dc.data_ptr(), da.data_ptr(), db.data_ptr(),
+                                         a.numel(), L.dt(a), L.stream(a.device)), "swiglu_bwd")
+        add("swiglu_bf16_fwd+bwd", timed2(sw_fwd, sw_bwd), 8 * a.numel() * 2, nr)
+        del c_out, da, db
         del a, b, dc
     # config 3: CrossEntropy bf16 [8192, 128256], 10 % ignored: read valid rows once, write all grad rows
     if want("cross_entropy"):
@@ -260,7 +301,7 @@ def per_op_table(device, pk, only=None, small=False):
     old, ref = cur + 0.05 * rn(B, Lc), cur + 0.1 * rn(B, Lc)
     A = int(mask.sum())
     add("grpo_bf16_fwd+bwd", timed(lambda: GR.grpo_loss_forward(logits, ids, adv, old, ref, mask, 1.0, 0.1, 0.2, 0.2, True),
-                                   reps=5),
+                                   iters=4),
         (A + B * (Lc + 1)) * v * 2, B * Lc)
     out["grpo_bf16_fwd+bwd"]["active_tokens"] = A
     return out

@@ -46,9 +46,12 @@ struct CEOp {
     loss_rows[row] = 0.f;
     if (lse_rows) lse_rows[row] = 0.f;
   }
-  __device__ __forceinline__ RowCoef finish(int64_t row, float lse, float x_t, bool writer) const {
-    float scale = 1.0f;
-    if (mean) scale = 1.0f / fmaxf((float)(*n_valid), 1.0f);
+  struct Pre { float scale; };
+  __device__ __forceinline__ Pre prefetch(int64_t) const {
+    return Pre{mean ? 1.0f / fmaxf((float)(*n_valid), 1.0f) : 1.0f};
+  }
+  __device__ __forceinline__ RowCoef finish(int64_t row, float lse, float x_t, bool writer, const Pre& pre) const {
+    const float scale = pre.scale;
     if (writer) {
       loss_rows[row] = (lse - x_t) * (scale_loss ? scale : 1.0f);
       if (lse_rows) lse_rows[row] = lse;
@@ -116,7 +119,21 @@ struct GRPOOp {
     loss[i] = 0.f; clipped[i] = 0.f; lse_out[i] = 0.f;
     if (kl) kl[i] = 0.f;
   }
-  __device__ __forceinline__ RowCoef finish(int64_t row, float lse, float x_t, bool writer) const {
+  struct Pre { float old, ref, adv, gscale; int has_old; };
+  __device__ __forceinline__ Pre prefetch(int64_t row) const {
+    Pre p{0.f, 0.f, 0.f, 0.f, 0};
+    if (logp_only) return p;
+    const int64_t b = row / (L + 1), l = row - b * (L + 1);
+    const int64_t i = b * L + l;
+    if (old_logp) { p.old = old_logp[i]; p.has_old = 1; }
+    if (beta != 0.f) p.ref = ref_logp[i];
+    p.adv = advantages[b];
+    // upstream scale for a unit loss gradient: mask / (seq_len_b * B), then 1/T
+    const float mval = mask ? (float)mask[i] : 1.0f;
+    p.gscale = (mval / (seq_len[b] * (float)B)) * inv_t;
+    return p;
+  }
+  __device__ __forceinline__ RowCoef finish(int64_t row, float lse, float x_t, bool writer, const Pre& pre) const {
     const int64_t b = row / (L + 1), l = row - b * (L + 1);
     const int64_t i = b * L + l;
     const float logp = x_t - lse;
@@ -124,9 +141,9 @@ struct GRPOOp {
       if (writer) logp_out[i] = logp;
       return RowCoef{0.f, 0.f};
     }
-    const float old = old_logp ? old_logp[i] : logp;
+    const float old = pre.has_old ? pre.old : logp;
     const float coef1 = expf(logp - old);
-    const float adv = advantages[b];
+    const float adv = pre.adv;
     const float lo = 1.0f - eps_low, hi = 1.0f + eps_high;
     const float coef2 = fminf(fmaxf(coef1, lo), hi);
     const bool is_clipped = ((coef1 < lo) && (adv < 0.f)) || ((coef1 > hi) && (adv > 0.f));
@@ -135,7 +152,7 @@ struct GRPOOp {
     float dlogp = (l2 >= l1) ? -coef1 * adv : 0.f;
     float klv = 0.f;
     if (beta != 0.f) {
-      const float d = ref_logp[i] - logp;
+      const float d = pre.ref - logp;
       const float e = expf(d);
       klv = e - d - 1.0f;
       ptl += beta * klv;
@@ -146,9 +163,7 @@ struct GRPOOp {
       if (kl) kl[i] = klv;
       if (logp_out) logp_out[i] = logp;
     }
-    // upstream scale for a unit loss gradient: mask / (seq_len_b * B), then 1/T
-    const float mval = mask ? (float)mask[i] : 1.0f;
-    const float g = dlogp * (mval / (seq_len[b] * (float)B)) * inv_t;
+    const float g = dlogp * pre.gscale;
     return RowCoef{-g, g};
   }
 };

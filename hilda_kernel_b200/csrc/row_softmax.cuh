@@ -140,7 +140,7 @@ constexpr int ROW_THREADS_DEFAULT = 256;
 // Register-resident, cluster-per-row kernel. Requires V % VEC == 0 and 16-byte aligned rows.
 // CTAs per SM the register budget is held to (the row slice itself takes 4*NV registers).
 constexpr int row_min_blocks(int threads, int nv) {
-  return nv <= 8 ? (threads <= 256 ? 4 : (threads <= 320 ? 3 : 2)) : (nv <= 10 ? 3 : 2);
+  return nv <= 10 ? (threads <= 256 ? 4 : (threads <= 320 ? 3 : 2)) : 2;
 }
 
 template <typename T, int ROW_THREADS, int NV, int CLUSTER, class Op>
@@ -183,6 +183,8 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
   const float k = inv_t * LOG2E;  // logits -> log2 domain
   float x_t = 0.f;
   if (target >= 0 && target < V) x_t = VT<T>::load1(xr + target) * inv_t;
+  // the per-row scalars finish() needs are fetched now, under the row loads, not after the reduction
+  const typename Op::Pre pre = op.prefetch(row);
 
   // pass 1: max of the raw logits (k > 0, so the scale is applied once to the maximum)
   typename RowMath<T>::MaxAcc macc = RowMath<T>::max_init();
@@ -222,7 +224,7 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
   const float lse2 = M + log2f(S);
   const float lse = lse2 * LN2;  // natural-log logsumexp of logits/T
 
-  const RowCoef co = op.finish(row, lse, x_t, writer);
+  const RowCoef co = op.finish(row, lse, x_t, writer, pre);
   if (!gr) return;
 
   // softmax_j = e_j * 2^(m_cta - lse2)
@@ -275,7 +277,7 @@ row_softmax_generic_kernel(const T* __restrict__ logits, T* __restrict__ grad, i
   s = block_sum<512>(s, red);
   const float lse2 = m + log2f(s);
   const float lse = lse2 * LN2;
-  const RowCoef co = op.finish(row, lse, x_t, writer);
+  const RowCoef co = op.finish(row, lse, x_t, writer, op.prefetch(row));
   if (!gr) return;
   for (int64_t c = tid; c < V; c += 512) {
     float g = co.alpha * ex2_approx(fmaf(VT<T>::load1(xr + c), k, -lse2));
@@ -306,6 +308,7 @@ static inline RowPlan plan_row(int64_t V, int vec, bool aligned, int force_nv, i
   else if (n_vec <= per * 8 * 2) { p.nv = 8; p.cluster = 2; }
   else if (n_vec <= per * 8 * 4) { p.nv = 8; p.cluster = 4; }
   else if (n_vec <= per * 8 * 8) { p.nv = 8; p.cluster = 8; }
+  else if (n_vec <= per * 10 * 8) { p.nv = 10; p.cluster = 8; }
   else if (n_vec <= 320 * 8 * 8) { p.threads = 320; p.nv = 8; p.cluster = 8; }
   else if (n_vec <= 384 * 8 * 8) { p.threads = 384; p.nv = 8; p.cluster = 8; }
   else if (n_vec <= 512 * 8 * 8) { p.threads = 512; p.nv = 8; p.cluster = 8; }

@@ -138,7 +138,7 @@ norm_fwd_generic_kernel(const T* __restrict__ X, const T* __restrict__ R, const 
 }
 
 template <typename T, int THREADS, int VPT>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, (sizeof(T) == 2 && VPT <= 2) ? (1024 / THREADS) : 1)
 norm_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __restrict__ X,
                 const void* __restrict__ W, int w_dt, const float* __restrict__ RSTD,
                 T* __restrict__ dX, float* __restrict__ partial, int64_t n_rows, int n_cols) {

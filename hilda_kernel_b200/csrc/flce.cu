@@ -114,6 +114,18 @@ flce_dlogits_kernel(T* __restrict__ logits, int64_t pitch, const float* __restri
 
 static inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
 
+// dst[i, :] = src[idx[i], :] (gather) or dst[idx[i], :] = src[i, :] (scatter); rows of `vecs` 16-byte vectors.
+__global__ void __launch_bounds__(256)
+move_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, const int64_t* __restrict__ idx, int64_t n_idx,
+                 int64_t vecs, int scatter) {
+  for (int64_t i = blockIdx.x; i < n_idx; i += gridDim.x) {
+    const int64_t r = idx[i];
+    const uint4* s = src + (scatter ? i : r) * vecs;
+    uint4* d = dst + (scatter ? r : i) * vecs;
+    for (int64_t v = threadIdx.x; v < vecs; v += 256) d[v] = s[v];
+  }
+}
+
 // 1: GEMMs run as CTA pairs (256 x 256 tiles, cta_group::2); 0: one CTA per 128 x 256 tile.
 // HILDA_GEMM_PAIR in the environment presets it.
 static int g_gemm_pair = []() {
@@ -439,6 +451,34 @@ int hilda_flce_profile_collect(float* ms_per_kind, int* launches_per_kind) {
     ms_per_kind[g_prof_kind[i]] += ms;
     launches_per_kind[g_prof_kind[i]] += 1;
   }
+  return HILDA_OK;
+}
+
+// Row compaction helpers for skipping ignored tokens: gather dst[i] = src[idx[i]] and scatter
+// dst[idx[i]] = src[i] over rows of row_bytes (a multiple of 16) bytes; idx is int64 on the device.
+// The scatter first clears dst (n_dst_rows rows), so rows not named by idx come out as zeros.
+int hilda_gather_rows(const void* src, const int64_t* idx, void* dst, int64_t n_idx, int64_t row_bytes, void* stream) {
+  if (n_idx == 0) return HILDA_OK;
+  if (!src || !idx || !dst) return HILDA_ERR_NULL;
+  if (row_bytes <= 0 || row_bytes % 16 != 0 || !aligned16(src) || !aligned16(dst)) return HILDA_ERR_ALIGN;
+  int64_t grid = n_idx < (int64_t)sm_count() * 16 ? n_idx : (int64_t)sm_count() * 16;
+  move_rows_kernel<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>((const uint4*)src, (uint4*)dst, idx, n_idx,
+                                                                     row_bytes / 16, 0);
+  HILDA_LAUNCH_CHECK();
+  return HILDA_OK;
+}
+int hilda_scatter_rows(const void* src, const int64_t* idx, void* dst, int64_t n_idx, int64_t n_dst_rows,
+                       int64_t row_bytes, void* stream) {
+  if (!dst) return HILDA_ERR_NULL;
+  if (row_bytes <= 0 || row_bytes % 16 != 0 || !aligned16(dst)) return HILDA_ERR_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (n_dst_rows > 0 && cudaMemsetAsync(dst, 0, (size_t)(n_dst_rows * row_bytes), st) != cudaSuccess) return HILDA_ERR_CUDA;
+  if (n_idx == 0) return HILDA_OK;
+  if (!src || !idx) return HILDA_ERR_NULL;
+  if (!aligned16(src)) return HILDA_ERR_ALIGN;
+  int64_t grid = n_idx < (int64_t)sm_count() * 16 ? n_idx : (int64_t)sm_count() * 16;
+  move_rows_kernel<<<(unsigned)grid, 256, 0, st>>>((const uint4*)src, (uint4*)dst, idx, n_idx, row_bytes / 16, 1);
+  HILDA_LAUNCH_CHECK();
   return HILDA_OK;
 }
 

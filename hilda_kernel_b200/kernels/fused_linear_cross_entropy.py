@@ -19,11 +19,44 @@ _RED = {"none": 0, "mean": 1, "sum": 2}
 CHUNK_ROWS = None
 # Set True to synchronise after each call and raise if a device-side bounded wait ran out.
 CHECK_STATUS = False
+# Ignored tokens contribute nothing to the loss or to either gradient, so by default their rows are
+# compacted away before the three GEMMs run (their d(hidden) rows come back as zeros). Building
+# the row list costs one host synchronisation, the same one the reference pays for n_valid
+# (fused_linear_cross_entropy.py:121). Set False to keep the call free of host synchronisation.
+SKIP_IGNORED_ROWS = True
+
+
+def _move_rows(fn_name, src, idx, dst, *extra):
+    with device_guard(src.device):
+        rc = getattr(L.lib(), fn_name)(L.ptr(src), L.ptr(idx), L.ptr(dst), idx.numel(), *extra, L.stream(src.device))
+    L.check(rc, fn_name)
 
 
 def fused_linear_cross_entropy_forward(hidden_states, weight, targets, ignore_index=-100, reduction='mean',
-                                       compute_grad=True, chunk_rows=None):
-    """Returns (loss, grad_input, grad_weight, n_valid); n_valid is a device scalar (no host sync)."""
+                                       compute_grad=True, chunk_rows=None, skip_ignored=None):
+    """Returns (loss, grad_input, grad_weight, n_valid); n_valid is a device scalar."""
+    if skip_ignored is None:
+        skip_ignored = SKIP_IGNORED_ROWS
+    if skip_ignored and hidden_states.is_cuda and hidden_states.dim() == 2 and targets.dim() == 1:
+        keep = (targets != ignore_index).nonzero().squeeze(1)  # the one host sync (size of the result)
+        BT = targets.shape[0]
+        if 0 < keep.numel() < BT:
+            H = hidden_states.shape[1]
+            hs = hidden_states.contiguous()
+            h_c = torch.empty(keep.numel(), H, dtype=hs.dtype, device=hs.device)
+            _move_rows("hilda_gather_rows", hs, keep, h_c, H * hs.element_size())
+            t_c = targets.contiguous()[keep]
+            loss, dh_c, dw, n_valid = fused_linear_cross_entropy_forward(
+                h_c, weight, t_c, ignore_index, reduction, compute_grad, chunk_rows, skip_ignored=False)
+            dh = None
+            if compute_grad:
+                dh = torch.empty_like(hs)
+                _move_rows("hilda_scatter_rows", dh_c, keep, dh, BT, H * hs.element_size())
+            if reduction == 'none':
+                full = torch.zeros(BT, dtype=loss.dtype, device=loss.device)
+                full[keep] = loss
+                loss = full
+            return loss, dh, dw, n_valid
     if reduction not in _RED:
         raise ValueError(f"reduction must be one of {list(_RED)}, got {reduction!r}")
     dev = L.require_cuda(hidden_states, weight, targets)

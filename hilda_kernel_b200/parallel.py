@@ -118,7 +118,30 @@ class VocabParallelFLCE:
         self.last_status = None
 
     def __call__(self, hidden, weight_shard, targets, vocab_start, ignore_index=-100, reduction='mean',
-                 compute_grad=True, chunk_rows=None):
+                 compute_grad=True, chunk_rows=None, skip_ignored=None):
+        from .kernels import fused_linear_cross_entropy as FL
+        if skip_ignored is None:
+            skip_ignored = FL.SKIP_IGNORED_ROWS
+        if skip_ignored:
+            # hidden and targets are replicated, so every rank drops the same ignored rows
+            keep = (targets != ignore_index).nonzero().squeeze(1)
+            BT = targets.shape[0]
+            if 0 < keep.numel() < BT:
+                hs = hidden.contiguous()
+                H = hs.shape[1]
+                h_c = torch.empty(keep.numel(), H, dtype=hs.dtype, device=hs.device)
+                FL._move_rows("hilda_gather_rows", hs, keep, h_c, H * hs.element_size())
+                loss, dh_c, dw = self(h_c, weight_shard, targets.contiguous()[keep], vocab_start, ignore_index,
+                                      reduction, compute_grad, chunk_rows, skip_ignored=False)
+                dh = None
+                if compute_grad:
+                    dh = torch.empty_like(hs)
+                    FL._move_rows("hilda_scatter_rows", dh_c, keep, dh, BT, H * hs.element_size())
+                if reduction == 'none':
+                    full = torch.zeros(BT, dtype=loss.dtype, device=loss.device)
+                    full[keep] = loss
+                    loss = full
+                return loss, dh, dw
         dev = L.require_cuda(hidden, weight_shard, targets)
         world, rank = _world(self.group)
         BT, H = hidden.shape

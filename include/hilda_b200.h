@@ -168,6 +168,13 @@ int hilda_flce_grad_weight(const void* dlogits, const void* hidden, float* dw32,
 void hilda_flce_profile(int enable);
 int hilda_flce_profile_collect(float* ms_per_kind, int* launches_per_kind);
 
+/* Row compaction for skipping ignored tokens (no counterpart in the reference, which runs its
+ * GEMMs over ignored rows too): dst[i,:] = src[idx[i],:] and dst[idx[i],:] = src[i,:] over rows of
+ * row_bytes (multiple of 16) bytes; the scatter zero-fills the n_dst_rows rows of dst first. */
+int hilda_gather_rows(const void* src, const int64_t* idx, void* dst, int64_t n_idx, int64_t row_bytes, void* stream);
+int hilda_scatter_rows(const void* src, const int64_t* idx, void* dst, int64_t n_idx, int64_t n_dst_rows,
+                       int64_t row_bytes, void* stream);
+
 /* GEMM variant used by the FLCE entry points (no counterpart in the reference): 1 = CTA pairs
  * (tcgen05 cta_group::2, 256 x 256 tiles over two SMs), 0 = one CTA per 128 x 256 tile. */
 void hilda_gemm_set_pair(int enable);

@@ -147,6 +147,23 @@ def test_flce_cta_pair_mode_matches_single_cta():
     assert_close(dw1, dw0.float(), torch.bfloat16, what="d weight", normalize=True)
 
 
+def test_flce_skip_ignored_rows_matches_full_path():
+    """Compacting ignored tokens away before the GEMMs changes nothing but the time."""
+    from hilda_kernel_b200.kernels.fused_linear_cross_entropy import fused_linear_cross_entropy_forward
+    for frac in (0.0, 0.3, 1.0):
+        hidden, weight, targets = _flce_inputs(600, 256, 2000, torch.bfloat16, ignore_frac=frac)
+        hd, wd, td = hidden.to(DEV), weight.to(DEV), targets.to(DEV)
+        for red in ("mean", "sum", "none"):
+            l0, dh0, dw0, n0 = fused_linear_cross_entropy_forward(hd, wd, td, reduction=red, skip_ignored=False)
+            l1, dh1, dw1, n1 = fused_linear_cross_entropy_forward(hd, wd, td, reduction=red, skip_ignored=True)
+            assert int(n0) == int(n1) == int((targets != -100).sum())
+            torch.testing.assert_close(l1, l0, rtol=1e-5, atol=1e-6)
+            assert_close(dh1, dh0.float(), torch.bfloat16, what="d hidden", normalize=frac < 1.0)
+            assert_close(dw1, dw0.float(), torch.bfloat16, what="d weight", normalize=frac < 1.0)
+            if frac > 0:
+                assert float(dh1[(targets == -100).to(DEV)].abs().max()) == 0.0
+
+
 def test_flce_golden_and_upstream_scale(golden):
     import hilda_kernel_b200 as hk
     c = golden["linear_ce_f32"]  # fp32 reference output; inputs rounded to bf16 for the tensor-core path

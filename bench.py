@@ -307,6 +307,75 @@ def per_op_table(device, pk, only=None, small=False):
     return out
 
 
+def sharded_ops_table(device, world, pk):
+    """Row-sharded operators at N > 1 (every rank calls this): each rank runs the ordinary operator on
+    its 1/N of the BASELINE rows, plus the one small exchange the operator needs (parallel.py). Device
+    time, max over ranks; GB/s is the whole job's algorithmic bytes over that time (weak in rows per
+    second, the batch is fixed so per-rank work shrinks with N)."""
+    import torch.distributed as dist
+    from hilda_kernel_b200 import parallel as P
+    from hilda_kernel_b200.kernels import fused_add_rms_norm as FA
+    g = torch.Generator(device=device).manual_seed(100 + dist.get_rank())
+    rn = lambda *s: torch.randn(*s, device=device, generator=g)
+    out = {}
+
+    def timed(fn, iters=5):
+        for _ in range(2):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def add(name, ms, total_bytes):
+        gbs = total_bytes / ms / 1e6
+        out[name] = {"us": round(ms * 1e3, 1), "GB/s_whole_job": round(gbs), "GB/s_per_gpu": round(gbs / world),
+                     "frac_of_measured_hbm_per_gpu": round(gbs / world / pk["hbm"], 3)}
+
+    # CrossEntropy, rows sharded: [8192 / N, 128256] per rank; exchange = (sum loss, n_valid)
+    n, v = 8192 // world, 128256
+    logits = (2 * rn(n, v)).bfloat16()
+    t = torch.randint(0, v, (n,), device=device, generator=g)
+    t[torch.randperm(n, device=device, generator=g)[: n // 10]] = -100
+    nv = torch.tensor([float((t != -100).sum())], device=device)
+    dist.all_reduce(nv)
+    add("cross_entropy_bf16_rows_sharded", timed(lambda: P.sharded_cross_entropy(logits, t)),
+        (float(nv[0]) + n * world) * v * 2)
+    del logits
+    # GRPO, sequences sharded: [16 / N, 1024, 151936] per rank; exchange = 4 floats
+    B, Lc, v = max(16 // world, 1), 1023, 151936
+    logits = (2 * rn(B, Lc + 1, v)).bfloat16()
+    ids = torch.randint(0, v, (B, Lc), device=device, generator=g)
+    lens = torch.randint(256, 1025, (B,), device=device, generator=g).clamp(max=Lc)
+    mask = (torch.arange(Lc, device=device)[None] < lens[:, None]).int()
+    old = rn(B, Lc) * 0.05 - 12
+    A = torch.tensor([float(mask.sum())], device=device)
+    dist.all_reduce(A)
+    add("grpo_bf16_sequences_sharded",
+        timed(lambda: P.sharded_grpo_loss(logits, ids, rn(B), old, old + 0.1, mask, 1.0, 0.1, 0.2, 0.2), iters=3),
+        (float(A[0]) + B * world * (Lc + 1)) * v * 2)
+    del logits
+    # FusedAddRMSNorm backward, rows sharded, dW all-reduced
+    rows = 16384 // world
+    x, r, w = rn(rows, 4096).bfloat16(), rn(rows, 4096).bfloat16(), (1 + 0.1 * rn(4096)).bfloat16()
+    dy, ds = rn(rows, 4096).bfloat16(), rn(rows, 4096).bfloat16()
+    _, s_, rstd = FA.fused_add_rms_norm_forward(x, r, w)
+
+    def fa_step():
+        FA.fused_add_rms_norm_forward(x, r, w)
+        _, _, dw = FA.fused_add_rms_norm_backward(dy, ds, s_, w, rstd)
+        return P.allreduce_weight_grad(dw)
+    add("fused_add_rms_norm_bf16_rows_sharded_fwd+bwd", timed(fa_step), 8 * 16384 * 4096 * 2)
+    return out
+
+
 def run_ours(args):
     world, rank, local = dist_env()
     if not torch.cuda.is_available():
@@ -399,6 +468,15 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_value = BT / float(t[0]) * 1e3
 
+    sharded = None
+    if world > 1 and not args.no_ops:
+        del h_host, h_dev
+        torch.cuda.empty_cache()
+        try:
+            sharded = sharded_ops_table(device, world, pk)
+        except Exception as e:  # the headline line must still print
+            sharded = {"error": repr(e)}
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -435,11 +513,13 @@ def run_ours(args):
                      "per_kind_ms_per_step": {"logits": ms_kind[0] / args.steps, "d_hidden": ms_kind[1] / args.steps,
                                               "d_weight": ms_kind[2] / args.steps},
                      "traffic": None},
-        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h_host.numel() * 2 + t_host.numel() * 8,
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": BT * H * 2 + BT * 8,
                 "d2h_bytes_per_step": 4, "steps": e2e_steps},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }
+    if sharded is not None:
+        result["ops_row_sharded"] = sharded
     if world == 1:
         del h_host, h_dev
         if not args.no_ops:

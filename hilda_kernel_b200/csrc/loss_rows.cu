@@ -96,6 +96,7 @@ struct GRPOOp {
   const float* seq_len;      // [B] clamp(sum(mask), 1)
   float* loss; float* kl; float* clipped; float* lse_out; float* logp_out;  // [B, L] each; kl/logp_out optional
   int64_t B, L;
+  float b_norm;              // sequences the loss is averaged over (all shards' when row-sharded)
   float inv_t, beta, eps_low, eps_high;
   int logp_only;             // selective log-softmax: write logp_out only
 
@@ -130,7 +131,7 @@ struct GRPOOp {
     p.adv = advantages[b];
     // upstream scale for a unit loss gradient: mask / (seq_len_b * B), then 1/T
     const float mval = mask ? (float)mask[i] : 1.0f;
-    p.gscale = (mval / (seq_len[b] * (float)B)) * inv_t;
+    p.gscale = (mval / (seq_len[b] * b_norm)) * inv_t;
     return p;
   }
   __device__ __forceinline__ RowCoef finish(int64_t row, float lse, float x_t, bool writer, const Pre& pre) const {
@@ -180,12 +181,12 @@ grpo_seq_len_kernel(const int32_t* __restrict__ mask, int64_t L, float* __restri
   if (threadIdx.x == 0) seq_len[b] = fmaxf(acc, 1.0f);
 }
 
-// out[0] = mean_b( sum_l loss*mask / seq_len_b ); out[1] = sum(kl*mask)/max(sum mask,1);
+// out[0] = sum_b( sum_l loss*mask / seq_len_b ) / b_norm; out[3] = sum mask; out[1] = sum(kl*mask)/max(sum mask,1);
 // out[2] = sum(clipped*mask)/max(sum mask,1). One CTA, one warp per sequence at a time.
 __global__ void __launch_bounds__(1024)
 grpo_reduce_kernel(const float* __restrict__ loss, const float* __restrict__ kl, const float* __restrict__ clipped,
                    const int32_t* __restrict__ mask, const float* __restrict__ seq_len, int64_t B, int64_t L,
-                   float* __restrict__ out) {
+                   float b_norm, float* __restrict__ out) {
   __shared__ float red[4][33];
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   float a_loss = 0.f, a_kl = 0.f, a_clip = 0.f, a_mask = 0.f;
@@ -206,7 +207,7 @@ grpo_reduce_kernel(const float* __restrict__ loss, const float* __restrict__ kl,
     float v0 = warp_sum(red[0][lane]), v1 = warp_sum(red[1][lane]), v2 = warp_sum(red[2][lane]), v3 = warp_sum(red[3][lane]);
     if (lane == 0) {
       const float msum = fmaxf(v3, 1.0f);
-      out[0] = v0 / (float)B; out[1] = v1 / msum; out[2] = v2 / msum;
+      out[0] = v0 / b_norm; out[1] = v1 / msum; out[2] = v2 / msum; out[3] = v3;
     }
   }
 }
@@ -240,8 +241,8 @@ int64_t hilda_cross_entropy_workspace_bytes(int64_t n_rows) { return 16 + (n_row
 // reduction: 0 none, 1 mean, 2 sum. grad may be null (inference path: loss only).
 // loss_out: scalar for mean/sum; unused for none (per-row loss is in loss_rows).
 int hilda_cross_entropy_fwd(const void* logits, const int64_t* targets, void* grad, float* loss_rows, float* lse_rows,
-                            float* loss_out, void* workspace, int64_t n_rows, int64_t V, int64_t ignore_index,
-                            int reduction, int dtype, void* stream) {
+                            float* loss_out, void* workspace, const int* n_valid_in, int64_t n_rows, int64_t V,
+                            int64_t ignore_index, int reduction, int dtype, void* stream) {
   if (!logits || !targets || !workspace) return HILDA_ERR_NULL;
   if (n_rows < 0 || V <= 0) return HILDA_ERR_SIZE;
   if (reduction < 0 || reduction > 2) return HILDA_ERR_ARG;
@@ -253,8 +254,10 @@ int hilda_cross_entropy_fwd(const void* logits, const int64_t* targets, void* gr
   float* rows = loss_rows ? loss_rows : reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 16);
   count_valid_kernel<<<1, 1024, 0, st>>>(targets, n_rows, ignore_index, n_valid);
   HILDA_LAUNCH_CHECK();
+  // row-sharded callers pass the count of valid rows over ALL shards, so that 'mean' is the global mean
+  const int* nv = n_valid_in ? n_valid_in : n_valid;
   CEOp op;
-  op.targets = targets; op.ignore_index = ignore_index; op.n_valid = n_valid;
+  op.targets = targets; op.ignore_index = ignore_index; op.n_valid = nv;
   // training path: loss rows and grad pre-scaled by 1/n_valid; inference path: divide afterwards
   op.mean = (reduction == 1) ? 1 : 0;
   op.scale_loss = (grad != nullptr) ? 1 : 0;
@@ -269,7 +272,7 @@ int hilda_cross_entropy_fwd(const void* logits, const int64_t* targets, void* gr
   if (rc != HILDA_OK) return rc;
   if (reduction != 0) {
     const int divide = (reduction == 1 && grad == nullptr) ? 1 : 0;
-    sum_rows_kernel<<<1, 1024, 0, st>>>(rows, n_rows, n_valid, divide, loss_out);
+    sum_rows_kernel<<<1, 1024, 0, st>>>(rows, n_rows, nv, divide, loss_out);
     HILDA_LAUNCH_CHECK();
   }
   return HILDA_OK;
@@ -293,13 +296,15 @@ int64_t hilda_grpo_workspace_bytes(int64_t B) { return 16 + (B > 0 ? B : 0) * 4;
 
 // logits [B, L+1, V] contiguous; ids [B, L] int64; mask [B, L] int32 or null; advantages [B] fp32;
 // old_logp / ref_logp [B, L] fp32 or null. Per-token outputs loss/kl/clipped/lse [B, L] fp32
-// (kl may be null when beta == 0). scalars_out[3] = {loss, kl_mean, clip_ratio}.
+// (kl may be null when beta == 0). scalars_out[4] = {loss, kl_mean, clip_ratio, sum(mask)}. B_total > 0: the
+// loss and the gradient are normalised by B_total sequences instead of B (sequences sharded over ranks).
 // grad: [B, L+1, V] in the logits dtype (gradient for a unit upstream loss gradient) or null.
 // workspace: hilda_grpo_workspace_bytes(B); seq_len[b] lives at byte 16.
 int hilda_grpo_loss_fwd(const void* logits, const int64_t* ids, const float* advantages, const float* old_logp,
                         const float* ref_logp, const int32_t* mask, void* grad, float* loss, float* kl, float* clipped,
                         float* lse, float* scalars_out, void* workspace, int64_t B, int64_t L, int64_t V,
-                        float temperature, float beta, float eps_low, float eps_high, int dtype, void* stream) {
+                        int64_t B_total, float temperature, float beta, float eps_low, float eps_high, int dtype,
+                        void* stream) {
   if (!logits || !ids || !advantages || !loss || !clipped || !lse || !scalars_out || !workspace) return HILDA_ERR_NULL;
   if (beta != 0.f && (!ref_logp || !kl)) return HILDA_ERR_NULL;
   if (B < 0 || L < 0 || V <= 0 || !(temperature > 0.f)) return HILDA_ERR_SIZE;
@@ -314,7 +319,7 @@ int hilda_grpo_loss_fwd(const void* logits, const int64_t* ids, const float* adv
   GRPOOp op;
   op.ids = ids; op.mask = mask; op.advantages = advantages; op.old_logp = old_logp; op.ref_logp = ref_logp;
   op.seq_len = seq_len; op.loss = loss; op.kl = (beta != 0.f) ? kl : nullptr; op.clipped = clipped; op.lse_out = lse;
-  op.logp_out = nullptr; op.B = B; op.L = L; op.inv_t = 1.0f / temperature; op.beta = beta; op.eps_low = eps_low;
+  op.logp_out = nullptr; op.B = B; op.L = L; op.b_norm = (float)(B_total > 0 ? B_total : B); op.inv_t = 1.0f / temperature; op.beta = beta; op.eps_low = eps_low;
   op.eps_high = eps_high; op.logp_only = 0;
   const int64_t n_rows = B * (L + 1);
   int rc;
@@ -325,7 +330,7 @@ int hilda_grpo_loss_fwd(const void* logits, const int64_t* ids, const float* adv
     default: return HILDA_ERR_DTYPE;
   }
   if (rc != HILDA_OK) return rc;
-  grpo_reduce_kernel<<<1, 1024, 0, st>>>(loss, op.kl, clipped, mask, seq_len, B, L, scalars_out);
+  grpo_reduce_kernel<<<1, 1024, 0, st>>>(loss, op.kl, clipped, mask, seq_len, B, L, op.b_norm, scalars_out);
   HILDA_LAUNCH_CHECK();
   return HILDA_OK;
 }

@@ -18,8 +18,11 @@ def _is_unit_scalar(x):
     return x.ndim == 0 and x.dtype == torch.float32 and bool(x == 1.0)
 
 
-def cross_entropy_forward(logits, targets, ignore_index=-100, reduction='mean', needs_grad=False):
-    """Returns (loss, aux, n_valid): aux is the saved dlogits on the training path, lse otherwise."""
+def cross_entropy_forward(logits, targets, ignore_index=-100, reduction='mean', needs_grad=False,
+                          n_valid_global=None):
+    """Returns (loss, aux, n_valid): aux is the saved dlogits on the training path, lse otherwise.
+    n_valid_global (int32 device scalar, optional): divide 'mean' by this count instead of the
+    number of valid rows in this call (row-sharded use)."""
     if reduction not in _RED:
         raise ValueError(f"reduction must be one of {list(_RED)}, got {reduction!r}")
     dev = L.require_cuda(logits, targets)
@@ -40,7 +43,7 @@ def cross_entropy_forward(logits, targets, ignore_index=-100, reduction='mean', 
         lib = L.lib()
         ws = torch.empty(lib.hilda_cross_entropy_workspace_bytes(0) // 4, dtype=torch.int32, device=dev)
         rc = lib.hilda_cross_entropy_fwd(L.ptr(logits), L.ptr(targets), L.ptr(grad), L.ptr(per_token_loss), L.ptr(lse),
-                                         L.ptr(loss_out), L.ptr(ws), n_rows, n_cols, int(ignore_index),
+                                         L.ptr(loss_out), L.ptr(ws), L.ptr(n_valid_global), n_rows, n_cols, int(ignore_index),
                                          _RED[reduction], L.dt(logits), L.stream(dev))
     L.check(rc, "cross_entropy_fwd")
     n_valid = ws[0]

@@ -41,8 +41,9 @@ def fused_selective_log_softmax(logits, input_ids, temperature=1.0, mask=None):
 
 
 def grpo_loss_forward(logits, completion_ids, advantages, old_logp=None, ref_logp=None, completion_mask=None,
-                      temperature=1.0, beta=0.0, eps_low=0.2, eps_high=0.2, needs_grad=False):
-    """Returns (loss, kl_mean | None, clip_ratio, lse, mask, dlogits | None)."""
+                      temperature=1.0, beta=0.0, eps_low=0.2, eps_high=0.2, needs_grad=False, batch_total=None):
+    """Returns (loss, kl_mean | None, clip_ratio, lse, mask, dlogits | None). batch_total: number of
+    sequences the loss is averaged over when this call sees only a shard of them."""
     assert logits.is_contiguous()
     dev = L.require_cuda(logits, completion_ids, advantages, old_logp, ref_logp, completion_mask)
     B, L_plus_1, N = logits.shape
@@ -63,14 +64,15 @@ def grpo_loss_forward(logits, completion_ids, advantages, old_logp=None, ref_log
     lse = torch.empty_like(loss)
     is_clipped = torch.empty_like(loss)
     kl = torch.empty_like(loss) if beta != 0.0 else None
-    scalars = torch.empty(3, device=dev, dtype=torch.float32)
+    scalars = torch.empty(4, device=dev, dtype=torch.float32)
     dlogits = torch.empty_like(logits) if needs_grad else None
     with device_guard(dev):
         lib = L.lib()
         ws = torch.empty(lib.hilda_grpo_workspace_bytes(B) // 4 + 1, dtype=torch.float32, device=dev)
         rc = lib.hilda_grpo_loss_fwd(L.ptr(logits), L.ptr(ids), L.ptr(adv), L.ptr(old), L.ptr(ref), L.ptr(mask_i),
                                      L.ptr(dlogits), L.ptr(loss), L.ptr(kl), L.ptr(is_clipped), L.ptr(lse),
-                                     L.ptr(scalars), L.ptr(ws), B, Lc, N, float(temperature), float(beta),
+                                     L.ptr(scalars), L.ptr(ws), B, Lc, N, int(batch_total or 0), float(temperature),
+                                     float(beta),
                                      float(eps_low), float(eps_high), L.dt(logits), L.stream(dev))
     L.check(rc, "grpo_loss_fwd")
     kl_mean = scalars[1] if beta != 0.0 else None

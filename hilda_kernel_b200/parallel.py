@@ -63,32 +63,34 @@ def allreduce_weight_grad(dW: torch.Tensor, group=None) -> torch.Tensor:
 
 
 def sharded_cross_entropy(logits_local, targets_local, ignore_index=-100, group=None):
-    """Mean cross entropy over ALL ranks' rows. Each rank holds a row shard. Returns (loss, dlogits_local)
-    with dlogits scaled by the global 1/n_valid. One all-reduce of two floats."""
+    """Mean cross entropy over ALL ranks' rows; each rank holds a row shard. Returns (loss,
+    dlogits_local). The valid-row count is all-reduced first (one int), so the kernel writes the
+    gradient already scaled by the global 1/n_valid; the loss numerators are all-reduced after."""
     from .kernels.cross_entropy import cross_entropy_forward
-    loss_sum, grad, n_valid = cross_entropy_forward(logits_local, targets_local, ignore_index, 'sum', needs_grad=True)
-    pair = torch.stack([loss_sum, n_valid.to(torch.float32)])
     world, _ = _world(group)
+    n_valid = (targets_local != ignore_index).sum(dtype=torch.int32)
     if world > 1:
-        dist.all_reduce(pair, op=dist.ReduceOp.SUM, group=group)
-    inv = 1.0 / pair[1].clamp_min(1.0)
-    scale = inv.reshape(1).contiguous()
-    with device_guard(grad.device):
-        rc = L.lib().hilda_scale_rows(L.ptr(grad), L.ptr(grad), L.ptr(scale), 0, grad.shape[0], grad.shape[1],
-                                      L.dt(grad), L.stream(grad.device))
-    L.check(rc, "scale_rows")
-    return pair[0] * inv, grad
+        dist.all_reduce(n_valid, op=dist.ReduceOp.SUM, group=group)
+    # 'mean' with the global count: loss_local = sum_local(loss rows) / n_valid_global
+    loss, grad, _ = cross_entropy_forward(logits_local, targets_local, ignore_index, 'mean', needs_grad=True,
+                                          n_valid_global=n_valid.reshape(1))
+    if world > 1:
+        loss = loss.clone()
+        dist.all_reduce(loss, op=dist.ReduceOp.SUM, group=group)
+    return loss, grad
 
 
 def sharded_grpo_loss(logits_local, ids_local, adv_local, old_logp=None, ref_logp=None, mask_local=None,
                       temperature=1.0, beta=0.0, eps_low=0.2, eps_high=0.2, group=None):
     """GRPO loss over sequences sharded across ranks (equal sequences per rank). Returns
-    (loss, kl_mean | None, clip_ratio, dlogits_local). One all-reduce of four floats."""
+    (loss, kl_mean | None, clip_ratio, dlogits_local). The kernel normalises by the global number
+    of sequences, so the only exchange is one all-reduce of four floats."""
     from .kernels.grpo_loss import grpo_loss_forward
     world, _ = _world(group)
+    B = logits_local.shape[0]
     loss, kl_mean, clip, lse, mask, dlogits = grpo_loss_forward(
         logits_local, ids_local, adv_local, old_logp, ref_logp, mask_local, temperature, beta, eps_low, eps_high,
-        needs_grad=True)
+        needs_grad=True, batch_total=B * world)
     if world == 1:
         return loss, kl_mean, clip, dlogits
     msum = mask.sum()
@@ -97,14 +99,7 @@ def sharded_grpo_loss(logits_local, ids_local, adv_local, old_logp=None, ref_log
     vec = torch.stack([loss, (kl_mean * mden) if kl_mean is not None else z, clip * mden, msum])
     dist.all_reduce(vec, op=dist.ReduceOp.SUM, group=group)
     gden = vec[3].clamp(min=1.0)
-    # the local gradient was scaled by 1/B_local; the global mean over sequences needs 1/(B_local*world)
-    scale = torch.full((1,), 1.0 / world, device=loss.device, dtype=torch.float32)
-    B, Lp1, V = dlogits.shape
-    with device_guard(dlogits.device):
-        rc = L.lib().hilda_scale_rows(L.ptr(dlogits), L.ptr(dlogits), L.ptr(scale), 0, B * Lp1, V, L.dt(dlogits),
-                                      L.stream(dlogits.device))
-    L.check(rc, "scale_rows")
-    return vec[0] / world, (vec[1] / gden) if kl_mean is not None else None, vec[2] / gden, dlogits
+    return vec[0], (vec[1] / gden) if kl_mean is not None else None, vec[2] / gden, dlogits
 
 
 # ------------------------------------------------------------------ vocab-parallel FusedLinearCE

@@ -104,10 +104,13 @@ int64_t hilda_cross_entropy_workspace_bytes(int64_t n_rows);
  * targets int64. grad != null: training path, grad = d loss / d logits for the given reduction
  * (0 none, 1 mean, 2 sum), written in the same pass; grad == null: inference path. loss_rows
  * [n_rows] fp32 (may be null -> kept in workspace), lse_rows optional, loss_out fp32 scalar for
- * mean/sum. Rows whose target equals ignore_index give loss 0 and a zero gradient row. */
+ * mean/sum. Rows whose target equals ignore_index give loss 0 and a zero gradient row.
+ * n_valid_in (nullable device int): number of valid rows to divide by for 'mean' instead of this
+ * call's own count (row-sharded use: the count over all shards). */
 int hilda_cross_entropy_fwd(const void* logits, const int64_t* targets, void* grad, float* loss_rows,
-                            float* lse_rows, float* loss_out, void* workspace, int64_t n_rows, int64_t V,
-                            int64_t ignore_index, int reduction, int dtype, void* stream);
+                            float* lse_rows, float* loss_out, void* workspace, const int* n_valid_in,
+                            int64_t n_rows, int64_t V, int64_t ignore_index, int reduction, int dtype,
+                            void* stream);
 
 /* Replaces _ce_scale_grad_kernel (kernels/cross_entropy.py:173-189) and _element_mul_kernel
  * (kernels/fused_linear_cross_entropy.py:84-96): out = in * scale[0] or in[r,:] * scale[r];
@@ -191,13 +194,14 @@ int64_t hilda_grpo_workspace_bytes(int64_t B);
 /* Replaces grpo_loss_forward + grpo_loss_backward (kernels/grpo_loss.py:241-297, :300-330) in one
  * pass. logits [B, L+1, V]; ids [B, L] int64; mask [B, L] int32 or null; advantages [B] fp32;
  * old_logp/ref_logp [B, L] fp32 or null. Per-token fp32 outputs loss/kl/clipped/lse [B, L];
- * scalars_out[3] = {loss, kl_mean, clip_ratio}. grad (nullable): d loss / d logits for a unit
+ * scalars_out[4] = {loss, kl_mean, clip_ratio, sum(mask)}; B_total > 0 normalises loss and gradient by
+ * B_total sequences instead of B (sequences sharded over ranks). grad (nullable): d loss / d logits for a unit
  * upstream gradient, [B, L+1, V] in dtype, last position and masked tokens zero. */
 int hilda_grpo_loss_fwd(const void* logits, const int64_t* ids, const float* advantages, const float* old_logp,
                         const float* ref_logp, const int32_t* mask, void* grad, float* loss, float* kl,
                         float* clipped, float* lse, float* scalars_out, void* workspace, int64_t B, int64_t L,
-                        int64_t V, float temperature, float beta, float eps_low, float eps_high, int dtype,
-                        void* stream);
+                        int64_t V, int64_t B_total, float temperature, float beta, float eps_low, float eps_high,
+                        int dtype, void* stream);
 
 /* Replaces fused_selective_log_softmax (kernels/grpo_loss.py:65-80). */
 int hilda_selective_log_softmax(const void* logits, const int64_t* ids, const int32_t* mask, float* logp,

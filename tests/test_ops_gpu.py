@@ -494,3 +494,52 @@ def test_grpo_golden_variants(golden):
     with torch.no_grad():
         l2, _, _ = hk.hilda_grpo_loss(logits.to(DEV), ids.to(DEV), adv.to(DEV), None, ref.to(DEV), mask.to(DEV), 0.7, 0.05)
     assert_loss_close(l2, loss)
+
+
+# ------------------------------------------------------------------ row-sharded normalisation
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_row_sharded_losses_use_global_counts(dtype):
+    """Each shard's kernel divides by the count over ALL shards (valid rows for CE, sequences for
+    GRPO), so the shards' losses add up to the unsharded loss and their gradients concatenate to
+    the unsharded gradient: what parallel.sharded_cross_entropy / sharded_grpo_loss rely on."""
+    from hilda_kernel_b200.kernels.cross_entropy import cross_entropy_forward
+    from hilda_kernel_b200.kernels.grpo_loss import grpo_loss_forward
+    g = gen(21)
+    n, v = 48, 5000
+    logits = (2.0 * torch.randn(n, v, generator=g)).to(dtype)
+    targets = torch.randint(0, v, (n,), generator=g)
+    targets[torch.randperm(n, generator=g)[:9]] = -100
+    lr = logits.float().clone().requires_grad_(True)
+    ref = R.cross_entropy(lr, targets)
+    ref.backward()
+    ld, td = logits.to(DEV), targets.to(DEV)
+    n_valid = (td != -100).sum(dtype=torch.int32).reshape(1)
+    cuts = [0, 20, 48]  # unequal shards, different numbers of ignored rows
+    total, grads = 0.0, []
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        loss, grad, nv_local = cross_entropy_forward(ld[a:b], td[a:b], -100, 'mean', needs_grad=True,
+                                                     n_valid_global=n_valid)
+        assert int(nv_local) == int((targets[a:b] != -100).sum())
+        total += float(loss)
+        grads.append(grad)
+    assert abs(total - float(ref)) <= 1e-4 * abs(float(ref))
+    assert_close(torch.cat(grads), lr.grad, dtype, what="sharded CE dlogits", normalize=True)
+
+    B, L, V = 4, 12, 3000
+    logits, ids, adv, old, refp, mask = _grpo_inputs(B, L, V, dtype, seed=22)
+    lr = logits.float().clone().requires_grad_(True)
+    ref = R.grpo_loss(lr, ids, adv, old, refp, mask, beta=0.1)
+    ref.backward()
+    kl_ref, clip_ref = R.grpo_aux(logits.float(), ids, adv, old, refp, mask, beta=0.1)
+    total, kl_num, clip_num, msum, grads = 0.0, 0.0, 0.0, 0.0, []
+    for a, b in ((0, 2), (2, 4)):
+        d = lambda t: t[a:b].to(DEV)
+        loss, kl, clip, _, m, grad = grpo_loss_forward(d(logits), d(ids), d(adv), d(old), d(refp), d(mask), 1.0, 0.1,
+                                                       0.2, 0.2, needs_grad=True, batch_total=B)
+        ms = float(m.sum())
+        total += float(loss); kl_num += float(kl) * ms; clip_num += float(clip) * ms; msum += ms
+        grads.append(grad)
+    assert abs(total - float(ref)) <= 1e-4 * abs(float(ref))
+    assert abs(kl_num / msum - float(kl_ref)) <= 1e-4 * abs(float(kl_ref))
+    assert abs(clip_num / msum - float(clip_ref)) < 1e-6 + 1.0 / (B * L)
+    assert_close(torch.cat(grads), lr.grad, dtype, what="sharded GRPO dlogits", normalize=True)

@@ -13,6 +13,7 @@
 //   4. dHidden = dlogits @ W and dW += dlogits^T @ hidden run on the same tcgen05 kernel with
 //      MN-major operands (no transposed copies); dW is accumulated across chunks in fp32 and
 //      rounded once at the end (the reference accumulates in the 16-bit dtype).
+#include <cstdio>
 #include <cstdlib>
 #include "tcgen05_gemm2.cuh"
 #include "reduce_kernels.cuh"
@@ -128,15 +129,27 @@ move_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, const i
 
 // 1: GEMMs run as CTA pairs (256 x 256 tiles, cta_group::2); 0: one CTA per 128 x 256 tile.
 // HILDA_GEMM_PAIR in the environment presets it.
+// L2 prefetch lookahead of the single-CTA GEMM's producer ("dist,mask" in HILDA_GEMM_PREFETCH)
+static int g_gemm_pf_dist = 0, g_gemm_pf_mask = 3;
+static int g_gemm_pf_env = []() {
+  const char* e = getenv("HILDA_GEMM_PREFETCH");
+  if (e) { int d = 0, m = 3; if (sscanf(e, "%d,%d", &d, &m) >= 1) { g_gemm_pf_dist = d; g_gemm_pf_mask = m; } }
+  return 0;
+}();
+static int g_debug_mfast = 1;
+static long long* g_gemm_probe = nullptr;
+static int g_gemm_dry = 0;
 static int g_gemm_pair = []() {
   const char* e = getenv("HILDA_GEMM_PAIR");
-  return e ? atoi(e) : 0;
+  return e ? (atoi(e) & 7) : 7;
 }();
 
 template <bool A_MN, bool B_MN, int EPI>
-static int run_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, const GemmParams& p, cudaStream_t st) {
-  if (g_gemm_pair) return launch_gemm2<A_MN, B_MN, EPI>(A, lda, B, ldb, p, st);
-  return run_gemm<A_MN, B_MN, EPI>(A, lda, B, ldb, p, st);
+static int run_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, GemmParams p, cudaStream_t st,
+                    int kind_bit = 7) {
+  p.pf_dist = g_gemm_pf_dist; p.pf_mask = g_gemm_pf_mask; p.probe = g_gemm_probe; p.dry = g_gemm_dry;
+  if (g_gemm_pair & kind_bit) return launch_gemm2<A_MN, B_MN, EPI>(A, lda, B, ldb, p, st);
+  return launch_gemm<A_MN, B_MN, EPI>(A, lda, B, ldb, p, st);
 }
 
 // Optional timing of the GEMM launches with CUDA events on the launching stream (off by default).
@@ -175,7 +188,7 @@ static int flce_logits(const void* hidden, const void* W, void* logits, float* s
   p.stats = reinterpret_cast<float2*>(stats); p.stats_ld = (V + BN - 1) / BN;
   p.status = status;
   ProfScope prof(0, st);
-  return run_gemm<false, false, EPI_LOGITS_STATS>(hidden, H, W, H, p, st);
+  return run_gemm<false, false, EPI_LOGITS_STATS>(hidden, H, W, H, p, st, 1);
 }
 
 static int flce_grad_hidden(const void* dlogits, const void* W, void* dh16, float* dh32, int64_t rows, int64_t H,
@@ -187,10 +200,10 @@ static int flce_grad_hidden(const void* dlogits, const void* W, void* dh16, floa
   ProfScope prof(1, st);
   if (dh16) {
     p.C16 = dh16; p.ldc16 = H;
-    return run_gemm<false, true, EPI_STORE16>(dlogits, pitch, W, H, p, st);
+    return run_gemm<false, true, EPI_STORE16>(dlogits, pitch, W, H, p, st, 2);
   }
   p.C32 = dh32; p.ldc32 = H;
-  return run_gemm<false, true, EPI_STORE32>(dlogits, pitch, W, H, p, st);
+  return run_gemm<false, true, EPI_STORE32>(dlogits, pitch, W, H, p, st, 2);
 }
 
 // mode 0: dw32 = D^T h; 1: dw32 += D^T h; 2: dw16 = dw32 + D^T h; 3: dw16 = D^T h
@@ -202,10 +215,10 @@ static int flce_grad_weight(const void* dlogits, const void* hidden, float* dw32
   const int64_t pitch = round_up(V, BN);
   ProfScope prof(2, st);
   switch (mode) {
-    case 0: return run_gemm<true, true, EPI_STORE32>(dlogits, pitch, hidden, H, p, st);
-    case 1: return run_gemm<true, true, EPI_ACCUM32>(dlogits, pitch, hidden, H, p, st);
-    case 2: return run_gemm<true, true, EPI_ACCUM_FINAL16>(dlogits, pitch, hidden, H, p, st);
-    case 3: return run_gemm<true, true, EPI_STORE16>(dlogits, pitch, hidden, H, p, st);
+    case 0: return run_gemm<true, true, EPI_STORE32>(dlogits, pitch, hidden, H, p, st, 4);
+    case 1: return run_gemm<true, true, EPI_ACCUM32>(dlogits, pitch, hidden, H, p, st, 4);
+    case 2: return run_gemm<true, true, EPI_ACCUM_FINAL16>(dlogits, pitch, hidden, H, p, st, 4);
+    case 3: return run_gemm<true, true, EPI_STORE16>(dlogits, pitch, hidden, H, p, st, 4);
   }
   return HILDA_ERR_ARG;
 }
@@ -482,8 +495,19 @@ int hilda_scatter_rows(const void* src, const int64_t* idx, void* dst, int64_t n
   return HILDA_OK;
 }
 
-// Select the GEMM variant: 1 = CTA pairs (cta_group::2, 256 x 256 tiles), 0 = single CTAs.
-void hilda_gemm_set_pair(int enable) { g_gemm_pair = enable ? 1 : 0; }
+// Select the GEMM variant per use: bit 0 = logits, bit 1 = d(hidden), bit 2 = d(W) run on CTA pairs
+// (cta_group::2, 256 x 256 tiles); a clear bit = single CTAs. hilda_debug_gemm uses pairs if any bit is set.
+void hilda_gemm_set_pair(int mask) { g_gemm_pair = mask & 7; }
+// Tuning hooks: L2 prefetch lookahead (k-blocks; mask bit 0 = A, bit 1 = B) of the single-CTA
+// kernel, and the tile walk order used by hilda_debug_gemm (1 = M first, 0 = N first).
+void hilda_gemm_set_prefetch(int dist, int mask) { g_gemm_pf_dist = dist < 0 ? 0 : dist; g_gemm_pf_mask = mask & 3; }
+void hilda_debug_gemm_set_order(int m_fast) { g_debug_mfast = m_fast ? 1 : 0; }
+// Cycle counters of the single-CTA GEMM's role loops: device buffer of [sm_count][8] int64
+// {producer wait-for-slot, producer total, issuer wait-for-data, issuer wait-for-accumulator,
+//  issuer total, epilogue wait-for-accumulator, epilogue busy, 0}; null switches it off.
+// dry != 0 (measurement only, results are garbage): the producer signals its slots full without
+// loading anything, which shows the rate of the MMA / barrier loop with the memory system out of it.
+void hilda_gemm_set_probe(void* buf, int dry) { g_gemm_probe = (long long*)buf; g_gemm_dry = dry; }
 int hilda_gemm_get_pair(void) { return g_gemm_pair; }
 
 // Plain GEMM through the same kernel, for validating operand layouts against a library matmul.
@@ -496,7 +520,7 @@ int hilda_debug_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, voi
   // the epilogue stores 16-byte vectors: rows of C must start on 16-byte boundaries
   if (ldc % 8 != 0 || N % 8 != 0 || !aligned16(c16) || !aligned16(c32)) return HILDA_ERR_ALIGN;
   GemmParams p = {};
-  p.M = M; p.N = N; p.K = K; p.m_fast = 1; p.is_bf16 = dtype == HILDA_BF16; p.status = status;
+  p.M = M; p.N = N; p.K = K; p.m_fast = g_debug_mfast; p.is_bf16 = dtype == HILDA_BF16; p.status = status;
   p.C16 = c16; p.ldc16 = ldc; p.C32 = c32; p.ldc32 = ldc;
   p.mn_lbo = (uint32_t)mn_lbo; p.mn_sbo = (uint32_t)mn_sbo;
   cudaStream_t st = (cudaStream_t)stream;

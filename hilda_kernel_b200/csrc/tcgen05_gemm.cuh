@@ -44,6 +44,12 @@ struct GemmParams {
   float2* stats; int64_t stats_ld;
   int* status;       // device word; non-zero = a bounded wait ran out
   uint32_t mn_lbo, mn_sbo;  // descriptor byte offsets for MN-major operands (8192, 1024)
+  int pf_dist;       // L2 prefetch lookahead of the TMA producer in k-blocks (0 = off)
+  int pf_mask;       // bit 0: prefetch A, bit 1: prefetch B
+  int pf_a_div, pf_b_div;  // CTAs that stream the same A / B slab at the same time: they share the
+                           // prefetch duty, each taking the k-blocks congruent to its own rank
+  long long* probe;  // optional [gridDim.x][8] cycle counters of the role loops (null = off)
+  int dry;           // measurement only: the producer signals "full" without loading (results are garbage)
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------
@@ -87,6 +93,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tma
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1) : "memory");
 }
+// Bring one box of a tensor map into L2 only (no shared-memory destination, no barrier).
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* tmap, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(c0), "r"(c1) : "memory");
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
 }
@@ -102,6 +112,63 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
       "setp.ne.b32 p, %4, 0;\n"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Same instruction with the two shared-memory descriptors passed as 32-bit halves: the issuing
+// thread only adds a constant to the low words between MMAs (its serial instruction latency, not
+// the tensor pipe, is what bounds a k-block otherwise).
+__device__ __forceinline__ void umma_f16_split(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+      "mov.b64 da, {%1, %2};\n"
+      "mov.b64 db, {%3, %4};\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Halves of the 128-byte-swizzle descriptor (see make_smem_desc): the low word carries the start
+// address (16-byte units, bits 0-13) and LBO (bits 16-29); the high word SBO, version and swizzle.
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t addr, uint32_t lbo_bytes) {
+  return ((addr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ uint32_t smem_desc_hi(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+// One k-block of the issuer, as a single instruction sequence: peek at the NEXT slot's "full"
+// barrier first (its latency then hides under the MMA issue instead of sitting between two
+// k-blocks), the four K = 16 MMAs of this slot, the commit that frees it, and only then the
+// peek's result. Returns 1 when the next slot was already full. peek_bar == 0 skips the peek.
+template <uint32_t A_KSTEP, uint32_t B_KSTEP>
+__device__ __forceinline__ uint32_t umma_kblock(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                                uint32_t idesc, uint32_t accumulate, uint32_t empty_bar_addr,
+                                                uint32_t peek_bar, uint32_t peek_parity) {
+  uint32_t ready;
+  asm volatile(
+      "{\n.reg .pred p, q, t;\n.reg .b64 da, db;\n.reg .b32 al, bl;\n"
+      "setp.ne.b32 t, %9, 0;\n"
+      "mov.pred q, 0;\n"
+      "@t mbarrier.try_wait.parity.shared::cta.b64 q, [%9], %10;\n"
+      "setp.ne.b32 p, %7, 0;\n"
+      "mov.b64 da, {%2, %3};\n"
+      "mov.b64 db, {%4, %5};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %6, p;\n"
+      "setp.ne.b32 p, 1, 0;\n"
+      "add.u32 al, %2, %11;\n add.u32 bl, %4, %12;\n"
+      "mov.b64 da, {al, %3};\n mov.b64 db, {bl, %5};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %6, p;\n"
+      "add.u32 al, al, %11;\n add.u32 bl, bl, %12;\n"
+      "mov.b64 da, {al, %3};\n mov.b64 db, {bl, %5};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %6, p;\n"
+      "add.u32 al, al, %11;\n add.u32 bl, bl, %12;\n"
+      "mov.b64 da, {al, %3};\n mov.b64 db, {bl, %5};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %6, p;\n"
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%8];\n"
+      "selp.u32 %0, 1, 0, q;\n}"
+      : "=r"(ready)
+      : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(empty_bar_addr),
+        "r"(peek_bar), "r"(peek_parity), "n"(A_KSTEP), "n"(B_KSTEP)
+      : "memory");
+  return ready;
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -282,14 +349,46 @@ tcgen05_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      long long w_empty = 0;
+      const long long t_begin = clock64();
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int mt = p.m_fast ? tile % p.m_tiles : tile / p.n_tiles;
         const int nt = p.m_fast ? tile / p.m_tiles : tile % p.n_tiles;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (p.pf_dist > 0) {
+            // L2 lookahead: the boxes pf_dist k-blocks from now (in this tile or the next one this
+            // CTA owns). CTAs streaming the same slab split the duty, so each box is requested once
+            // and the shared-memory ring only ever waits on L2 latency, not on DRAM.
+            int pk = kb + p.pf_dist, ptile = tile;
+            if (pk >= p.k_blocks) { pk -= p.k_blocks; ptile += gridDim.x; }
+            if (ptile < total_tiles && pk < p.k_blocks) {
+              const int pmt = p.m_fast ? ptile % p.m_tiles : ptile / p.n_tiles;
+              const int pnt = p.m_fast ? ptile / p.m_tiles : ptile % p.n_tiles;
+              if ((p.pf_mask & 1) && pk % p.pf_a_div == pnt % p.pf_a_div) {
+                if constexpr (!A_MN) {
+                  tma_prefetch_2d(&tmA, pk * BK, pmt * BM);
+                } else {
+#pragma unroll
+                  for (int j = 0; j < BM / 64; ++j) tma_prefetch_2d(&tmA, pmt * BM + j * 64, pk * BK);
+                }
+              }
+              if ((p.pf_mask & 2) && pk % p.pf_b_div == pmt % p.pf_b_div) {
+                if constexpr (!B_MN) {
+                  tma_prefetch_2d(&tmB, pk * BK, pnt * BN);
+                } else {
+#pragma unroll
+                  for (int j = 0; j < BN / 64; ++j) tma_prefetch_2d(&tmB, pnt * BN + j * 64, pk * BK);
+                }
+              }
+            }
+          }
+          const long long t0 = p.probe ? clock64() : 0;
           if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abortp, p.status, 1)) { ok = false; break; }
+          if (p.probe) w_empty += clock64() - t0;
           const uint32_t fb = smem_u32(&full_bar[stage]);
           const uint32_t sA = stage_base + stage * STAGE_BYTES;
           const uint32_t sB = sA + A_STAGE_BYTES;
+          if (p.dry) { mbar_arrive(fb); if (++stage == GEMM_STAGES) { stage = 0; phase ^= 1u; } continue; }
           mbar_expect_tx(fb, STAGE_BYTES);
           if constexpr (!A_MN) {
             tma_load_2d(sA, &tmA, fb, kb * BK, mt * BM);
@@ -306,34 +405,58 @@ tcgen05_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if (++stage == GEMM_STAGES) { stage = 0; phase ^= 1u; }
         }
       }
+      if (p.probe) { p.probe[blockIdx.x * 8 + 0] = w_empty; p.probe[blockIdx.x * 8 + 1] = clock64() - t_begin; }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
+      long long w_full = 0, w_tempty = 0;
+      const long long t_begin = clock64();
+      // everything the loop needs, in registers: this thread's instruction latency per k-block
+      // has to stay under the 4 x 128 cycles the tensor pipe takes for it
+      const bool probing = p.probe != nullptr;
+      const int k_blocks = p.k_blocks;
+      const uint32_t idesc = p.idesc;
+      const uint32_t a_hi = smem_desc_hi(A_MN ? p.mn_sbo : 1024u), b_hi = smem_desc_hi(B_MN ? p.mn_sbo : 1024u);
+      const uint32_t a_lo0 = smem_desc_lo(stage_base, A_MN ? p.mn_lbo : 0u);
+      const uint32_t b_lo0 = smem_desc_lo(stage_base + A_STAGE_BYTES, B_MN ? p.mn_lbo : 0u);
+      constexpr uint32_t A_KSTEP = (A_MN ? 2048u : 32u) >> 4, B_KSTEP = (B_MN ? 2048u : 32u) >> 4;  // per UMMA_K, 16-byte units
+      const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
+      uint32_t ready = 0;  // set when the peek of the previous k-block already saw this slot full
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const long long t1 = probing ? clock64() : 0;
         if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1u, abortp, p.status, 2)) break;
+        if (probing) w_tempty += clock64() - t1;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abortp, p.status, 3)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t sA = stage_base + stage * STAGE_BYTES;
-          const uint32_t sB = sA + A_STAGE_BYTES;
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t ad = A_MN ? make_smem_desc(sA + k * 2048, p.mn_lbo, p.mn_sbo) : make_smem_desc(sA + k * 32, 0, 1024);
-            const uint64_t bd = B_MN ? make_smem_desc(sB + k * 2048, p.mn_lbo, p.mn_sbo) : make_smem_desc(sB + k * 32, 0, 1024);
-            umma_f16(d_tmem, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
+        uint32_t accum = 0;
+        const bool more_tiles = tile + (int)gridDim.x < total_tiles;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!ready) {
+            const long long t0 = probing ? clock64() : 0;
+            if (!mbar_wait(full0 + stage * 8u, phase, abortp, p.status, 3)) { ok = false; break; }
+            if (probing) w_full += clock64() - t0;
           }
-          umma_commit(smem_u32(&empty_bar[stage]));  // frees the smem slot when these MMAs retire
+          tc_fence_after();
+          const uint32_t a_lo = a_lo0 + stage * (uint32_t)(STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + stage * (uint32_t)(STAGE_BYTES >> 4);
+          const uint32_t empty_addr = empty0 + stage * 8u;
           if (++stage == GEMM_STAGES) { stage = 0; phase ^= 1u; }
+          // the next slot of the ring is this CTA's next k-block, in this tile or its next one
+          const uint32_t peek = (kb + 1 < k_blocks || more_tiles) ? full0 + stage * 8u : 0u;
+          ready = umma_kblock<A_KSTEP, B_KSTEP>(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, accum, empty_addr, peek, phase);
+          accum = 1u;
         }
         if (!ok) break;
         umma_commit(smem_u32(&tfull_bar[acc]));  // accumulator complete
         acc ^= 1u;
         if (acc == 0) acc_phase ^= 1u;
+      }
+      if (p.probe) {
+        p.probe[blockIdx.x * 8 + 2] = w_full; p.probe[blockIdx.x * 8 + 3] = w_tempty;
+        p.probe[blockIdx.x * 8 + 4] = clock64() - t_begin;
       }
     }
   } else {
@@ -341,10 +464,14 @@ tcgen05_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int q = warp & 3;  // TMEM lane quadrant this warp may access
     const int row_in_tile = q * 32 + lane;
     uint32_t acc = 0, acc_phase = 0;
+    long long w_tfull = 0, t_epi = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       const int mt = p.m_fast ? tile % p.m_tiles : tile / p.n_tiles;
       const int nt = p.m_fast ? tile / p.m_tiles : tile % p.n_tiles;
+      const long long t0 = p.probe ? clock64() : 0;
       if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase, abortp, p.status, 4)) break;
+      const long long t1 = p.probe ? clock64() : 0;
+      w_tfull += t1 - t0;
       tc_fence_after();
       const int64_t row = (int64_t)mt * BM + row_in_tile;
       const int col0 = nt * BN;
@@ -353,9 +480,11 @@ tcgen05_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+      if (p.probe) t_epi += clock64() - t1;
       acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (p.probe && warp == 2 && lane == 0) { p.probe[blockIdx.x * 8 + 5] = w_tfull; p.probe[blockIdx.x * 8 + 6] = t_epi; }
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -412,6 +541,21 @@ static inline uint32_t make_idesc(int is_bf16, bool a_mn, bool b_mn) {
 // C[M,N] = A x B with A given as [M,K] (K-major, a_mn=false) or stored [K,M] (MN-major, a_mn=true),
 // B given as [N,K] (K-major) or stored [K,N] (MN-major). lda/ldb are row pitches in elements of the
 // STORED matrices.
+// How many of the `concurrent` CTAs (or CTA pairs) stream the same A slab / B slab at a time,
+// given the tile walk order: they split the L2 prefetch duty among themselves.
+static inline void gemm_prefetch_duty(GemmParams& p, int concurrent) {
+  auto clampdiv = [](int v) { return v < 1 ? 1 : v; };
+  if (p.m_fast) {
+    p.pf_b_div = clampdiv(p.m_tiles < concurrent ? p.m_tiles : concurrent);
+    p.pf_a_div = clampdiv(concurrent / clampdiv(p.m_tiles));
+    if (p.pf_a_div > p.n_tiles) p.pf_a_div = clampdiv(p.n_tiles);
+  } else {
+    p.pf_a_div = clampdiv(p.n_tiles < concurrent ? p.n_tiles : concurrent);
+    p.pf_b_div = clampdiv(concurrent / clampdiv(p.n_tiles));
+    if (p.pf_b_div > p.m_tiles) p.pf_b_div = clampdiv(p.m_tiles);
+  }
+}
+
 template <bool A_MN, bool B_MN, int EPI>
 static int launch_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, GemmParams p, cudaStream_t st) {
   if (p.M <= 0 || p.N <= 0 || p.K <= 0) return HILDA_ERR_SIZE;
@@ -435,6 +579,7 @@ static int launch_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, G
   if (tiles > 0x7fffffffLL) return HILDA_ERR_SIZE;
   int grid = sm_count();
   if (tiles < grid) grid = (int)tiles;
+  gemm_prefetch_duty(p, grid);
   kern<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(tmA, tmB, p);
   HILDA_LAUNCH_CHECK();
   return HILDA_OK;

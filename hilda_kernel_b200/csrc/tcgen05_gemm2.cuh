@@ -16,7 +16,7 @@
 
 namespace hilda {
 
-constexpr int G2_STAGES = 6;
+constexpr int G2_STAGES = 7;
 constexpr int G2_B_ROWS = BN / 2;                      // B columns staged per CTA
 constexpr int G2_A_BYTES = BM * BK * 2;                // 16 KB
 constexpr int G2_B_BYTES = G2_B_ROWS * BK * 2;         // 16 KB
@@ -70,6 +70,43 @@ __device__ __forceinline__ void g2_umma_commit_pair(uint32_t bar) {
                ::"r"(bar), "h"(mask) : "memory");
 }
 
+// One k-block of the pair's issuer as a single instruction sequence (see umma_kblock): peek at
+// the next slot's "full" barrier, four cta_group::2 MMAs, the commit that frees the slot in both
+// CTAs, then the peek's result.
+template <uint32_t A_KSTEP, uint32_t B_KSTEP>
+__device__ __forceinline__ uint32_t g2_umma_kblock(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                   uint32_t b_hi, uint32_t idesc, uint32_t accumulate,
+                                                   uint32_t empty_bar_addr, uint32_t peek_bar, uint32_t peek_parity) {
+  uint32_t ready;
+  const uint16_t mask = 0x3;
+  asm volatile(
+      "{\n.reg .pred p, q, t;\n.reg .b64 da, db;\n.reg .b32 al, bl;\n"
+      "setp.ne.b32 t, %9, 0;\n"
+      "mov.pred q, 0;\n"
+      "@t mbarrier.try_wait.parity.shared::cta.b64 q, [%9], %10;\n"
+      "setp.ne.b32 p, %7, 0;\n"
+      "mov.b64 da, {%2, %3};\n"
+      "mov.b64 db, {%4, %5};\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], da, db, %6, p;\n"
+      "setp.ne.b32 p, 1, 0;\n"
+      "add.u32 al, %2, %11;\n add.u32 bl, %4, %12;\n"
+      "mov.b64 da, {al, %3};\n mov.b64 db, {bl, %5};\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], da, db, %6, p;\n"
+      "add.u32 al, al, %11;\n add.u32 bl, bl, %12;\n"
+      "mov.b64 da, {al, %3};\n mov.b64 db, {bl, %5};\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], da, db, %6, p;\n"
+      "add.u32 al, al, %11;\n add.u32 bl, bl, %12;\n"
+      "mov.b64 da, {al, %3};\n mov.b64 db, {bl, %5};\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], da, db, %6, p;\n"
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%8], %13;\n"
+      "selp.u32 %0, 1, 0, q;\n}"
+      : "=r"(ready)
+      : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(empty_bar_addr),
+        "r"(peek_bar), "r"(peek_parity), "n"(A_KSTEP), "n"(B_KSTEP), "h"(mask)
+      : "memory");
+  return ready;
+}
+
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 tcgen05_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
@@ -111,17 +148,53 @@ tcgen05_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      long long w_empty = 0;
+      const long long t_begin = clock64();
       for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
         const int mt = p.m_fast ? tile % p.m_tiles : tile / p.n_tiles;
         const int nt = p.m_fast ? tile / p.m_tiles : tile % p.n_tiles;
         const int m0 = mt * (2 * BM) + (int)rank * BM;        // this CTA's 128 rows of A
         const int n0 = nt * BN + (int)rank * G2_B_ROWS;        // this CTA's 128 columns of B
         for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (p.pf_dist > 0) {
+            // L2 lookahead, duty shared among the pairs that stream the same slab (see the
+            // single-CTA kernel); each CTA of the pair looks after its own halves
+            int pk = kb + p.pf_dist, ptile = tile;
+            if (pk >= p.k_blocks) { pk -= p.k_blocks; ptile += n_pairs; }
+            if (ptile < total_tiles && pk < p.k_blocks) {
+              const int pmt = p.m_fast ? ptile % p.m_tiles : ptile / p.n_tiles;
+              const int pnt = p.m_fast ? ptile / p.m_tiles : ptile % p.n_tiles;
+              const int pm0 = pmt * (2 * BM) + (int)rank * BM, pn0 = pnt * BN + (int)rank * G2_B_ROWS;
+              if ((p.pf_mask & 1) && pk % p.pf_a_div == pnt % p.pf_a_div) {
+                if constexpr (!A_MN) {
+                  tma_prefetch_2d(&tmA, pk * BK, pm0);
+                } else {
+#pragma unroll
+                  for (int j = 0; j < BM / 64; ++j) tma_prefetch_2d(&tmA, pm0 + j * 64, pk * BK);
+                }
+              }
+              if ((p.pf_mask & 2) && pk % p.pf_b_div == pmt % p.pf_b_div) {
+                if constexpr (!B_MN) {
+                  tma_prefetch_2d(&tmB, pk * BK, pn0);
+                } else {
+#pragma unroll
+                  for (int j = 0; j < G2_B_ROWS / 64; ++j) tma_prefetch_2d(&tmB, pn0 + j * 64, pk * BK);
+                }
+              }
+            }
+          }
+          const long long t0 = p.probe ? clock64() : 0;
           if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abortp, p.status, 21)) { ok = false; break; }
+          if (p.probe) w_empty += clock64() - t0;
           const uint32_t fb_local = smem_u32(&full_bar[stage]);
           const uint32_t fb = g2_map_rank(fb_local, 0);  // the leader's barrier
           const uint32_t sA = stage_base + stage * G2_STAGE_BYTES;
           const uint32_t sB = sA + G2_A_BYTES;
+          if (p.dry) {
+            if (leader) mbar_arrive(fb_local);
+            if (++stage == G2_STAGES) { stage = 0; phase ^= 1u; }
+            continue;
+          }
           if (leader) mbar_expect_tx(fb_local, 2 * G2_STAGE_BYTES);
           if constexpr (!A_MN) {
             g2_tma_load_2d(sA, &tmA, fb, kb * BK, m0);
@@ -138,34 +211,54 @@ tcgen05_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           if (++stage == G2_STAGES) { stage = 0; phase ^= 1u; }
         }
       }
+      if (p.probe && leader) { p.probe[pair * 8 + 0] = w_empty; p.probe[pair * 8 + 1] = clock64() - t_begin; }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && leader) {
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
+      long long w_full = 0, w_tempty = 0;
+      const long long t_begin = clock64();
+      const bool probing = p.probe != nullptr;
+      const int k_blocks = p.k_blocks;
+      const uint32_t idesc = p.idesc;
+      const uint32_t a_hi = smem_desc_hi(A_MN ? p.mn_sbo : 1024u), b_hi = smem_desc_hi(B_MN ? p.mn_sbo : 1024u);
+      const uint32_t a_lo0 = smem_desc_lo(stage_base, A_MN ? p.mn_lbo : 0u);
+      const uint32_t b_lo0 = smem_desc_lo(stage_base + G2_A_BYTES, B_MN ? p.mn_lbo : 0u);
+      constexpr uint32_t A_KSTEP = (A_MN ? 2048u : 32u) >> 4, B_KSTEP = (B_MN ? 2048u : 32u) >> 4;
+      const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
+      uint32_t ready = 0;  // set when the peek of the previous k-block already saw this slot full
       for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+        const long long t1 = probing ? clock64() : 0;
         if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1u, abortp, p.status, 22)) break;
+        if (probing) w_tempty += clock64() - t1;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abortp, p.status, 23)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t sA = stage_base + stage * G2_STAGE_BYTES;
-          const uint32_t sB = sA + G2_A_BYTES;
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t ad = A_MN ? make_smem_desc(sA + k * 2048, p.mn_lbo, p.mn_sbo) : make_smem_desc(sA + k * 32, 0, 1024);
-            const uint64_t bd = B_MN ? make_smem_desc(sB + k * 2048, p.mn_lbo, p.mn_sbo) : make_smem_desc(sB + k * 32, 0, 1024);
-            g2_umma_f16(d_tmem, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
+        uint32_t accum = 0;
+        const bool more_tiles = tile + n_pairs < total_tiles;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!ready) {
+            const long long t0 = probing ? clock64() : 0;
+            if (!mbar_wait(full0 + stage * 8u, phase, abortp, p.status, 23)) { ok = false; break; }
+            if (probing) w_full += clock64() - t0;
           }
-          g2_umma_commit_pair(smem_u32(&empty_bar[stage]));  // frees this stage in both CTAs
+          tc_fence_after();
+          const uint32_t a_lo = a_lo0 + stage * (uint32_t)(G2_STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + stage * (uint32_t)(G2_STAGE_BYTES >> 4);
+          const uint32_t empty_addr = empty0 + stage * 8u;
           if (++stage == G2_STAGES) { stage = 0; phase ^= 1u; }
+          const uint32_t peek = (kb + 1 < k_blocks || more_tiles) ? full0 + stage * 8u : 0u;
+          ready = g2_umma_kblock<A_KSTEP, B_KSTEP>(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, accum, empty_addr, peek, phase);
+          accum = 1u;
         }
         if (!ok) break;
         g2_umma_commit_pair(smem_u32(&tfull_bar[acc]));  // accumulator halves complete in both CTAs
         acc ^= 1u;
         if (acc == 0) acc_phase ^= 1u;
+      }
+      if (p.probe) {
+        p.probe[pair * 8 + 2] = w_full; p.probe[pair * 8 + 3] = w_tempty; p.probe[pair * 8 + 4] = clock64() - t_begin;
       }
     }
   } else {
@@ -173,10 +266,14 @@ tcgen05_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     const int q = warp & 3;
     const int row_in_tile = q * 32 + lane;
     uint32_t acc = 0, acc_phase = 0;
+    long long w_tfull = 0, t_epi = 0;
     for (int tile = pair; tile < total_tiles; tile += n_pairs) {
       const int mt = p.m_fast ? tile % p.m_tiles : tile / p.n_tiles;
       const int nt = p.m_fast ? tile / p.m_tiles : tile % p.n_tiles;
+      const long long t0 = p.probe ? clock64() : 0;
       if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase, abortp, p.status, 24)) break;
+      const long long t1 = p.probe ? clock64() : 0;
+      w_tfull += t1 - t0;
       tc_fence_after();
       const int64_t row = (int64_t)mt * (2 * BM) + (int64_t)rank * BM + row_in_tile;
       const uint32_t taddr0 = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
@@ -184,9 +281,11 @@ tcgen05_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       tc_fence_before();
       __syncwarp();
       if (lane == 0) g2_mbar_arrive_remote(g2_map_rank(smem_u32(&tempty_bar[acc]), 0));
+      if (p.probe) t_epi += clock64() - t1;
       acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (p.probe && leader && warp == 2 && lane == 0) { p.probe[pair * 8 + 5] = w_tfull; p.probe[pair * 8 + 6] = t_epi; }
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -226,6 +325,7 @@ static int launch_gemm2(const void* A, int64_t lda, const void* B, int64_t ldb, 
   if (tiles > 0x7fffffffLL) return HILDA_ERR_SIZE;
   int pairs = sm_count() / 2;
   if (tiles < pairs) pairs = (int)tiles;
+  gemm_prefetch_duty(p, pairs);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(pairs * 2), 1, 1);
   cfg.blockDim = dim3(GEMM_THREADS, 1, 1);

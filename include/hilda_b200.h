@@ -178,10 +178,23 @@ int hilda_gather_rows(const void* src, const int64_t* idx, void* dst, int64_t n_
 int hilda_scatter_rows(const void* src, const int64_t* idx, void* dst, int64_t n_idx, int64_t n_dst_rows,
                        int64_t row_bytes, void* stream);
 
-/* GEMM variant used by the FLCE entry points (no counterpart in the reference): 1 = CTA pairs
- * (tcgen05 cta_group::2, 256 x 256 tiles over two SMs), 0 = one CTA per 128 x 256 tile. */
-void hilda_gemm_set_pair(int enable);
+/* GEMM variant used by the FLCE entry points (no counterpart in the reference), per use: bit 0 =
+ * logits GEMM, bit 1 = d(hidden) GEMM, bit 2 = d(W) GEMM run on CTA pairs (tcgen05 cta_group::2,
+ * 256 x 256 tiles over two SMs); a clear bit = one CTA per 128 x 256 tile. hilda_debug_gemm uses
+ * pairs when any bit is set. Initial value: environment HILDA_GEMM_PAIR, else the built-in default. */
+void hilda_gemm_set_pair(int mask);
 int hilda_gemm_get_pair(void);
+/* Tuning hooks (no counterpart in the reference): L2 prefetch lookahead of the single-CTA GEMM's
+ * TMA producer in k-blocks (0 = off; mask bit 0 = operand A, bit 1 = operand B), and the tile walk
+ * order hilda_debug_gemm uses (1 = M first, 0 = N first). */
+void hilda_gemm_set_prefetch(int dist, int mask);
+void hilda_debug_gemm_set_order(int m_fast);
+/* Cycle counters of the single-CTA GEMM's role loops, written by every launch while set: device
+ * buffer of [SM count][8] int64 {producer wait-for-slot, producer total, issuer wait-for-data,
+ * issuer wait-for-accumulator, issuer total, epilogue wait-for-accumulator, epilogue busy, 0};
+ * NULL switches it off (the default). dry != 0 is for measurement only (results are garbage): the
+ * producer marks its slots full without loading, taking the memory system out of the loop. */
+void hilda_gemm_set_probe(void* buf, int dry);
 
 /* Validation hook: plain C = A x B through the tcgen05 kernel with either operand K-major
  * ([M,K] / [N,K]) or MN-major (stored [K,M] / [K,N]). No counterpart in the reference. */

@@ -23,16 +23,17 @@ def _lib():
 @pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 0), (1, 1)])
 @pytest.mark.parametrize("mnk", [(128, 256, 64), (300, 520, 200), (1000, 1000, 1000), (129, 264, 72), (64, 8, 4096)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("pair", [0, 1])
+@pytest.mark.parametrize("pair", [0, 7])
 def test_tcgen05_gemm_layouts(a_mn, b_mn, mnk, dtype, pair):
     """C = A x B through the tcgen05 kernel for K-major and MN-major operands, ragged sizes; as single
     CTAs (128 x 256 tiles) and as CTA pairs (cta_group::2, 256 x 256 tiles)."""
     L = _lib()
+    default = L.lib().hilda_gemm_get_pair()
     L.lib().hilda_gemm_set_pair(pair)
     try:
         _gemm_case(L, a_mn, b_mn, mnk, dtype)
     finally:
-        L.lib().hilda_gemm_set_pair(0)
+        L.lib().hilda_gemm_set_pair(default)
 
 
 def _gemm_case(L, a_mn, b_mn, mnk, dtype):
@@ -135,13 +136,15 @@ def test_flce_cta_pair_mode_matches_single_cta():
     from hilda_kernel_b200.kernels.fused_linear_cross_entropy import fused_linear_cross_entropy_forward
     hidden, weight, targets = _flce_inputs(700, 512, 3000, torch.bfloat16)
     hd, wd, td = hidden.to(DEV), weight.to(DEV), targets.to(DEV)
-    l0, dh0, dw0, _ = fused_linear_cross_entropy_forward(hd, wd, td, chunk_rows=256)
-    L.lib().hilda_gemm_set_pair(1)
+    default = L.lib().hilda_gemm_get_pair()
+    L.lib().hilda_gemm_set_pair(0)
     try:
+        l0, dh0, dw0, _ = fused_linear_cross_entropy_forward(hd, wd, td, chunk_rows=256)
+        L.lib().hilda_gemm_set_pair(7)
         l1, dh1, dw1, _ = fused_linear_cross_entropy_forward(hd, wd, td, chunk_rows=256)
         torch.cuda.synchronize()
     finally:
-        L.lib().hilda_gemm_set_pair(0)
+        L.lib().hilda_gemm_set_pair(default)
     assert_loss_close(l1, l0)
     assert_close(dh1, dh0.float(), torch.bfloat16, what="d hidden", normalize=True)
     assert_close(dw1, dw0.float(), torch.bfloat16, what="d weight", normalize=True)

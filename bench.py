@@ -490,7 +490,8 @@ def run_ours(args):
     rows_alg = n_valid if FL.SKIP_IGNORED_ROWS else BT
     flops_rank = 6.0 * rows_alg * (v1 - v0) * H
     achieved = flops_rank * args.steps / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
-    n_chunks = -(-BT // int(lib.hilda_flce_default_chunk_rows(BT, H, v1 - v0)))
+    chunk_rows = FL.CHUNK_ROWS or int(lib.hilda_flce_default_chunk_rows(rows_alg, H, v1 - v0))
+    n_chunks = -(-rows_alg // chunk_rows)
     launches_per_step = 2 + 6 * n_chunks
     result = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -501,7 +502,7 @@ def run_ours(args):
                    "sharding": "single GPU" if world == 1 else f"W vocab-sharded over {world} ranks, hidden replicated",
                    "ignored_rows": f"compacted away before the GEMMs ({n_valid} of {BT} rows computed)"
                    if FL.SKIP_IGNORED_ROWS else "computed like any other row",
-                   "row_chunks": n_chunks, "l2": "inputs (1.05 GB W per pass) exceed the 126 MB L2; no flush needed"},
+                   "row_chunks": n_chunks, "chunk_rows": chunk_rows, "l2": "inputs (1.05 GB W per pass) exceed the 126 MB L2; no flush needed"},
         "tflops_whole_step": 6.0 * rows_alg * V * H / world / (ms_step * 1e-3) / 1e12,
         "roofline": {"bound": "tensor", "kernel": "tcgen05_gemm_kernel (logits, d hidden, d W instantiations)",
                      "achieved": achieved, "peak": pk["tf_sustained"], "unit": "TFLOP/s",

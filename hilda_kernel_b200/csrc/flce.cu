@@ -129,13 +129,6 @@ move_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, const i
 
 // 1: GEMMs run as CTA pairs (256 x 256 tiles, cta_group::2); 0: one CTA per 128 x 256 tile.
 // HILDA_GEMM_PAIR in the environment presets it.
-// L2 prefetch lookahead of the single-CTA GEMM's producer ("dist,mask" in HILDA_GEMM_PREFETCH)
-static int g_gemm_pf_dist = 0, g_gemm_pf_mask = 3;
-static int g_gemm_pf_env = []() {
-  const char* e = getenv("HILDA_GEMM_PREFETCH");
-  if (e) { int d = 0, m = 3; if (sscanf(e, "%d,%d", &d, &m) >= 1) { g_gemm_pf_dist = d; g_gemm_pf_mask = m; } }
-  return 0;
-}();
 static int g_debug_mfast = 1;
 static long long* g_gemm_probe = nullptr;
 static int g_gemm_dry = 0;
@@ -147,7 +140,7 @@ static int g_gemm_pair = []() {
 template <bool A_MN, bool B_MN, int EPI>
 static int run_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, GemmParams p, cudaStream_t st,
                     int kind_bit = 7) {
-  p.pf_dist = g_gemm_pf_dist; p.pf_mask = g_gemm_pf_mask; p.probe = g_gemm_probe; p.dry = g_gemm_dry;
+  p.probe = g_gemm_probe; p.dry = g_gemm_dry;
   if (g_gemm_pair & kind_bit) return launch_gemm2<A_MN, B_MN, EPI>(A, lda, B, ldb, p, st);
   return launch_gemm<A_MN, B_MN, EPI>(A, lda, B, ldb, p, st);
 }
@@ -322,26 +315,30 @@ int hilda_flce_grad_weight(const void* dlogits, const void* hidden, float* dw32,
 // Default rows per chunk. The scratch [chunk, pitch(V)] is kept at or below 1.25 GiB (about a
 // quarter of the full logits at the 16384 x 128256 benchmark shape). Within [half of that, that]
 // the chunk is chosen so that the d(hidden) GEMM, the one with few output tiles
-// (chunk/128 x H/256), fills whole waves of SMs: e.g. 37 x 16 = 592 tiles = 4 x 148.
+// (chunk/256 x H/256 on CTA pairs, chunk/128 x H/256 on single CTAs), fills whole waves: e.g.
+// 4608 rows = 18 x 16 = 288 pair tiles, just under 4 x 74.
 int64_t hilda_flce_default_chunk_rows(int64_t BT, int64_t H, int64_t V) {
+  // the d(hidden) GEMM's tile height and the number of units that run tiles at a time
+  const bool pair = (g_gemm_pair & 2) != 0;
+  const int64_t tile_rows = pair ? 2 * BM : BM;
+  const int64_t units = pair ? 148 / 2 : 148;
   const int64_t pitch = round_up(V > 0 ? V : 1, BN);
   int64_t cap = (((int64_t)5 << 28)) / (pitch * 2);
-  cap = cap / BM * BM;
-  if (cap < BM) cap = BM;
+  cap = cap / tile_rows * tile_rows;
+  if (cap < tile_rows) cap = tile_rows;
   if (BT <= cap) return BT > 0 ? BT : 1;
   const int64_t n_tiles = (H + BN - 1) / BN;
-  const int64_t sms = 148;
   int64_t best = cap;
   double best_eff = -1.0;
-  for (int64_t c = cap; c >= cap / 2 && c >= BM; c -= BM) {
+  for (int64_t c = cap; c >= cap / 2 && c >= tile_rows; c -= tile_rows) {
     int64_t waves = 0, tiles = 0;
     for (int64_t r0 = 0; r0 < BT; r0 += c) {
       const int64_t rows = (BT - r0 < c) ? BT - r0 : c;
-      const int64_t t = ((rows + BM - 1) / BM) * n_tiles;
+      const int64_t t = ((rows + tile_rows - 1) / tile_rows) * n_tiles;
       tiles += t;
-      waves += (t + sms - 1) / sms;
+      waves += (t + units - 1) / units;
     }
-    const double eff = (double)tiles / (double)(waves * sms);
+    const double eff = (double)tiles / (double)(waves * units);
     if (eff > best_eff + 1e-9) { best_eff = eff; best = c; }
   }
   return best;
@@ -498,9 +495,7 @@ int hilda_scatter_rows(const void* src, const int64_t* idx, void* dst, int64_t n
 // Select the GEMM variant per use: bit 0 = logits, bit 1 = d(hidden), bit 2 = d(W) run on CTA pairs
 // (cta_group::2, 256 x 256 tiles); a clear bit = single CTAs. hilda_debug_gemm uses pairs if any bit is set.
 void hilda_gemm_set_pair(int mask) { g_gemm_pair = mask & 7; }
-// Tuning hooks: L2 prefetch lookahead (k-blocks; mask bit 0 = A, bit 1 = B) of the single-CTA
-// kernel, and the tile walk order used by hilda_debug_gemm (1 = M first, 0 = N first).
-void hilda_gemm_set_prefetch(int dist, int mask) { g_gemm_pf_dist = dist < 0 ? 0 : dist; g_gemm_pf_mask = mask & 3; }
+// Tile walk order used by hilda_debug_gemm (1 = M first, 0 = N first).
 void hilda_debug_gemm_set_order(int m_fast) { g_debug_mfast = m_fast ? 1 : 0; }
 // Cycle counters of the single-CTA GEMM's role loops: device buffer of [sm_count][8] int64
 // {producer wait-for-slot, producer total, issuer wait-for-data, issuer wait-for-accumulator,

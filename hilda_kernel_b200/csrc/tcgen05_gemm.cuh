@@ -21,7 +21,7 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int GEMM_SMEM_BYTES = GEMM_STAGES * STAGE_BYTES + 1024;  // + slack for 1024-byte alignment
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 224;  // warp 0: TMA of A, warp 1: MMA, warps 2-5: epilogue, warp 6: TMA of B
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t WAIT_CAP = 1u << 22;  // bounded spin: try_wait attempts before giving up
 
@@ -44,10 +44,6 @@ struct GemmParams {
   float2* stats; int64_t stats_ld;
   int* status;       // device word; non-zero = a bounded wait ran out
   uint32_t mn_lbo, mn_sbo;  // descriptor byte offsets for MN-major operands (8192, 1024)
-  int pf_dist;       // L2 prefetch lookahead of the TMA producer in k-blocks (0 = off)
-  int pf_mask;       // bit 0: prefetch A, bit 1: prefetch B
-  int pf_a_div, pf_b_div;  // CTAs that stream the same A / B slab at the same time: they share the
-                           // prefetch duty, each taking the k-blocks congruent to its own rank
   long long* probe;  // optional [gridDim.x][8] cycle counters of the role loops (null = off)
   int dry;           // measurement only: the producer signals "full" without loading (results are garbage)
 };
@@ -92,10 +88,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tma
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1) : "memory");
-}
-// Bring one box of a tensor map into L2 only (no shared-memory destination, no barrier).
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* tmap, int c0, int c1) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(c0), "r"(c1) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
@@ -344,68 +336,56 @@ tcgen05_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   const int total_tiles = p.m_tiles * p.n_tiles;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+  if (warp == 0 || warp == 6) {
+    // ------------------------------------------------------------------ TMA producers
+    // Warp 0 copies operand A and posts the expect-tx arrive, warp 6 copies operand B: two
+    // threads issue a slot's copies side by side. The ring is latency-bound (slot freed -> copy
+    // issued -> data landed -> MMA), so nothing sits between the wait for a free slot and the
+    // copies but the copies themselves: addresses and coordinates are ready before the wait, and
+    // the expect-tx arrive follows the copies (the transaction count may run negative until then).
     if (lane == 0) {
+      const bool is_a = warp == 0;
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       long long w_empty = 0;
       const long long t_begin = clock64();
+      const bool probing = p.probe != nullptr, dry = p.dry != 0;
+      const int k_blocks = p.k_blocks;
+      const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int mt = p.m_fast ? tile % p.m_tiles : tile / p.n_tiles;
         const int nt = p.m_fast ? tile / p.m_tiles : tile % p.n_tiles;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (p.pf_dist > 0) {
-            // L2 lookahead: the boxes pf_dist k-blocks from now (in this tile or the next one this
-            // CTA owns). CTAs streaming the same slab split the duty, so each box is requested once
-            // and the shared-memory ring only ever waits on L2 latency, not on DRAM.
-            int pk = kb + p.pf_dist, ptile = tile;
-            if (pk >= p.k_blocks) { pk -= p.k_blocks; ptile += gridDim.x; }
-            if (ptile < total_tiles && pk < p.k_blocks) {
-              const int pmt = p.m_fast ? ptile % p.m_tiles : ptile / p.n_tiles;
-              const int pnt = p.m_fast ? ptile / p.m_tiles : ptile % p.n_tiles;
-              if ((p.pf_mask & 1) && pk % p.pf_a_div == pnt % p.pf_a_div) {
-                if constexpr (!A_MN) {
-                  tma_prefetch_2d(&tmA, pk * BK, pmt * BM);
-                } else {
-#pragma unroll
-                  for (int j = 0; j < BM / 64; ++j) tma_prefetch_2d(&tmA, pmt * BM + j * 64, pk * BK);
-                }
-              }
-              if ((p.pf_mask & 2) && pk % p.pf_b_div == pmt % p.pf_b_div) {
-                if constexpr (!B_MN) {
-                  tma_prefetch_2d(&tmB, pk * BK, pnt * BN);
-                } else {
-#pragma unroll
-                  for (int j = 0; j < BN / 64; ++j) tma_prefetch_2d(&tmB, pnt * BN + j * 64, pk * BK);
-                }
-              }
-            }
-          }
-          const long long t0 = p.probe ? clock64() : 0;
-          if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abortp, p.status, 1)) { ok = false; break; }
-          if (p.probe) w_empty += clock64() - t0;
-          const uint32_t fb = smem_u32(&full_bar[stage]);
+        const int m0 = mt * BM, n0 = nt * BN;
+        for (int kb = 0, kc = 0; kb < k_blocks; ++kb, kc += BK) {
+          const uint32_t fb = full0 + stage * 8u, eb = empty0 + stage * 8u;
           const uint32_t sA = stage_base + stage * STAGE_BYTES;
           const uint32_t sB = sA + A_STAGE_BYTES;
-          if (p.dry) { mbar_arrive(fb); if (++stage == GEMM_STAGES) { stage = 0; phase ^= 1u; } continue; }
-          mbar_expect_tx(fb, STAGE_BYTES);
-          if constexpr (!A_MN) {
-            tma_load_2d(sA, &tmA, fb, kb * BK, mt * BM);
-          } else {
-#pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sA + j * 8192, &tmA, fb, mt * BM + j * 64, kb * BK);
-          }
-          if constexpr (!B_MN) {
-            tma_load_2d(sB, &tmB, fb, kb * BK, nt * BN);
-          } else {
-#pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sB + j * 8192, &tmB, fb, nt * BN + j * 64, kb * BK);
-          }
+          const uint32_t want = phase ^ 1u;
           if (++stage == GEMM_STAGES) { stage = 0; phase ^= 1u; }
+          const long long t0 = probing ? clock64() : 0;
+          if (!mbar_wait(eb, want, abortp, p.status, 1)) { ok = false; break; }
+          if (probing) w_empty += clock64() - t0;
+          if (is_a) {
+            if (dry) { mbar_arrive(fb); continue; }
+            if constexpr (!A_MN) {
+              tma_load_2d(sA, &tmA, fb, kc, m0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j) tma_load_2d(sA + j * 8192, &tmA, fb, m0 + j * 64, kc);
+            }
+            mbar_expect_tx(fb, STAGE_BYTES);
+          } else {
+            if (dry) continue;
+            if constexpr (!B_MN) {
+              tma_load_2d(sB, &tmB, fb, kc, n0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j) tma_load_2d(sB + j * 8192, &tmB, fb, n0 + j * 64, kc);
+            }
+          }
         }
       }
-      if (p.probe) { p.probe[blockIdx.x * 8 + 0] = w_empty; p.probe[blockIdx.x * 8 + 1] = clock64() - t_begin; }
+      if (probing && is_a) { p.probe[blockIdx.x * 8 + 0] = w_empty; p.probe[blockIdx.x * 8 + 1] = clock64() - t_begin; }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
@@ -541,21 +521,6 @@ static inline uint32_t make_idesc(int is_bf16, bool a_mn, bool b_mn) {
 // C[M,N] = A x B with A given as [M,K] (K-major, a_mn=false) or stored [K,M] (MN-major, a_mn=true),
 // B given as [N,K] (K-major) or stored [K,N] (MN-major). lda/ldb are row pitches in elements of the
 // STORED matrices.
-// How many of the `concurrent` CTAs (or CTA pairs) stream the same A slab / B slab at a time,
-// given the tile walk order: they split the L2 prefetch duty among themselves.
-static inline void gemm_prefetch_duty(GemmParams& p, int concurrent) {
-  auto clampdiv = [](int v) { return v < 1 ? 1 : v; };
-  if (p.m_fast) {
-    p.pf_b_div = clampdiv(p.m_tiles < concurrent ? p.m_tiles : concurrent);
-    p.pf_a_div = clampdiv(concurrent / clampdiv(p.m_tiles));
-    if (p.pf_a_div > p.n_tiles) p.pf_a_div = clampdiv(p.n_tiles);
-  } else {
-    p.pf_a_div = clampdiv(p.n_tiles < concurrent ? p.n_tiles : concurrent);
-    p.pf_b_div = clampdiv(concurrent / clampdiv(p.n_tiles));
-    if (p.pf_b_div > p.m_tiles) p.pf_b_div = clampdiv(p.m_tiles);
-  }
-}
-
 template <bool A_MN, bool B_MN, int EPI>
 static int launch_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, GemmParams p, cudaStream_t st) {
   if (p.M <= 0 || p.N <= 0 || p.K <= 0) return HILDA_ERR_SIZE;
@@ -579,7 +544,6 @@ static int launch_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, G
   if (tiles > 0x7fffffffLL) return HILDA_ERR_SIZE;
   int grid = sm_count();
   if (tiles < grid) grid = (int)tiles;
-  gemm_prefetch_duty(p, grid);
   kern<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(tmA, tmB, p);
   HILDA_LAUNCH_CHECK();
   return HILDA_OK;

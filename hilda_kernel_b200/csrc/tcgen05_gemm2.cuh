@@ -143,75 +143,59 @@ tcgen05_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 
   const int total_tiles = p.m_tiles * p.n_tiles;  // m_tiles counts 256-row tiles here
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer (both CTAs)
+  if (warp == 0 || warp == 6) {
+    // ------------------------------------------------------------------ TMA producers (both CTAs)
+    // as in the single-CTA kernel: warp 0 copies this CTA's half of A (and, in the leader, posts
+    // the expect-tx arrive for both CTAs' bytes), warp 6 copies its half of B; nothing sits
+    // between the wait for a free slot and the copies
     if (lane == 0) {
+      const bool is_a = warp == 0;
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       long long w_empty = 0;
       const long long t_begin = clock64();
+      const bool probing = p.probe != nullptr, dry = p.dry != 0;
+      const int k_blocks = p.k_blocks;
+      const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
+      const uint32_t full0_leader = g2_map_rank(full0, 0);  // the leader's barriers, 8 bytes apart like ours
       for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
         const int mt = p.m_fast ? tile % p.m_tiles : tile / p.n_tiles;
         const int nt = p.m_fast ? tile / p.m_tiles : tile % p.n_tiles;
         const int m0 = mt * (2 * BM) + (int)rank * BM;        // this CTA's 128 rows of A
         const int n0 = nt * BN + (int)rank * G2_B_ROWS;        // this CTA's 128 columns of B
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (p.pf_dist > 0) {
-            // L2 lookahead, duty shared among the pairs that stream the same slab (see the
-            // single-CTA kernel); each CTA of the pair looks after its own halves
-            int pk = kb + p.pf_dist, ptile = tile;
-            if (pk >= p.k_blocks) { pk -= p.k_blocks; ptile += n_pairs; }
-            if (ptile < total_tiles && pk < p.k_blocks) {
-              const int pmt = p.m_fast ? ptile % p.m_tiles : ptile / p.n_tiles;
-              const int pnt = p.m_fast ? ptile / p.m_tiles : ptile % p.n_tiles;
-              const int pm0 = pmt * (2 * BM) + (int)rank * BM, pn0 = pnt * BN + (int)rank * G2_B_ROWS;
-              if ((p.pf_mask & 1) && pk % p.pf_a_div == pnt % p.pf_a_div) {
-                if constexpr (!A_MN) {
-                  tma_prefetch_2d(&tmA, pk * BK, pm0);
-                } else {
-#pragma unroll
-                  for (int j = 0; j < BM / 64; ++j) tma_prefetch_2d(&tmA, pm0 + j * 64, pk * BK);
-                }
-              }
-              if ((p.pf_mask & 2) && pk % p.pf_b_div == pmt % p.pf_b_div) {
-                if constexpr (!B_MN) {
-                  tma_prefetch_2d(&tmB, pk * BK, pn0);
-                } else {
-#pragma unroll
-                  for (int j = 0; j < G2_B_ROWS / 64; ++j) tma_prefetch_2d(&tmB, pn0 + j * 64, pk * BK);
-                }
-              }
-            }
-          }
-          const long long t0 = p.probe ? clock64() : 0;
-          if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abortp, p.status, 21)) { ok = false; break; }
-          if (p.probe) w_empty += clock64() - t0;
-          const uint32_t fb_local = smem_u32(&full_bar[stage]);
-          const uint32_t fb = g2_map_rank(fb_local, 0);  // the leader's barrier
+        for (int kb = 0, kc = 0; kb < k_blocks; ++kb, kc += BK) {
+          const uint32_t fb_local = full0 + stage * 8u, fb = full0_leader + stage * 8u, eb = empty0 + stage * 8u;
           const uint32_t sA = stage_base + stage * G2_STAGE_BYTES;
           const uint32_t sB = sA + G2_A_BYTES;
-          if (p.dry) {
-            if (leader) mbar_arrive(fb_local);
-            if (++stage == G2_STAGES) { stage = 0; phase ^= 1u; }
-            continue;
-          }
-          if (leader) mbar_expect_tx(fb_local, 2 * G2_STAGE_BYTES);
-          if constexpr (!A_MN) {
-            g2_tma_load_2d(sA, &tmA, fb, kb * BK, m0);
-          } else {
-#pragma unroll
-            for (int j = 0; j < BM / 64; ++j) g2_tma_load_2d(sA + j * 8192, &tmA, fb, m0 + j * 64, kb * BK);
-          }
-          if constexpr (!B_MN) {
-            g2_tma_load_2d(sB, &tmB, fb, kb * BK, n0);
-          } else {
-#pragma unroll
-            for (int j = 0; j < G2_B_ROWS / 64; ++j) g2_tma_load_2d(sB + j * 8192, &tmB, fb, n0 + j * 64, kb * BK);
-          }
+          const uint32_t want = phase ^ 1u;
           if (++stage == G2_STAGES) { stage = 0; phase ^= 1u; }
+          const long long t0 = probing ? clock64() : 0;
+          if (!mbar_wait(eb, want, abortp, p.status, 21)) { ok = false; break; }
+          if (probing) w_empty += clock64() - t0;
+          if (is_a) {
+            if (dry) {
+              if (leader) mbar_arrive(fb_local);
+              continue;
+            }
+            if constexpr (!A_MN) {
+              g2_tma_load_2d(sA, &tmA, fb, kc, m0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j) g2_tma_load_2d(sA + j * 8192, &tmA, fb, m0 + j * 64, kc);
+            }
+            if (leader) mbar_expect_tx(fb_local, 2 * G2_STAGE_BYTES);
+          } else {
+            if (dry) continue;
+            if constexpr (!B_MN) {
+              g2_tma_load_2d(sB, &tmB, fb, kc, n0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < G2_B_ROWS / 64; ++j) g2_tma_load_2d(sB + j * 8192, &tmB, fb, n0 + j * 64, kc);
+            }
+          }
         }
       }
-      if (p.probe && leader) { p.probe[pair * 8 + 0] = w_empty; p.probe[pair * 8 + 1] = clock64() - t_begin; }
+      if (probing && leader && is_a) { p.probe[pair * 8 + 0] = w_empty; p.probe[pair * 8 + 1] = clock64() - t_begin; }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
@@ -325,7 +309,6 @@ static int launch_gemm2(const void* A, int64_t lda, const void* B, int64_t ldb, 
   if (tiles > 0x7fffffffLL) return HILDA_ERR_SIZE;
   int pairs = sm_count() / 2;
   if (tiles < pairs) pairs = (int)tiles;
-  gemm_prefetch_duty(p, pairs);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(pairs * 2), 1, 1);
   cfg.blockDim = dim3(GEMM_THREADS, 1, 1);

@@ -8,6 +8,8 @@ rescales them when the upstream gradient is not 1. The three GEMMs run on one ha
 tcgen05/TMEM kernel; the logsumexp statistics come out of the first GEMM's epilogue.
 Supported compute dtypes: bfloat16 and float16 (the tensor-core path); hidden dim multiple of 8.
 """
+import os
+
 import torch
 
 from .. import _lib as L
@@ -15,8 +17,9 @@ from .._lib import device_guard
 
 _RED = {"none": 0, "mean": 1, "sum": 2}
 
-# Rows per chunk; None lets the library choose (scratch <= 1 GiB). Exposed for tests and tuning.
-CHUNK_ROWS = None
+# Rows per chunk; None lets the library choose (scratch <= 1.25 GiB). Exposed for tests and tuning
+# (environment HILDA_FLCE_CHUNK_ROWS sets the initial value).
+CHUNK_ROWS = int(os.environ["HILDA_FLCE_CHUNK_ROWS"]) if os.environ.get("HILDA_FLCE_CHUNK_ROWS") else None
 # Set True to synchronise after each call and raise if a device-side bounded wait ran out.
 CHECK_STATUS = False
 # Ignored tokens contribute nothing to the loss or to either gradient, so by default their rows are

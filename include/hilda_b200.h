@@ -184,12 +184,9 @@ int hilda_scatter_rows(const void* src, const int64_t* idx, void* dst, int64_t n
  * pairs when any bit is set. Initial value: environment HILDA_GEMM_PAIR, else the built-in default. */
 void hilda_gemm_set_pair(int mask);
 int hilda_gemm_get_pair(void);
-/* Tuning hooks (no counterpart in the reference): L2 prefetch lookahead of the single-CTA GEMM's
- * TMA producer in k-blocks (0 = off; mask bit 0 = operand A, bit 1 = operand B), and the tile walk
- * order hilda_debug_gemm uses (1 = M first, 0 = N first). */
-void hilda_gemm_set_prefetch(int dist, int mask);
+/* Tile walk order hilda_debug_gemm uses (1 = M first, 0 = N first); no counterpart in the reference. */
 void hilda_debug_gemm_set_order(int m_fast);
-/* Cycle counters of the single-CTA GEMM's role loops, written by every launch while set: device
+/* Cycle counters of the GEMM kernels' role loops, written by every launch while set: device
  * buffer of [SM count][8] int64 {producer wait-for-slot, producer total, issuer wait-for-data,
  * issuer wait-for-accumulator, issuer total, epilogue wait-for-accumulator, epilogue busy, 0};
  * NULL switches it off (the default). dry != 0 is for measurement only (results are garbage): the

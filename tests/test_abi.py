@@ -42,7 +42,14 @@ def test_size_queries_need_no_gpu(libpath):
     assert lib.hilda_flce_logits_pitch(16032) == 16128
     assert lib.hilda_flce_padded_rows(100) == 256
     assert lib.hilda_flce_stat_tiles(128256) == 501
-    assert lib.hilda_flce_default_chunk_rows(16384, 4096, 128256) == 4736  # 37 x 16 tiles = 4 waves of 148 SMs
+    default = lib.hilda_gemm_get_pair()
+    try:
+        lib.hilda_gemm_set_pair(0)
+        assert lib.hilda_flce_default_chunk_rows(16384, 4096, 128256) == 4736  # 37 x 16 tiles = 4 waves of 148 SMs
+        lib.hilda_gemm_set_pair(7)
+        assert lib.hilda_flce_default_chunk_rows(16384, 4096, 128256) == 4608  # 18 x 16 pair tiles <= 4 waves of 74
+    finally:
+        lib.hilda_gemm_set_pair(default)
     assert lib.hilda_flce_default_chunk_rows(100, 64, 1000) == 100
     assert lib.hilda_flce_default_chunk_rows(4096, 4096, 128256) == 4096
     one = lib.hilda_flce_workspace_bytes(4096, 4096, 128256, 4096, 1)

@@ -376,6 +376,96 @@ def sharded_ops_table(device, world, pk):
     return out
 
 
+def gemm_roles_table(device):
+    """--gemm-roles: the three FLCE GEMM shapes of one row chunk, each run back to back for about a
+    second (the power-capped regime a long step sees) through the plain-GEMM hook of the library, as
+    single CTAs and as CTA pairs, with the kernels' own cycle counters switched on: cycles of the MMA
+    issuer per k-block (4 MMAs of 128 cycles = 512 is the tensor pipe's own rate), the share of its
+    time spent waiting for operands or for a free accumulator, and the same with the memory system
+    taken out ("dry": slots are marked full without copying; results are garbage). cuBLAS (torch.mm)
+    on the same operands is timed the same way beside them. Prints one JSON line."""
+    import hilda_kernel_b200._lib as L
+    lib = L.lib()
+    R = int(lib.hilda_flce_default_chunk_rows(BT, H, V))
+    g = torch.Generator(device=device).manual_seed(11)
+    rn = lambda *s: torch.randn(*s, device=device, generator=g)
+    hid, W = rn(R, H).bfloat16(), (0.02 * rn(V, H)).bfloat16()
+    dlog = (0.01 * rn(R, V)).bfloat16()
+    out = {1: torch.empty(R, V, device=device, dtype=torch.bfloat16),
+           2: torch.empty(R, H, device=device, dtype=torch.bfloat16),
+           3: torch.empty(V, H, device=device, dtype=torch.bfloat16)}
+    status = torch.zeros(4, dtype=torch.int32, device=device)
+    n_units = torch.cuda.get_device_properties(device).multi_processor_count
+    probe = torch.zeros(n_units, 8, dtype=torch.int64, device=device)
+    st = L.stream(device)
+    names = {1: "logits = hidden x W^T (K-major, K-major)", 2: "d_hidden = dlogits x W (K-major, MN-major)",
+             3: "d_W = dlogits^T x hidden (MN-major, MN-major)"}
+    kblocks = {1: H // 64, 2: -(-V // 64), 3: -(-R // 64)}
+
+    def ours(kind):
+        if kind == 1:
+            lib.hilda_debug_gemm_set_order(1)
+            return lib.hilda_debug_gemm(hid.data_ptr(), H, W.data_ptr(), H, out[1].data_ptr(), None, V, R, V, H, 0, 0, 1,
+                                        0, 0, status.data_ptr(), st)
+        if kind == 2:
+            lib.hilda_debug_gemm_set_order(1)
+            return lib.hilda_debug_gemm(dlog.data_ptr(), V, W.data_ptr(), H, out[2].data_ptr(), None, H, R, H, V, 0, 1, 1,
+                                        0, 0, status.data_ptr(), st)
+        lib.hilda_debug_gemm_set_order(0)
+        return lib.hilda_debug_gemm(dlog.data_ptr(), V, hid.data_ptr(), H, out[3].data_ptr(), None, H, V, H, R, 1, 1, 1,
+                                    0, 0, status.data_ptr(), st)
+
+    def cublas(kind):
+        if kind == 1:
+            torch.mm(hid, W.t(), out=out[1])
+        elif kind == 2:
+            torch.mm(dlog, W, out=out[2])
+        else:
+            torch.mm(dlog.t(), hid, out=out[3])
+
+    def sustained(fn, secs=1.0):
+        fn(); torch.cuda.synchronize()
+        t0 = time.perf_counter(); fn(); torch.cuda.synchronize()
+        n = max(5, int(secs / max(time.perf_counter() - t0, 1e-4)))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    flops = 2.0 * R * H * V
+    default_pair = lib.hilda_gemm_get_pair()
+    table = {}
+    try:
+        for kind in (1, 2, 3):
+            row = {"cublas_TFLOPs": round(flops / sustained(lambda: cublas(kind)) / 1e9, 1)}
+            for pair in (0, 7):
+                units = n_units // 2 if pair else n_units
+                m_tiles = -(-(V if kind == 3 else R) // (256 if pair else 128))
+                n_tiles = -(-(V if kind == 1 else H) // 256)
+                kb_per_unit = m_tiles * n_tiles / units * kblocks[kind]
+                for dry in (0, 1):
+                    lib.hilda_gemm_set_pair(pair)
+                    lib.hilda_gemm_set_probe(None, dry)
+                    ms = sustained(lambda: ours(kind))
+                    lib.hilda_gemm_set_probe(probe.data_ptr(), dry); probe.zero_()
+                    ours(kind); torch.cuda.synchronize()
+                    lib.hilda_gemm_set_probe(None, 0)
+                    c = probe[:units].double().mean(0).tolist()
+                    row[("pair" if pair else "single") + ("_dry" if dry else "")] = {
+                        "TFLOPs": round(flops / ms / 1e9, 1), "issuer_cycles_per_kblock": round(c[4] / kb_per_unit, 1),
+                        "issuer_wait_operands": round(c[2] / c[4], 3), "issuer_wait_accumulator": round(c[3] / c[4], 3),
+                        "producer_wait_slot": round(c[0] / max(c[1], 1.0), 3),
+                        "epilogue_cycles_per_tile": round(c[6] / (m_tiles * n_tiles / units))}
+            table[names[kind]] = row
+    finally:
+        lib.hilda_gemm_set_pair(default_pair)
+        lib.hilda_gemm_set_probe(None, 0)
+    EMIT(json.dumps({"gemm_roles": table, "chunk_rows": R, "H": H, "V": V, "status": int(status[0]),
+                     "ideal_issuer_cycles_per_kblock": 512}))
+
+
 def run_ours(args):
     world, rank, local = dist_env()
     if not torch.cuda.is_available():
@@ -572,10 +662,15 @@ def main():
                     help="run the GEMMs over ignored tokens too (default: their rows are compacted away)")
     ap.add_argument("--only-op", default=None, help="time one operator of the per-op table and exit")
     ap.add_argument("--small", action="store_true", help="with --only-op: 1/8 of the rows (profiler captures)")
+    ap.add_argument("--gemm-roles", action="store_true",
+                    help="cycle counters of the tcgen05 GEMM roles on the FLCE shapes, beside cuBLAS, and exit")
     args = ap.parse_args()
     BT, V, H = args.bt, args.vocab, args.hidden
     EMIT = _protect_stdout()
-    if args.impl == "reference":
+    if args.gemm_roles:
+        torch.cuda.set_device(0)
+        gemm_roles_table(torch.device("cuda", 0))
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -289,21 +289,51 @@ def per_op_table(device, pk, only=None, small=False):
             (nvalid + n) * v * 2, n)
         del logits
     # config 5: GRPO bf16 logits [16, 1024, 151936] (L = 1023), beta 0.1
-    if not want("grpo"):
-        return out
-    B, Lc, v = 16 // div, 1023, 151936
-    logits = (2 * rn(B, Lc + 1, v)).bfloat16()
-    ids = torch.randint(0, v, (B, Lc), device=device, generator=g)
-    adv = rn(B)
-    lens = torch.randint(256, 1025, (B,), device=device, generator=g).clamp(max=Lc)
-    mask = (torch.arange(Lc, device=device)[None] < lens[:, None]).int()
-    cur = GR.fused_selective_log_softmax(logits, ids)
-    old, ref = cur + 0.05 * rn(B, Lc), cur + 0.1 * rn(B, Lc)
-    A = int(mask.sum())
-    add("grpo_bf16_fwd+bwd", timed(lambda: GR.grpo_loss_forward(logits, ids, adv, old, ref, mask, 1.0, 0.1, 0.2, 0.2, True),
-                                   iters=4),
-        (A + B * (Lc + 1)) * v * 2, B * Lc)
-    out["grpo_bf16_fwd+bwd"]["active_tokens"] = A
+    if want("grpo"):
+        B, Lc, v = 16 // div, 1023, 151936
+        logits = (2 * rn(B, Lc + 1, v)).bfloat16()
+        ids = torch.randint(0, v, (B, Lc), device=device, generator=g)
+        adv = rn(B)
+        lens = torch.randint(256, 1025, (B,), device=device, generator=g).clamp(max=Lc)
+        mask = (torch.arange(Lc, device=device)[None] < lens[:, None]).int()
+        cur = GR.fused_selective_log_softmax(logits, ids)
+        old, ref = cur + 0.05 * rn(B, Lc), cur + 0.1 * rn(B, Lc)
+        A = int(mask.sum())
+        add("grpo_bf16_fwd+bwd", timed(lambda: GR.grpo_loss_forward(logits, ids, adv, old, ref, mask, 1.0, 0.1, 0.2, 0.2, True),
+                                       iters=4),
+            (A + B * (Lc + 1)) * v * 2, B * Lc)
+        out["grpo_bf16_fwd+bwd"]["active_tokens"] = A
+    # ---- the divergence losses (reference bench shapes: bench_kl_div.py:158, bench_jsd.py:175,
+    # bench_fused_linear_jsd.py:165, in bf16)
+    if want("kl_div"):
+        from hilda_kernel_b200.kernels.kl_div import kl_div_backward, kl_div_forward
+        n, v = 8192 // div, 128256
+        sets = [(rn(n, v).log_softmax(-1).bfloat16(), rn(n, v).softmax(-1).bfloat16()) for _ in range(2)]
+        one = torch.ones((), device=device)
+        add("kl_div_bf16_fwd+bwd",
+            timed2([(lambda yp=yp, yt=yt: kl_div_forward(yp, yt)) for yp, yt in sets],
+                   [(lambda yt=yt: kl_div_backward(yt, one)) for _, yt in sets]),
+            4 * n * v * 2, n)  # forward reads y_pred and y_true; backward reads y_true, writes dy_pred
+        del sets
+    if want("jsd_bf16"):
+        from hilda_kernel_b200.kernels.jsd import jsd_forward
+        n, v = 4096 // div, 128256
+        sets = [(rn(n, v).log_softmax(-1).bfloat16(), rn(n, v).log_softmax(-1).bfloat16()) for _ in range(2)]
+        add("jsd_bf16_fwd+bwd", timed([(lambda x=x, y=y: jsd_forward(x, y, 0.5)) for x, y in sets]),
+            3 * n * v * 2, n)  # one pass: read X and Y, write dX
+        del sets
+    if want("fused_linear_jsd"):
+        from hilda_kernel_b200.kernels.fused_linear_jsd import fused_linear_jsd_forward
+        n, h, v = 2048 // div, 4096, 128256
+        si, sw = (0.02 * rn(n, h)).bfloat16(), (0.02 * rn(v, h)).bfloat16()
+        ti, tw = (0.02 * rn(n, h)).bfloat16(), (0.02 * rn(v, h)).bfloat16()
+        ms = timed(lambda: fused_linear_jsd_forward(si, sw, ti, tw, None, 0.5, 1.0), iters=3)
+        flops = 8.0 * n * h * v  # two logits GEMMs, d input, d weight
+        out["fused_linear_jsd_bf16_fwd+bwd"] = {
+            "us": round(ms * 1e3, 1), "TFLOP/s": round(flops / ms / 1e9, 1),
+            "frac_of_measured_bf16_sustained": round(flops / ms / 1e9 / pk["tf_sustained"], 3),
+            "tokens/s": round(n / (ms * 1e-3))}
+        del si, sw, ti, tw
     return out
 
 

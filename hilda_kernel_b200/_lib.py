@@ -48,6 +48,11 @@ SIGNATURES = {
     "hilda_flce_padded_rows": (_i64, [_i64]),
     "hilda_flce_stat_tiles": (_i64, [_i64]),
     "hilda_flce_logits": (_i32, [_p, _p, _p, _p, _i64, _i64, _i64, _i32, _p, _p]),
+    "hilda_flce_logits_scaled": (_i32, [_p, _p, _p, _p, _i64, _i64, _i64, _f32, _i32, _p, _p]),
+    "hilda_kl_div_fwd": (_i32, [_p, _p, _p, _p, _i64, _i64, _i32, _i32, _f32, _i32, _p]),
+    "hilda_kl_div_bwd": (_i32, [_p, _p, _p, _i64, _i64, _i32, _i32, _i32, _p]),
+    "hilda_jsd_fwd": (_i32, [_p, _p, _p, _p, _p, _p, _i64, _p, _i64, _i64, _f32, _i32, _p]),
+    "hilda_fljsd_dlogits": (_i32, [_p, _p, _p, _p, _p, _i64, _p, _i64, _p, _i64, _i64, _f32, _f32, _i32, _p]),
     "hilda_flce_row_stats": (_i32, [_p, _p, _p, _p, _i64, _i64, _i64, _i32, _p]),
     "hilda_flce_finalize": (_i32, [_p, _p, _i64, _p, _p, _i64, _p]),
     "hilda_flce_dlogits": (_i32, [_p, _p, _p, _i64, _p, _i64, _i64, _i64, _i32, _p]),

@@ -42,7 +42,7 @@ flce_row_stats_kernel(const float2* __restrict__ stats, int64_t stats_ld, int n_
   }
   s = warp_sum(s);
   if (lane == 0) {
-    const int64_t t = targets[row] - vocab_start;
+    const int64_t t = targets ? targets[row] - vocab_start : -1;
     float xt = 0.f;
     if (t >= 0 && t < V) {
       const uint16_t raw = logits[row * pitch + t];
@@ -174,8 +174,9 @@ struct ProfScope {
 };
 
 static int flce_logits(const void* hidden, const void* W, void* logits, float* stats, int64_t rows, int64_t H,
-                       int64_t V, int is_bf16, int* status, cudaStream_t st) {
+                       int64_t V, int is_bf16, int* status, cudaStream_t st, float inv_temperature = 1.0f) {
   GemmParams p = {};
+  p.stat_scale = FL_LOG2E * inv_temperature;
   p.M = (int)rows; p.N = (int)V; p.K = (int)H; p.m_fast = 1; p.is_bf16 = is_bf16;
   p.C16 = logits; p.ldc16 = round_up(V, BN);
   p.stats = reinterpret_cast<float2*>(stats); p.stats_ld = (V + BN - 1) / BN;
@@ -248,9 +249,22 @@ int hilda_flce_logits(const void* hidden, const void* W, void* logits, float* st
   return flce_logits(hidden, W, logits, stats, rows, H, V, dtype == HILDA_BF16, status, (cudaStream_t)stream);
 }
 
+// The same GEMM with the epilogue statistics taken of logits * inv_temperature (the stored logits are
+// unscaled): the log-softmax at a temperature of the fused linear + JSD loss
+// (kernels/fused_linear_jsd.py:46-62).
+int hilda_flce_logits_scaled(const void* hidden, const void* W, void* logits, float* stats, int64_t rows, int64_t H,
+                             int64_t V, float inv_temperature, int dtype, int* status, void* stream) {
+  if (!hidden || !W || !logits || !stats) return HILDA_ERR_NULL;
+  if (!(inv_temperature > 0.f)) return HILDA_ERR_ARG;
+  int rc = flce_check(rows, H, V, dtype);
+  if (rc) return rc;
+  return flce_logits(hidden, W, logits, stats, rows, H, V, dtype == HILDA_BF16, status, (cudaStream_t)stream,
+                     inv_temperature);
+}
+
 int hilda_flce_row_stats(const float* stats, const void* logits, const int64_t* targets, float* rowstat, int64_t rows,
                          int64_t V, int64_t vocab_start, int dtype, void* stream) {
-  if (!stats || !logits || !targets || !rowstat) return HILDA_ERR_NULL;
+  if (!stats || !logits || !rowstat) return HILDA_ERR_NULL;  // targets == null: no target logit (rowstat[2] = 0)
   if (rows <= 0) return HILDA_OK;
   const int n_tiles = (int)((V + BN - 1) / BN);
   flce_row_stats_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, (cudaStream_t)stream>>>(

@@ -42,6 +42,7 @@ struct GemmParams {
   void* C16; int64_t ldc16;
   float* C32; int64_t ldc32;
   float2* stats; int64_t stats_ld;
+  float stat_scale;  // EPI_LOGITS_STATS: factor on the rounded logits before the base-2 (max, sum-exp)
   int* status;       // device word; non-zero = a bounded wait ran out
   uint32_t mn_lbo, mn_sbo;  // descriptor byte offsets for MN-major operands (8192, 1024)
   long long* probe;  // optional [gridDim.x][8] cycle counters of the role loops (null = off)
@@ -219,6 +220,7 @@ __device__ __forceinline__ float ex2_fast(float x) {
 template <int EPI>
 __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t taddr0, int64_t row, int col0, int nt) {
   float run_m = -INFINITY, run_s = 0.f;
+  const float stat_scale = p.stat_scale;  // log2(e) / temperature: the statistics are of logits / temperature
 #pragma unroll 1
   for (int c = 0; c < BN / 32; ++c) {
     uint32_t r[32];
@@ -239,8 +241,8 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t
         float cm = -INFINITY;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          const float lo = unpack16_lo(h[j], p.is_bf16) * 1.4426950408889634f;
-          const float hi = unpack16_hi(h[j], p.is_bf16) * 1.4426950408889634f;
+          const float lo = unpack16_lo(h[j], p.is_bf16) * stat_scale;
+          const float hi = unpack16_hi(h[j], p.is_bf16) * stat_scale;
           y[2 * j] = (cbase + 2 * j < p.N) ? lo : -INFINITY;
           y[2 * j + 1] = (cbase + 2 * j + 1 < p.N) ? hi : -INFINITY;
           cm = fmaxf(cm, fmaxf(y[2 * j], y[2 * j + 1]));

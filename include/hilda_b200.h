@@ -148,6 +148,11 @@ int hilda_count_valid(const int64_t* targets, int64_t n, int64_t ignore_index, i
 /* logits = hidden @ W^T rounded to dtype (fused_linear_cross_entropy.py:140) + online-LSE tile stats. */
 int hilda_flce_logits(const void* hidden, const void* W, void* logits, float* stats, int64_t rows, int64_t H,
                       int64_t V, int dtype, int* status, void* stream);
+/* The same with the statistics taken of logits * inv_temperature (stored logits unscaled): the
+ * log-softmax at a temperature of the fused linear + JSD loss (kernels/fused_linear_jsd.py:46-62). */
+int hilda_flce_logits_scaled(const void* hidden, const void* W, void* logits, float* stats, int64_t rows, int64_t H,
+                             int64_t V, float inv_temperature, int dtype, int* status, void* stream);
+/* targets may be null: no target logit is fetched (rowstat[2] = 0). */
 int hilda_flce_row_stats(const float* stats, const void* logits, const int64_t* targets, float* rowstat,
                          int64_t rows, int64_t V, int64_t vocab_start, int dtype, void* stream);
 int hilda_flce_finalize(const float* rowstat, const int64_t* targets, int64_t ignore_index, float* lse,
@@ -198,6 +203,33 @@ void hilda_gemm_set_probe(void* buf, int dry);
 int hilda_debug_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* c16, float* c32, int64_t ldc,
                      int M, int N, int K, int a_mn, int b_mn, int dtype, int mn_lbo, int mn_sbo, int* status,
                      void* stream);
+
+/* ---- KL divergence, JSD, fused linear + JSD ------------------------------------------------ */
+/* Replaces kl_div_forward (kernels/kl_div.py:114-137): y_pred log-probs, y_true probs (log-probs
+ * when log_target) [n_rows, n_cols] in dtype; loss_rows [n_rows] fp32 = the per-row sums;
+ * reduction 0 none, 1 sum, 2 mean (/ (n_rows * n_cols)), 3 batchmean (/ n_rows) -> loss_out. */
+int hilda_kl_div_fwd(const void* y_pred, const void* y_true, float* loss_rows, float* loss_out, int64_t n_rows,
+                     int64_t n_cols, int reduction, int log_target, float eps, int dtype, void* stream);
+/* Replaces kl_div_backward (kernels/kl_div.py:140-165): dy_pred = -y_true (or -exp(y_true)) *
+ * grad_out[0] * the reduction's factor; grad_out is a DEVICE fp32 scalar (the reference reads it on
+ * the host); reduction 0 uses scale 1 as the reference does. */
+int hilda_kl_div_bwd(const void* y_true, void* dy_pred, const float* grad_out, int64_t n_rows, int64_t n_cols,
+                     int reduction, int log_target, int dtype, void* stream);
+/* Replaces jsd_forward (kernels/jsd.py:97-135): X student, Y teacher log-probs [n_rows, V]; one
+ * pass writes dX (already divided by the number of rows whose label != ignore_index; labels may
+ * be null), loss_rows and loss_out = their sum. workspace: 4 bytes, needed with labels. */
+int hilda_jsd_fwd(const void* X, const void* Y, void* dX, float* loss_rows, float* loss_out, const int64_t* labels,
+                  int64_t ignore_index, void* workspace, int64_t n_rows, int64_t V, float beta, int dtype,
+                  void* stream);
+/* Row pass of fused_linear_jsd_forward (kernels/fused_linear_jsd.py:168-205: _log_softmax_kernel
+ * twice, _jsd_kernel, _softmax_grad_kernel) over one row chunk: from the two heads' logits
+ * (hilda_flce_logits_scaled scratch layout) and their row statistics (hilda_flce_row_stats) to the
+ * student's dlogits, in place over its logits, and the per-row loss. Divisor: *n_valid (device,
+ * clamped to 1) when given, else n_norm. */
+int hilda_fljsd_dlogits(void* s_logits, const void* t_logits, const float* rowstat_s, const float* rowstat_t,
+                        const int64_t* labels, int64_t ignore_index, const int* n_valid, int64_t n_norm,
+                        float* loss_rows, int64_t rows, int64_t V, float beta, float inv_temperature, int dtype,
+                        void* stream);
 
 /* ---- GRPO --------------------------------------------------------------------------------- */
 int64_t hilda_grpo_workspace_bytes(int64_t B);

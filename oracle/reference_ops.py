@@ -184,3 +184,84 @@ def grpo_aux(logits, completion_ids, advantages, old_logp=None, ref_logp=None, c
         kl = torch.exp(ref_logp - logp) - (ref_logp - logp) - 1
         kl_mean = (kl * mask).sum() / mask_sum
     return kl_mean, clip_ratio
+
+
+# --------------------------------------------------------------------------- KL divergence
+def kl_div(y_pred, y_true, reduction="batchmean", log_target=False):
+    """benchmarks/bench_kl_div.py:45, :66: ``torch.nn.functional.kl_div`` (y_pred log-probs,
+    y_true probs)."""
+    return F.kl_div(y_pred, y_true, reduction=reduction, log_target=log_target)
+
+
+def kl_div_rows(y_pred, y_true, reduction="batchmean", log_target=False, eps=1e-10):
+    """The operator's own contract (kernels/kl_div.py:52-64, :114-137): per-ROW sums of
+    t (log max(t, eps) - y) (or exp(t) (t - y) with log_target); 'none' returns the row sums,
+    'mean' divides by rows x cols, 'batchmean' by rows."""
+    y, t = y_pred.float(), y_true.float()
+    y2, t2 = y.reshape(-1, y.shape[-1]), t.reshape(-1, t.shape[-1])
+    per_row = (t2.exp() * (t2 - y2)).sum(-1) if log_target else (t2 * (t2.clamp_min(eps).log() - y2)).sum(-1)
+    if reduction == "none":
+        return per_row
+    if reduction == "sum":
+        return per_row.sum()
+    if reduction == "mean":
+        return per_row.sum() / y2.numel()
+    return per_row.sum() / y2.shape[0]
+
+
+# --------------------------------------------------------------------------- JSD
+def jsd(X, Y, beta=0.5):
+    """benchmarks/bench_jsd.py:30-44 (``pytorch_jsd``): X student, Y teacher log-probs."""
+    Q = X.exp()
+    P = Y.exp()
+    if beta == 0.0:
+        loss = (P * (Y - X)).sum(-1)
+    elif beta == 1.0:
+        loss = (Q * (X - Y)).sum(-1)
+    else:
+        M = beta * P + (1 - beta) * Q
+        log_M = M.log()
+        loss = beta * (P * (Y - log_M)).sum(-1) + (1 - beta) * (Q * (X - log_M)).sum(-1)
+    return loss.mean()
+
+
+def jsd_labels(X, Y, beta=0.5, labels=None, ignore_index=-100):
+    """The operator's contract with labels (kernels/jsd.py:49-58, :116-120): rows whose label is
+    ignore_index contribute nothing; the sum is divided by max(#other rows, 1)."""
+    Q, P = X.exp(), Y.exp()
+    if beta == 0.0:
+        per_row = (P * (Y - X)).sum(-1)
+    elif beta == 1.0:
+        per_row = (Q * (X - Y)).sum(-1)
+    else:
+        M = beta * P + (1 - beta) * Q
+        log_M = M.log()
+        per_row = beta * (P * (Y - log_M)).sum(-1) + (1 - beta) * (Q * (X - log_M)).sum(-1)
+    if labels is None:
+        return per_row.sum() / X.shape[0]
+    keep = labels != ignore_index
+    return (per_row * keep).sum() / max(int(keep.sum()), 1)
+
+
+# --------------------------------------------------------------------------- FusedLinearJSD
+def linear_jsd(s_input, s_weight, t_input, t_weight, beta=0.5, temperature=1.0):
+    """benchmarks/bench_fused_linear_jsd.py:31-43 (``pytorch_linear_jsd``); the bench feeds it fp32
+    copies of the inputs (:60, :83-85)."""
+    s_logits = (s_input @ s_weight.t()) / temperature
+    t_logits = (t_input @ t_weight.t()) / temperature
+    X = s_logits.log_softmax(dim=-1)
+    Y = t_logits.log_softmax(dim=-1)
+    Q = X.exp()
+    P = Y.exp()
+    M = beta * P + (1 - beta) * Q
+    log_M = M.log()
+    loss = beta * (P * (Y - log_M)).sum(-1) + (1 - beta) * (Q * (X - log_M)).sum(-1)
+    return loss.mean()
+
+
+def linear_jsd_labels(s_input, s_weight, t_input, t_weight, labels=None, beta=0.5, temperature=1.0, ignore_index=-100):
+    """The operator's contract (kernels/fused_linear_jsd.py:137-141, :182-190): any beta through
+    the JSD kernel's three branches, rows with an ignored label dropped, mean over the others."""
+    X = ((s_input @ s_weight.t()) / temperature).log_softmax(dim=-1)
+    Y = ((t_input @ t_weight.t()) / temperature).log_softmax(dim=-1)
+    return jsd_labels(X, Y, beta, labels, ignore_index)

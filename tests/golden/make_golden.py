@@ -7,8 +7,9 @@ Run once, in a container where the reference checkout is available:
 It imports the reference benchmark modules (``triton-kernels/benchmarks/bench_*.py``; importing them
 needs triton but no GPU) and calls the reference implementations they define
 (``pytorch_rms_norm``, ``pytorch_fused_add_rms_norm``, ``pytorch_rope``, ``pytorch_swiglu``, ``pytorch_geglu``,
-``pytorch_linear_ce``, ``pytorch_grpo_loss``) plus ``torch.nn.functional.cross_entropy`` exactly as
-``bench_cross_entropy.py:77-79`` calls it, on small seeded CPU inputs, including their autograd
+``pytorch_linear_ce``, ``pytorch_grpo_loss``, ``pytorch_jsd``, ``pytorch_linear_jsd``) plus
+``torch.nn.functional.cross_entropy`` exactly as ``bench_cross_entropy.py:77-79`` calls it and
+``torch.nn.functional.kl_div`` as ``bench_kl_div.py:45`` does, on small seeded CPU inputs, including their autograd
 gradients. Inputs and outputs are stored together so the tests need neither the reference nor
 this script at run time.
 """
@@ -27,7 +28,7 @@ def _import_reference(root):
     mods = {}
     with contextlib.redirect_stdout(io.StringIO()):
         for name in ("bench_rms_norm", "bench_fused_add_rms_norm", "bench_rope", "bench_swiglu", "bench_geglu",
-                     "bench_fused_linear_ce", "bench_grpo"):
+                     "bench_fused_linear_ce", "bench_grpo", "bench_jsd", "bench_fused_linear_jsd"):
             mods[name] = __import__(name)
     return mods
 
@@ -146,6 +147,40 @@ def main(root):
         loss.backward()
         out[f"grpo_{tag}"] = dict(logits=logits, ids=ids, adv=adv, old=old, ref=ref, mask=mask, beta=beta,
                                   loss=loss.detach(), dlogits=lr.grad)
+
+    # ---- KLDiv: F.kl_div(y_pred, y_true, reduction='batchmean') as bench_kl_div.py:42-45, :62-67
+    g = _g(8)
+    n, v = 10, 600
+    y_pred = torch.randn(n, v, generator=g).log_softmax(-1)
+    y_true = torch.randn(n, v, generator=g).softmax(-1)
+    yr = y_pred.clone().requires_grad_(True)
+    loss = torch.nn.functional.kl_div(yr, y_true, reduction="batchmean")
+    loss.backward()
+    out["kl_div_f32"] = dict(y_pred=y_pred, y_true=y_true, loss=loss.detach(), dy_pred=yr.grad)
+
+    # ---- JSD: pytorch_jsd at beta 0.5 / 0 / 1 (bench_jsd.py:30-44, :51-58)
+    for tag, beta in (("b05", 0.5), ("b0", 0.0), ("b1", 1.0)):
+        g = _g(9)
+        n, v = 9, 700
+        X = torch.randn(n, v, generator=g).log_softmax(-1)
+        Y = torch.randn(n, v, generator=g).log_softmax(-1)
+        xr = X.clone().requires_grad_(True)
+        loss = m["bench_jsd"].pytorch_jsd(xr, Y, beta)
+        loss.backward()
+        out[f"jsd_{tag}"] = dict(X=X, Y=Y, beta=beta, loss=loss.detach(), dX=xr.grad)
+
+    # ---- FusedLinearJSD: pytorch_linear_jsd on fp32 inputs (bench_fused_linear_jsd.py:31-43, :83-88)
+    g = _g(10)
+    bt, h, v = 40, 64, 520
+    s_in = torch.randn(bt, h, generator=g)
+    s_w = 0.05 * torch.randn(v, h, generator=g)
+    t_in = torch.randn(bt, h, generator=g)
+    t_w = 0.05 * torch.randn(v, h, generator=g)
+    sr, wr = s_in.clone().requires_grad_(True), s_w.clone().requires_grad_(True)
+    loss = m["bench_fused_linear_jsd"].pytorch_linear_jsd(sr, wr, t_in, t_w, beta=0.5, temperature=2.0)
+    loss.backward()
+    out["linear_jsd_f32"] = dict(s_in=s_in, s_w=s_w, t_in=t_in, t_w=t_w, beta=0.5, temperature=2.0,
+                                 loss=loss.detach(), dh=sr.grad, dw=wr.grad)
 
     dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden.pt")
     torch.save(out, dst)

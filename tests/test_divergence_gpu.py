@@ -1,0 +1,204 @@
+"""GPU parity tests of the divergence losses (KL, JSD, fused linear + JSD) against the CPU oracle
+(oracle/reference_ops.py) on identical seeded inputs, and against the golden outputs of
+hilda-kernel's reference functions. All calls go through the Python operator API / the C ABI."""
+import pytest
+import torch
+
+from oracle import reference_ops as R
+from tests.util import assert_close, assert_loss_close
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+DTYPES = [torch.float32, torch.bfloat16, torch.float16]
+
+
+def gen(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+FP16_MIN_NORMAL = 6.1e-5
+
+
+def fp16_grad_underflows(dtype, expected, actual):
+    """A gradient whose largest entry is below fp16's smallest normal number lives in the subnormal
+    range (steps of 6e-8) or below it: the reference's 16-bit gradient buffer loses it the same way.
+    Then only check that ours is no larger, and report that there is nothing to compare."""
+    if dtype != torch.float16 or float(expected.abs().max()) >= FP16_MIN_NORMAL:
+        return False
+    assert float(actual.abs().max()) <= 2 * FP16_MIN_NORMAL
+    return True
+
+
+# ------------------------------------------------------------------ KLDiv
+@pytest.mark.parametrize("shape", [(64, 32000), (16, 128256), (7, 200), (5, 33), (3, 4, 1000), (1, 1)])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("reduction", ["batchmean", "sum", "mean", "none"])
+@pytest.mark.parametrize("log_target", [False, True])
+def test_kl_div(shape, dtype, reduction, log_target):
+    import hilda_kernel_b200 as hk
+    g = gen(31)
+    y_pred = torch.randn(*shape, generator=g).log_softmax(-1).to(dtype)
+    y_true = torch.randn(*shape, generator=g).softmax(-1)
+    y_true = (y_true.log() if log_target else y_true).to(dtype)
+    yr = y_pred.float().clone().requires_grad_(True)
+    ref = R.kl_div_rows(yr, y_true.float(), reduction, log_target)
+    (ref.sum() if reduction == "none" else ref).backward()
+    yd = y_pred.to(DEV).requires_grad_(True)
+    loss = hk.hilda_kl_div(yd, y_true.to(DEV), reduction, log_target)
+    assert loss.dtype == torch.float32
+    if reduction == "none":
+        assert loss.shape == (y_pred.numel() // shape[-1],)
+        assert_close(loss, ref.detach(), torch.float32, what="row sums", scale=max(float(ref.detach().abs().max()), 1.0))
+        loss.sum().backward()
+    else:
+        assert abs(float(loss.detach()) - float(ref.detach())) <= 1e-4 * abs(float(ref.detach())) + 1e-6
+        (loss * 1.5).backward()
+        yr.grad.mul_(1.5)
+    assert yd.grad.dtype == dtype and yd.grad.shape == y_pred.shape
+    if fp16_grad_underflows(dtype, yr.grad, yd.grad):
+        return
+    assert_close(yd.grad, yr.grad, dtype, what="dy_pred", normalize=True)
+
+
+def test_kl_div_golden_and_module(golden):
+    import hilda_kernel_b200 as hk
+    c = golden["kl_div_f32"]
+    yd = c["y_pred"].to(DEV).requires_grad_(True)
+    loss = hk.KLDivLoss()(yd, c["y_true"].to(DEV))
+    loss.backward()
+    assert abs(float(loss) - float(c["loss"])) < 1e-4  # bench_kl_div.py fp32 threshold
+    assert float((yd.grad.cpu() - c["dy_pred"]).abs().max()) < 1e-5  # bench_kl_div.py:73 fp32 threshold
+    # eps clamps log(0): a zero target contributes nothing
+    yt = c["y_true"].clone(); yt[:, :7] = 0
+    l2 = hk.hilda_kl_div(c["y_pred"].to(DEV), yt.to(DEV))
+    assert_loss_close(l2, R.kl_div_rows(c["y_pred"], yt))
+
+
+# ------------------------------------------------------------------ JSD
+@pytest.mark.parametrize("nv", [(64, 32000), (16, 128256), (9, 700), (5, 33)])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("beta", [0.5, 0.0, 1.0, 0.1])
+@pytest.mark.parametrize("with_labels", [False, True])
+def test_jsd(nv, dtype, beta, with_labels):
+    import hilda_kernel_b200 as hk
+    n, v = nv
+    g = gen(32)
+    X = torch.randn(n, v, generator=g).log_softmax(-1).to(dtype)
+    Y = torch.randn(n, v, generator=g).log_softmax(-1).to(dtype)
+    labels = None
+    if with_labels:
+        labels = torch.randint(0, v, (n,), generator=g)
+        labels[torch.randperm(n, generator=g)[:max(1, n // 4)]] = -100
+    xr = X.float().clone().requires_grad_(True)
+    ref = R.jsd_labels(xr, Y.float(), beta, labels)
+    (ref * 0.5).backward()
+    xd = X.to(DEV).requires_grad_(True)
+    loss = hk.hilda_jsd(xd, Y.to(DEV), beta, labels.to(DEV) if with_labels else None)
+    assert loss.dtype == torch.float32 and loss.dim() == 0
+    assert abs(float(loss.detach()) - float(ref.detach())) <= 1e-4 * abs(float(ref.detach())) + 1e-6
+    (loss * 0.5).backward()
+    assert xd.grad.dtype == dtype
+    if fp16_grad_underflows(dtype, xr.grad, xd.grad):
+        return
+    assert_close(xd.grad, xr.grad, dtype, what="dX", normalize=True)
+    if with_labels:
+        assert float(xd.grad[(labels == -100).to(DEV)].abs().max()) == 0.0
+
+
+def test_jsd_golden_and_edges(golden):
+    import hilda_kernel_b200 as hk
+    for tag in ("b05", "b0", "b1"):
+        c = golden[f"jsd_{tag}"]
+        xd = c["X"].to(DEV).requires_grad_(True)
+        loss = hk.JSDLoss(beta=c["beta"])(xd, c["Y"].to(DEV))
+        loss.backward()
+        assert abs(float(loss) - float(c["loss"])) < 1e-4  # bench_jsd.py fp32 threshold
+        assert_close(xd.grad, c["dX"], torch.float32, what=f"dX {tag}", normalize=True)
+    # every label ignored: loss 0 and a zero gradient (divisor clamped to 1, jsd.py:117)
+    c = golden["jsd_b05"]
+    lab = torch.full((c["X"].shape[0],), -100)
+    xd = c["X"].to(DEV).requires_grad_(True)
+    loss = hk.hilda_jsd(xd, c["Y"].to(DEV), 0.5, lab.to(DEV))
+    loss.backward()
+    assert float(loss) == 0.0 and float(xd.grad.abs().max()) == 0.0
+    # log-probs so negative that both probabilities underflow give 0, not NaN
+    X = c["X"].clone(); Y = c["Y"].clone()
+    X[:, :5] = -200.0; Y[:, :5] = -200.0
+    loss = hk.hilda_jsd(X.to(DEV), Y.to(DEV), 0.5)
+    assert torch.isfinite(loss).item()
+
+
+# ------------------------------------------------------------------ FusedLinearJSD
+def _fljsd_oracle(s_in, s_w, t_in, t_w, labels, beta, temperature):
+    """fp32 autograd of the PyTorch reference on the (already rounded) 16-bit inputs, with both
+    heads' logits rounded to the compute dtype as the reference's GEMMs do."""
+    h, w = s_in.float().clone().requires_grad_(True), s_w.float().clone().requires_grad_(True)
+    sl = h @ w.T
+    sl = sl + (sl.to(s_in.dtype).float() - sl).detach()  # straight-through rounding
+    tl = (t_in.float() @ t_w.float().T).to(s_in.dtype).float()
+    X = (sl / temperature).log_softmax(-1)
+    Y = (tl / temperature).log_softmax(-1)
+    loss = R.jsd_labels(X, Y, beta, labels)
+    loss.backward()
+    return loss.detach(), h.grad, w.grad
+
+
+@pytest.mark.parametrize("shape", [(300, 256, 128, 3000), (512, 512, 512, 32000), (130, 64, 192, 520), (64, 256, 256, 50257),
+                                   (96, 128, 64, 600)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("beta,temperature", [(0.5, 1.0), (0.0, 2.0), (1.0, 1.0), (0.3, 0.7)])
+@pytest.mark.parametrize("chunk", [None, 128])
+def test_fused_linear_jsd(shape, dtype, beta, temperature, chunk):
+    import hilda_kernel_b200 as hk
+    from hilda_kernel_b200.kernels import fused_linear_jsd as FJ
+    BT, H, Ht, V = shape
+    if dtype == torch.float16 and V * BT > 60000:
+        # dlogits ~ 1/(V * n_rows) is below fp16's smallest normal number (6e-5): the 16-bit dlogits
+        # buffer (which the reference has too) holds subnormals or zeros, nothing to compare
+        pytest.skip("fp16 dlogits underflow at this size (as for FusedLinearCE)")
+    g = gen(33)
+    s_in = torch.randn(BT, H, generator=g).to(dtype)
+    s_w = (0.05 * torch.randn(V, H, generator=g)).to(dtype)
+    t_in = torch.randn(BT, Ht, generator=g).to(dtype)
+    t_w = (0.05 * torch.randn(V, Ht, generator=g)).to(dtype)
+    labels = torch.randint(0, V, (BT,), generator=g)
+    labels[torch.randperm(BT, generator=g)[:BT // 10]] = -100
+    loss_ref, dh_ref, dw_ref = _fljsd_oracle(s_in, s_w, t_in, t_w, labels, beta, temperature)
+    FJ.CHUNK_ROWS = chunk
+    try:
+        hd, wd = s_in.to(DEV).requires_grad_(True), s_w.to(DEV).requires_grad_(True)
+        loss = hk.hilda_fused_linear_jsd(hd, wd, t_in.to(DEV), t_w.to(DEV), labels.to(DEV), beta, temperature)
+        assert loss.dtype == torch.float32
+        (loss * 2.0).backward()
+        with torch.no_grad():
+            l_nolabel = hk.hilda_fused_linear_jsd(s_in.to(DEV), s_w.to(DEV), t_in.to(DEV), t_w.to(DEV), None, beta,
+                                                  temperature)
+    finally:
+        FJ.CHUNK_ROWS = None
+    torch.cuda.synchronize()
+    # the loss is a small difference of O(10) log-probabilities per element; against the oracle on
+    # the same rounded logits it agrees to the scalar-loss tolerance plus the approximate exp/log
+    assert abs(float(loss) - float(loss_ref)) <= 2e-4 * abs(float(loss_ref)) + 1e-6, (float(loss), float(loss_ref))
+    ref_nolabel, _, _ = _fljsd_oracle(s_in, s_w, t_in, t_w, None, beta, temperature)
+    assert abs(float(l_nolabel) - float(ref_nolabel)) <= 2e-4 * abs(float(ref_nolabel)) + 1e-6
+    assert hd.grad.dtype == dtype and wd.grad.dtype == dtype
+    assert_close(hd.grad, 2.0 * dh_ref, dtype, what="d student input", normalize=True)
+    assert_close(wd.grad, 2.0 * dw_ref, dtype, what="d student weight", normalize=True)
+    assert float(hd.grad[(labels == -100).to(DEV)].abs().max()) == 0.0
+
+
+def test_fused_linear_jsd_golden(golden):
+    import hilda_kernel_b200 as hk
+    c = golden["linear_jsd_f32"]
+    dt = torch.bfloat16
+    hd = c["s_in"].to(dt).to(DEV).requires_grad_(True)
+    wd = c["s_w"].to(dt).to(DEV).requires_grad_(True)
+    loss = hk.FusedLinearJSDLoss(beta=c["beta"], temperature=c["temperature"])(
+        hd, wd, c["t_in"].to(dt).to(DEV), c["t_w"].to(dt).to(DEV))
+    loss.backward()
+    # golden values are fp32 end to end; the operator rounds inputs and logits to bf16
+    # (bench_fused_linear_jsd.py:63 accepts 5e-1 for 16-bit runs; this is far inside it)
+    assert abs(float(loss) - float(c["loss"])) < 0.05 * abs(float(c["loss"])) + 1e-4
+    assert float((hd.grad.float().cpu() - c["dh"]).abs().max()) < 5e-2   # :95 thresholds
+    assert float((wd.grad.float().cpu() - c["dw"]).abs().max()) < 5e-1

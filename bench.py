@@ -303,6 +303,40 @@ def per_op_table(device, pk, only=None, small=False):
                                        iters=4),
             (A + B * (Lc + 1)) * v * 2, B * Lc)
         out["grpo_bf16_fwd+bwd"]["active_tokens"] = A
+    # ---- AttnRes bf16, 8 blocks of [4, 2048, 4096] (bench_attn_res.py:211): forward reads V, writes h;
+    # backward reads dh and V, writes dV
+    if want("attn_res"):
+        from hilda_kernel_b200.kernels.attn_res import attn_res_backward, attn_res_forward
+        nb, ntok, d = 8, 8192 // div, 4096
+        wq, wn = (0.02 * rn(d)).bfloat16(), (1 + 0.1 * rn(d)).bfloat16()
+        sets = []
+        for _ in range(2):
+            Vb, dh = rn(nb, ntok, d).bfloat16(), rn(ntok, d).bfloat16()
+            _, v3, al, rs = attn_res_forward(Vb, wq, wn)
+            sets.append((Vb, dh, v3, al, rs))
+        add("attn_res_bf16_fwd+bwd",
+            timed2([(lambda Vb=Vb: attn_res_forward(Vb, wq, wn)) for Vb, _, _, _, _ in sets],
+                   [(lambda dh=dh, v3=v3, al=al, rs=rs: attn_res_backward(dh, v3, wq, wn, al, rs)) for _, dh, v3, al, rs in sets]),
+            (nb + 1 + 1 + nb + nb) * ntok * d * 2, ntok)
+        del sets
+    # ---- paged FP8 decode attention, batch 32, 16 / 8 heads, context 4096, blocks of 256
+    # (bench_paged_attention_fp8.py:131): the K and V cache rows of every sequence read once
+    if want("paged_attention"):
+        from hilda_kernel_b200.kernels.paged_attention_fp8 import hilda_paged_attention_fp8_decode
+        batch, nh, nkv, ctx, bs = 32 // (4 if small else 1), 16, 8, 4096, 256
+        per_seq = ctx // bs
+        sets = []
+        for _ in range(3):
+            q = rn(batch, nh, 128).bfloat16()
+            kc = rn(batch * per_seq, bs, nkv, 128).to(torch.float8_e4m3fn)
+            vc = rn(batch * per_seq, bs, nkv, 128).to(torch.float8_e4m3fn)
+            bt = torch.randperm(batch * per_seq, device=device, generator=g).int().view(batch, per_seq)
+            cl = torch.full((batch,), ctx, device=device, dtype=torch.int32)
+            sets.append((q, kc, vc, bt, cl))
+        ms = timed([(lambda q=q, kc=kc, vc=vc, bt=bt, cl=cl: hilda_paged_attention_fp8_decode(q, kc, vc, bt, cl, 128 ** -0.5))
+                    for q, kc, vc, bt, cl in sets])
+        add("paged_attention_fp8_decode", ms, 2 * batch * ctx * nkv * 128, batch)
+        del sets
     # ---- the divergence losses (reference bench shapes: bench_kl_div.py:158, bench_jsd.py:175,
     # bench_fused_linear_jsd.py:165, in bf16)
     if want("kl_div"):

@@ -51,7 +51,13 @@ SIGNATURES = {
     "hilda_flce_logits_scaled": (_i32, [_p, _p, _p, _p, _i64, _i64, _i64, _f32, _i32, _p, _p]),
     "hilda_kl_div_fwd": (_i32, [_p, _p, _p, _p, _i64, _i64, _i32, _i32, _f32, _i32, _p]),
     "hilda_kl_div_bwd": (_i32, [_p, _p, _p, _i64, _i64, _i32, _i32, _i32, _p]),
-    "hilda_jsd_fwd": (_i32, [_p, _p, _p, _p, _p, _p, _i64, _p, _i64, _i64, _f32, _i32, _p]),
+    "hilda_jsd_fwd": (_i32, [_p, _p, _p, _p, _p, _p, _i64, _p, _i64, _i64, _f32, _i32, _p]),    "hilda_paged_attention_fp8_workspace_bytes": (_i64, [_i64] * 5),
+    "hilda_paged_attention_fp8_decode": (_i32, [_p, _i64, _i64, _p, _i64, _i64, _i64, _p, _i64, _i64, _i64, _p, _i64, _i64,
+                                                _p, _i64, _p, _p, _f32, _i64, _i64, _i64, _i64, _i64, _i64, _p]),
+
+    "hilda_attn_res_fwd": (_i32, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _p]),
+    "hilda_attn_res_bwd_workspace_bytes": (_i64, [_i64, _i64]),
+    "hilda_attn_res_bwd": (_i32, [_p] * 10 + [_i64, _i64, _i64, _i32, _i32, _i32, _p]),
     "hilda_fljsd_dlogits": (_i32, [_p, _p, _p, _p, _p, _i64, _p, _i64, _p, _i64, _i64, _f32, _f32, _i32, _p]),
     "hilda_flce_row_stats": (_i32, [_p, _p, _p, _p, _i64, _i64, _i64, _i32, _p]),
     "hilda_flce_finalize": (_i32, [_p, _p, _i64, _p, _p, _i64, _p]),

@@ -231,6 +231,40 @@ int hilda_fljsd_dlogits(void* s_logits, const void* t_logits, const float* rowst
                         float* loss_rows, int64_t rows, int64_t V, float beta, float inv_temperature, int dtype,
                         void* stream);
 
+/* ---- AttnRes ------------------------------------------------------------------------------ */
+/* Replaces attn_res_forward (kernels/attn_res.py:213-260): V [n_blocks, n_tokens, D] in dtype,
+ * w_query / w_norm [D] in their own dtypes, n_blocks <= 32; out [n_tokens, D] = sum_i alpha_i v_i
+ * with alpha = softmax_i <w_query, RMSNorm(v_i) * w_norm>; alpha and rstd [n_blocks, n_tokens]
+ * fp32 are saved for the backward. Every block row is read once. */
+int hilda_attn_res_fwd(const void* V, const void* w_query, const void* w_norm, void* out, float* alpha, float* rstd,
+                       int64_t n_blocks, int64_t n_tokens, int64_t D, float eps, int dtype, int wq_dtype,
+                       int wn_dtype, void* stream);
+/* Replaces attn_res_backward (kernels/attn_res.py:263-293): dV in dtype, dw_query / dw_norm in the
+ * weights' dtypes (summed in fp32 in a fixed order; the reference uses float atomics). */
+int64_t hilda_attn_res_bwd_workspace_bytes(int64_t n_tokens, int64_t D);
+int hilda_attn_res_bwd(const void* d_out, const void* V, const void* w_query, const void* w_norm, const float* alpha,
+                       const float* rstd, void* dV, void* dw_query, void* dw_norm, void* workspace,
+                       int64_t n_blocks, int64_t n_tokens, int64_t D, int dtype, int wq_dtype, int wn_dtype,
+                       void* stream);
+
+/* ---- Paged FP8 decode attention ----------------------------------------------------------- */
+/* Replaces hilda_paged_attention_fp8_decode (kernels/paged_attention_fp8.py:141-188): one query
+ * token per sequence. q [batch, n_heads, 128] bf16 (element strides q_sb, q_sh), k_cache / v_cache
+ * [blocks, block_size, n_kv_heads, 128] fp8 e4m3 (byte strides per block, token, kv head; multiples
+ * of 16), block_tables int32 [batch, max_blocks] (row stride bt_sb), context_lens int32 [batch],
+ * out [batch, n_heads, 128] bf16. n_heads % n_kv_heads == 0 (GQA); head_dim must be 128 as in the
+ * reference (:134). workspace: hilda_paged_attention_fp8_workspace_bytes(...) bytes (partial
+ * results of the context splits). */
+int64_t hilda_paged_attention_fp8_workspace_bytes(int64_t batch, int64_t n_heads, int64_t n_kv_heads,
+                                                  int64_t max_blocks, int64_t block_size);
+int hilda_paged_attention_fp8_decode(const void* q, int64_t q_sb, int64_t q_sh, const void* k_cache, int64_t k_sblk,
+                                     int64_t k_stok, int64_t k_sh, const void* v_cache, int64_t v_sblk,
+                                     int64_t v_stok, int64_t v_sh, void* out, int64_t o_sb, int64_t o_sh,
+                                     const int32_t* block_tables, int64_t bt_sb, const int32_t* context_lens,
+                                     void* workspace, float scale, int64_t batch, int64_t n_heads,
+                                     int64_t n_kv_heads, int64_t head_dim, int64_t block_size, int64_t max_blocks,
+                                     void* stream);
+
 /* ---- GRPO --------------------------------------------------------------------------------- */
 int64_t hilda_grpo_workspace_bytes(int64_t B);
 /* Replaces grpo_loss_forward + grpo_loss_backward (kernels/grpo_loss.py:241-297, :300-330) in one

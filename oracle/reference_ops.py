@@ -265,3 +265,38 @@ def linear_jsd_labels(s_input, s_weight, t_input, t_weight, labels=None, beta=0.
     X = ((s_input @ s_weight.t()) / temperature).log_softmax(dim=-1)
     Y = ((t_input @ t_weight.t()) / temperature).log_softmax(dim=-1)
     return jsd_labels(X, Y, beta, labels, ignore_index)
+
+
+# --------------------------------------------------------------------------- AttnRes
+def attn_res(V, w_query, w_norm, eps=1e-6):
+    """benchmarks/bench_attn_res.py:33-51 (``pytorch_attn_res``): V [N, B, T, D], w_query, w_norm [D]."""
+    V_f32 = V.float()
+    rms = torch.sqrt(V_f32.pow(2).mean(dim=-1, keepdim=True) + eps)
+    K = (V_f32 / rms).to(V.dtype) * w_norm
+    scores = torch.einsum('d, n b t d -> n b t', w_query.float(), K.float())
+    alpha = scores.softmax(dim=0)
+    h = torch.einsum('n b t, n b t d -> b t d', alpha, V.float()).to(V.dtype)
+    return h
+
+
+# --------------------------------------------------------------------------- paged FP8 decode attention
+def paged_attention_decode(q, k_cache, v_cache, block_tables, context_lens, scale):
+    """kernels/paged_attention_fp8.py:191-221 (``reference_paged_attention_decode``): q
+    [batch, heads, 128] bf16, caches [blocks, block_size, kv_heads, 128] fp8 e4m3; fp32 math,
+    bf16 result. Returns the fp32 result as well (second value) for tolerance checks."""
+    batch, num_heads, head_dim = q.shape
+    _, block_size, num_kv_heads, _ = k_cache.shape
+    kv_of_head = torch.arange(num_heads) // (num_heads // num_kv_heads)
+    out32 = torch.zeros((batch, num_heads, head_dim), dtype=torch.float32)
+    kf, vf = k_cache.float(), v_cache.float()
+    for b in range(batch):
+        n_ctx = int(context_lens[b])
+        if n_ctx == 0:
+            continue
+        n_blk = -(-n_ctx // block_size)
+        ids = block_tables[b, :n_blk].long()
+        k = kf.index_select(0, ids).reshape(-1, num_kv_heads, head_dim)[:n_ctx].index_select(1, kv_of_head)
+        v = vf.index_select(0, ids).reshape(-1, num_kv_heads, head_dim)[:n_ctx].index_select(1, kv_of_head)
+        probs = (torch.einsum('hd,thd->ht', q[b].float(), k) * scale).softmax(dim=-1)
+        out32[b] = torch.einsum('ht,thd->hd', probs, v)
+    return out32.to(torch.bfloat16), out32

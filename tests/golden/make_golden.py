@@ -7,7 +7,7 @@ Run once, in a container where the reference checkout is available:
 It imports the reference benchmark modules (``triton-kernels/benchmarks/bench_*.py``; importing them
 needs triton but no GPU) and calls the reference implementations they define
 (``pytorch_rms_norm``, ``pytorch_fused_add_rms_norm``, ``pytorch_rope``, ``pytorch_swiglu``, ``pytorch_geglu``,
-``pytorch_linear_ce``, ``pytorch_grpo_loss``, ``pytorch_jsd``, ``pytorch_linear_jsd``) plus
+``pytorch_linear_ce``, ``pytorch_grpo_loss``, ``pytorch_jsd``, ``pytorch_linear_jsd``, ``pytorch_attn_res``) plus
 ``torch.nn.functional.cross_entropy`` exactly as ``bench_cross_entropy.py:77-79`` calls it and
 ``torch.nn.functional.kl_div`` as ``bench_kl_div.py:45`` does, on small seeded CPU inputs, including their autograd
 gradients. Inputs and outputs are stored together so the tests need neither the reference nor
@@ -28,7 +28,7 @@ def _import_reference(root):
     mods = {}
     with contextlib.redirect_stdout(io.StringIO()):
         for name in ("bench_rms_norm", "bench_fused_add_rms_norm", "bench_rope", "bench_swiglu", "bench_geglu",
-                     "bench_fused_linear_ce", "bench_grpo", "bench_jsd", "bench_fused_linear_jsd"):
+                     "bench_fused_linear_ce", "bench_grpo", "bench_jsd", "bench_fused_linear_jsd", "bench_attn_res"):
             mods[name] = __import__(name)
     return mods
 
@@ -181,6 +181,33 @@ def main(root):
     loss.backward()
     out["linear_jsd_f32"] = dict(s_in=s_in, s_w=s_w, t_in=t_in, t_w=t_w, beta=0.5, temperature=2.0,
                                  loss=loss.detach(), dh=sr.grad, dw=wr.grad)
+
+    # ---- AttnRes: pytorch_attn_res (bench_attn_res.py:33-51), fp32 and bf16, with autograd gradients
+    for tag, dtype in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        g = _g(11)
+        nb, bsz, t, d = 5, 2, 7, 256
+        V = torch.randn(nb, bsz, t, d, generator=g).to(dtype)
+        wq = (0.02 * torch.randn(d, generator=g)).to(dtype)
+        wn = (1 + 0.1 * torch.randn(d, generator=g)).to(dtype)
+        dh = torch.randn(bsz, t, d, generator=g).to(dtype)
+        vr, qr, nr = (x.clone().requires_grad_(True) for x in (V, wq, wn))
+        h = m["bench_attn_res"].pytorch_attn_res(vr, qr, nr)
+        h.backward(dh)
+        out[f"attn_res_{tag}"] = dict(V=V, wq=wq, wn=wn, dh=dh, h=h.detach(), dV=vr.grad, dwq=qr.grad, dwn=nr.grad)
+
+    # ---- paged FP8 decode attention: the reference's own torch evaluation (paged_attention_fp8.py:191-221)
+    sys.path.insert(0, os.path.join(root, "triton-kernels"))
+    from kernels.paged_attention_fp8 import reference_paged_attention_decode
+    g = _g(12)
+    batch, nh, nkv, bs, nblk = 3, 8, 2, 16, 9
+    q = torch.randn(batch, nh, 128, generator=g).bfloat16()
+    kc = torch.randn(nblk, bs, nkv, 128, generator=g).to(torch.float8_e4m3fn)
+    vc = torch.randn(nblk, bs, nkv, 128, generator=g).to(torch.float8_e4m3fn)
+    bt = torch.tensor([[4, 0, 7], [2, 8, 8], [5, 1, 1]], dtype=torch.int32)
+    ctx = torch.tensor([37, 16, 5], dtype=torch.int32)
+    o = reference_paged_attention_decode(q, kc, vc, bt, ctx, 128 ** -0.5)
+    out["paged_attention_fp8"] = dict(q=q, k_cache=kc.view(torch.uint8), v_cache=vc.view(torch.uint8), block_tables=bt,
+                                      context_lens=ctx, scale=128 ** -0.5, out=o)
 
     dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden.pt")
     torch.save(out, dst)

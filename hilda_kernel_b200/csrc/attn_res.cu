@@ -40,6 +40,34 @@ __device__ __forceinline__ float ar_key(float v, float rstd, float wn, int wn_dt
   return round_any(round_any(v * rstd, wn_dt) * wn, wn_dt);
 }
 
+// acc += a.lo * b.lo + a.hi * b.hi for packed 16-bit pairs with an fp32 accumulator (mixed-precision
+// FMA: the product of two 16-bit floats is exact in fp32, so this equals converting first).
+template <typename T>
+__device__ __forceinline__ float fma2_mixed(uint32_t a, uint32_t b, float acc) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    asm("{\n.reg .b16 al, ah, bl, bh;\n mov.b32 {al, ah}, %1;\n mov.b32 {bl, bh}, %2;\n"
+        "fma.rn.f32.bf16 %0, al, bl, %0;\n fma.rn.f32.bf16 %0, ah, bh, %0;\n}" : "+f"(acc) : "r"(a), "r"(b));
+  } else {
+    asm("{\n.reg .b16 al, ah, bl, bh;\n mov.b32 {al, ah}, %1;\n mov.b32 {bl, bh}, %2;\n"
+        "fma.rn.f32.f16 %0, al, bl, %0;\n fma.rn.f32.f16 %0, ah, bh, %0;\n}" : "+f"(acc) : "r"(a), "r"(b));
+  }
+  return acc;
+}
+// sum of squares of the 8 values of a 16-byte vector of 16-bit floats, no unpacking
+template <typename T>
+__device__ __forceinline__ float sumsq16(const uint4& v, float acc) {
+  acc = fma2_mixed<T>(v.x, v.x, acc); acc = fma2_mixed<T>(v.y, v.y, acc);
+  acc = fma2_mixed<T>(v.z, v.z, acc); acc = fma2_mixed<T>(v.w, v.w, acc);
+  return acc;
+}
+// dot product of two 16-byte vectors of 16-bit floats, fp32 accumulation
+template <typename T>
+__device__ __forceinline__ float dot16(const uint4& a, const uint4& b, float acc) {
+  acc = fma2_mixed<T>(a.x, b.x, acc); acc = fma2_mixed<T>(a.y, b.y, acc);
+  acc = fma2_mixed<T>(a.z, b.z, acc); acc = fma2_mixed<T>(a.w, b.w, acc);
+  return acc;
+}
+
 // sum_e wq[e] * k(v[e]) over one 16-byte vector, with k as ar_key. The dtype test is hoisted out of
 // the element loop; when the keys round to the data's own 16-bit type the two roundings are one
 // packed convert and one packed multiply per pair.
@@ -429,10 +457,15 @@ attn_res_fwd_staged_kernel(const T* __restrict__ V, const void* __restrict__ w_q
 #pragma unroll
       for (int j = 0; j < VPT; ++j) {
         if (threadIdx.x + j * THREADS < n_vec) {
-          float vf[VEC];
-          VT<T>::unpack(*reinterpret_cast<const uint4*>(rows + i * D + j * THREADS * VEC), vf);
+          const uint4 raw = *reinterpret_cast<const uint4*>(rows + i * D + j * THREADS * VEC);
+          if constexpr (sizeof(T) == 2) {
+            ss = sumsq16<T>(raw, ss);
+          } else {
+            float vf[VEC];
+            VT<T>::unpack(raw, vf);
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) ss += vf[e] * vf[e];
+            for (int e = 0; e < VEC; ++e) ss += vf[e] * vf[e];
+          }
         }
       }
       ss = warp_sum(ss);
@@ -537,6 +570,11 @@ attn_res_bwd_staged_kernel(const T* __restrict__ dOut, const T* __restrict__ V, 
       dwq[j][e] = 0.f; dwn[j][e] = 0.f;
     }
   }
+  float g_w[VPT][VEC];  // w_query * w_norm, the gradient direction of a score through the key
+#pragma unroll
+  for (int j = 0; j < VPT; ++j)
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) g_w[j][e] = wq[j][e] * wn[j][e];
   const int64_t blk_stride = n_tokens * (int64_t)D;
   auto issue = [&](int64_t tok, int st) {
     if (tok < n_tokens) {
@@ -579,7 +617,7 @@ attn_res_bwd_staged_kernel(const T* __restrict__ dOut, const T* __restrict__ V, 
           float vf[VEC];
           VT<T>::unpack(*reinterpret_cast<const uint4*>(rows + (int64_t)i * D + (int64_t)v * VEC), vf);
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) { da += dh[j][e] * vf[e]; c += wq[j][e] * wn[j][e] * vf[e]; }
+          for (int e = 0; e < VEC; ++e) { da += dh[j][e] * vf[e]; c += g_w[j][e] * vf[e]; }
         }
       }
       da = warp_sum(da);
@@ -607,7 +645,7 @@ attn_res_bwd_staged_kernel(const T* __restrict__ dOut, const T* __restrict__ V, 
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
           const float q = wq[j][e], n = wn[j][e];
-          o[e] = a * dh[j][e] + coef_g * q * n - coef_v * vf[e];
+          o[e] = a * dh[j][e] + coef_g * g_w[j][e] - coef_v * vf[e];
           const float vn = vf[e] * rstd;
           dwq[j][e] += ds * vn * n;
           dwn[j][e] += ds * q * vn;

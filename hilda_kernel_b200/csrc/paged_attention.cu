@@ -35,17 +35,34 @@ struct PaParams {
   int n_heads, n_kv_heads, group, block_size, max_blocks, splits, tokens_per_split;
 };
 
-// 16 fp8 (e4m3) values in a uint4 -> 16 floats (exact).
-__device__ __forceinline__ void fp8x16_to_float(const uint4& raw, float* f) {
+// 16 fp8 (e4m3) values in a uint4 -> 8 packed half2 (exact: e4m3 is a subset of fp16).
+__device__ __forceinline__ void fp8x16_to_half2(const uint4& raw, uint32_t* h) {
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] & 0xffffu), __NV_E4M3);
     const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] >> 16), __NV_E4M3);
-    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
-    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&hi));
-    f[4 * i] = a.x; f[4 * i + 1] = a.y; f[4 * i + 2] = b.x; f[4 * i + 3] = b.y;
+    h[2 * i] = *reinterpret_cast<const uint32_t*>(&lo);
+    h[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&hi);
   }
+}
+// acc += a.lo * b.lo + a.hi * b.hi with fp16 inputs and an fp32 accumulator (mixed-precision FMA:
+// the products of two fp16 values are exact in fp32, so nothing is lost against converting first).
+__device__ __forceinline__ float fma2_f32_f16(uint32_t a, uint32_t b, float acc) {
+  asm("{\n.reg .b16 al, ah, bl, bh;\n"
+      "mov.b32 {al, ah}, %1;\n mov.b32 {bl, bh}, %2;\n"
+      "fma.rn.f32.f16 %0, al, bl, %0;\n"
+      "fma.rn.f32.f16 %0, ah, bh, %0;\n}"
+      : "+f"(acc) : "r"(a), "r"(b));
+  return acc;
+}
+// acc0 += v.lo * p, acc1 += v.hi * p (p an fp16 scalar replicated in both halves of pp).
+__device__ __forceinline__ void fma_pv(uint32_t v, uint32_t pp, float& acc0, float& acc1) {
+  asm("{\n.reg .b16 vl, vh, pl, ph;\n"
+      "mov.b32 {vl, vh}, %2;\n mov.b32 {pl, ph}, %3;\n"
+      "fma.rn.f32.f16 %0, vl, pl, %0;\n"
+      "fma.rn.f32.f16 %1, vh, ph, %1;\n}"
+      : "+f"(acc0), "+f"(acc1) : "r"(v), "r"(pp));
 }
 
 // G query heads of one kv head per pass; grid (kv_heads * passes, batch, splits).
@@ -64,12 +81,17 @@ paged_attention_fp8_kernel(const PaParams p) {
   int t_end = t_begin + p.tokens_per_split;
   if (t_end > ctx) t_end = ctx;
 
-  float q[G][16];
+  // q * scale as fp16 pairs: bf16 -> fp16 is exact except below fp16's normal range (|q| < 6e-5,
+  // where the product with a key no longer matters) and the scale is folded in before rounding
+  uint32_t q[G][8];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
     const __nv_bfloat16* qp = p.q + (int64_t)b * p.q_sb + (int64_t)(head0 + g) * p.q_sh + part * 16;
 #pragma unroll
-    for (int d = 0; d < 16; ++d) q[g][d] = __bfloat162float(qp[d]) * p.scale;
+    for (int d = 0; d < 8; ++d) {
+      const __half2 h = __floats2half2_rn(__bfloat162float(qp[2 * d]) * p.scale, __bfloat162float(qp[2 * d + 1]) * p.scale);
+      q[g][d] = *reinterpret_cast<const uint32_t*>(&h);
+    }
   }
   float m[G], l[G], acc[G][16];
 #pragma unroll
@@ -97,24 +119,31 @@ paged_attention_fp8_kernel(const PaParams p) {
 #pragma unroll
     for (int u = 0; u < PA_UNROLL; ++u) {
       const bool valid = t0 + u * PA_TOKENS_PER_STEP + sub < t_end;
-      float kf[16], vf[16];
-      fp8x16_to_float(kraw[u], kf);
-      fp8x16_to_float(vraw[u], vf);
+      uint32_t kh[8], vh[8];
+      fp8x16_to_half2(kraw[u], kh);
+      fp8x16_to_half2(vraw[u], vh);
 #pragma unroll
       for (int g = 0; g < G; ++g) {
         float s = 0.f;
 #pragma unroll
-        for (int d = 0; d < 16; ++d) s += q[g][d] * kf[d];
+        for (int d = 0; d < 8; ++d) s = fma2_f32_f16(q[g][d], kh[d], s);
         s += __shfl_xor_sync(0xffffffffu, s, 1);
         s += __shfl_xor_sync(0xffffffffu, s, 2);
         s += __shfl_xor_sync(0xffffffffu, s, 4);
         if (valid) {  // uniform over the eight lanes of a token
-          const float m_new = fmaxf(m[g], s);
-          const float corr = __expf(m[g] - m_new), pw = __expf(s - m_new);
-          l[g] = l[g] * corr + pw;
+          if (s > m[g]) {  // a new maximum (rare after the first tokens): rescale what is there
+            const float corr = __expf(m[g] - s);
+            l[g] *= corr;
 #pragma unroll
-          for (int d = 0; d < 16; ++d) acc[g][d] = acc[g][d] * corr + pw * vf[d];
-          m[g] = m_new;
+            for (int d = 0; d < 16; ++d) acc[g][d] *= corr;
+            m[g] = s;
+          }
+          const float pw = __expf(s - m[g]);
+          l[g] += pw;
+          const __half2 ph = __float2half2_rn(pw);
+          const uint32_t pp = *reinterpret_cast<const uint32_t*>(&ph);
+#pragma unroll
+          for (int d = 0; d < 8; ++d) fma_pv(vh[d], pp, acc[g][2 * d], acc[g][2 * d + 1]);
         }
       }
     }

@@ -5,10 +5,13 @@
 //   dHidden = dlogits x W     (A K-major, B MN-major) epilogue: store 16 bit / fp32
 //   dW     += dlogits^T x hidden (A MN-major, B MN-major) epilogue: fp32 accumulate / final 16-bit store
 //
-// CTA = 192 threads: warp 0 lane 0 issues TMA loads, warp 1 lane 0 issues MMAs (warp 1 also owns
-// the TMEM allocation), warps 2-5 are the epilogue (one TMEM lane quadrant each). Tile 128 x 256,
-// K block 64 (one 128-byte swizzle span), 4 stages of 48 KB. Every mbarrier wait is bounded: if
-// one runs out, the CTA records a code in the status word, stops, frees its TMEM and returns.
+// This file holds the single-CTA kernel and what it shares with the CTA-pair kernel
+// (tcgen05_gemm2.cuh, the default): PTX wrappers, descriptors, tensor maps and the epilogues.
+// CTA = 224 threads: lane 0 of warps 0 and 6 issue the TMA loads of operands A and B, warp 1 lane 0
+// issues the MMAs (warp 1 also owns the TMEM allocation), warps 2-5 are the epilogue (one TMEM lane
+// quadrant each). Tile 128 x 256, K block 64 (one 128-byte swizzle span), 4 stages of 48 KB. Every
+// mbarrier wait is bounded: if one runs out, the CTA records a code in the status word, stops,
+// frees its TMEM and returns.
 #pragma once
 #include <cuda.h>
 #include "common.cuh"
@@ -99,28 +102,13 @@ __device__ __forceinline__ void tmem_relinquish() {
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// Same instruction with the two shared-memory descriptors passed as 32-bit halves: the issuing
-// thread only adds a constant to the low words between MMAs (its serial instruction latency, not
-// the tensor pipe, is what bounds a k-block otherwise).
-__device__ __forceinline__ void umma_f16_split(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
-                                               uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\n.reg .b64 da, db;\n"
-      "mov.b64 da, {%1, %2};\n"
-      "mov.b64 db, {%3, %4};\n"
-      "setp.ne.b32 p, %6, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}"
-      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
-}
-// Halves of the 128-byte-swizzle descriptor (see make_smem_desc): the low word carries the start
-// address (16-byte units, bits 0-13) and LBO (bits 16-29); the high word SBO, version and swizzle.
+// Halves of the 64-bit shared-memory matrix descriptor, 128-byte swizzle: the low word carries the
+// start address (16-byte units, bits 0-13) and LBO (bits 16-29); the high word SBO (bits 32-45),
+// the sm_100 descriptor version (bit 46) and the swizzle mode (bits 61-63 = 2). K-major operand:
+// rows of 128 bytes, SBO = 1024 (8 rows), LBO unused. MN-major operand: 64-element (128-byte) runs
+// along M/N, LBO = byte distance between consecutive 64-element groups, SBO = byte distance between
+// groups of 8 K rows. The issuing thread keeps the halves in registers and only adds a constant to
+// the low word between MMAs.
 __device__ __forceinline__ uint32_t smem_desc_lo(uint32_t addr, uint32_t lbo_bytes) {
   return ((addr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
 }
@@ -179,19 +167,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
       : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, 128-byte swizzle. K-major operand: rows of 128 bytes, SBO = 1024
-// (8 rows), LBO unused. MN-major operand: 64-element (128-byte) runs along M/N, LBO = byte distance
-// between consecutive 64-element groups, SBO = byte distance between groups of 8 K rows.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
-  d |= (uint64_t)1 << 46;  // descriptor version for sm_100
-  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
-  return d;
-}
 
 __device__ __forceinline__ uint32_t pack16(float lo, float hi, int is_bf16) {
   if (is_bf16) {

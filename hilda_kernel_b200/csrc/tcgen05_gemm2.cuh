@@ -1,6 +1,6 @@
 // CTA-pair variant of the tcgen05 GEMM: two CTAs of a cluster (two SMs) work on one 256 x 256 tile
 // with `tcgen05.mma.cta_group::2`. Each CTA stages its own 128 rows of A and 128 of the 256 columns
-// of B (32 KB per stage instead of 48 KB, so 6 stages fit and the shared-memory operand traffic
+// of B (32 KB per stage instead of 48 KB, so 7 stages fit and the shared-memory operand traffic
 // per SM drops by a third); the leader CTA (cluster rank 0) issues the MMAs, which read both CTAs'
 // shared memory and write each CTA's half of the accumulator into that CTA's TMEM.
 //
@@ -54,13 +54,6 @@ __device__ __forceinline__ void g2_tmem_relinquish() {
 }
 __device__ __forceinline__ void g2_tmem_dealloc(uint32_t taddr, uint32_t ncols) {
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void g2_umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 // Arrive (once all prior MMAs of this thread retired) on the barrier at this shared-memory offset in
 // BOTH CTAs of the pair.

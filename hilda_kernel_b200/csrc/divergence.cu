@@ -27,6 +27,11 @@ __device__ __forceinline__ float dv_log(float x) {  // ln x through lg2.approx
   return y * DV_LN2;
 }
 
+// fp32 data: library expf / logf (the sums cancel to a small KL value, keep the margin); 16-bit
+// data: the approximate units.
+template <typename T> __device__ __forceinline__ float kl_exp(float x) { return sizeof(T) == 4 ? expf(x) : dv_exp(x); }
+template <typename T> __device__ __forceinline__ float kl_log(float x) { return sizeof(T) == 4 ? logf(x) : dv_log(x); }
+
 // ---------------------------------------------------------------------------------- KL divergence
 // loss_rows[row] = sum_j t * (log(max(t, eps)) - y)        (log_target == 0, kl_div.py:61-64)
 //                = sum_j exp(t) * (t - y)                   (log_target != 0, kl_div.py:57-59)
@@ -49,12 +54,12 @@ kl_div_fwd_kernel(const T* __restrict__ y_pred, const T* __restrict__ y_true, fl
         VT<T>::unpack(ld16_stream(yt + v * VEC), t);
 #pragma unroll
         for (int j = 0; j < VEC; ++j)
-          acc += log_target ? dv_exp(t[j]) * (t[j] - y[j]) : t[j] * (dv_log(fmaxf(t[j], eps)) - y[j]);
+          acc += log_target ? kl_exp<T>(t[j]) * (t[j] - y[j]) : t[j] * (kl_log<T>(fmaxf(t[j], eps)) - y[j]);
       }
     } else {
       for (int64_t c = threadIdx.x; c < n_cols; c += DV_THREADS) {
         const float y = VT<T>::load1(yp + c), t = VT<T>::load1(yt + c);
-        acc += log_target ? dv_exp(t) * (t - y) : t * (dv_log(fmaxf(t, eps)) - y);
+        acc += log_target ? kl_exp<T>(t) * (t - y) : t * (kl_log<T>(fmaxf(t, eps)) - y);
       }
     }
     acc = block_sum<DV_THREADS>(acc, red);
@@ -76,13 +81,13 @@ kl_div_bwd_kernel(const T* __restrict__ y_true, T* __restrict__ dy, const float*
     float t[VEC];
     VT<T>::unpack(ld16_stream(y_true + v * VEC), t);
 #pragma unroll
-    for (int j = 0; j < VEC; ++j) t[j] = -(log_target ? dv_exp(t[j]) : t[j]) * scale;
+    for (int j = 0; j < VEC; ++j) t[j] = -(log_target ? kl_exp<T>(t[j]) : t[j]) * scale;
     st16_stream(dy + v * VEC, VT<T>::pack(t));
   }
   // ragged tail (n not a multiple of the vector width)
   for (int64_t i = n_vec * VEC + (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
     const float t = VT<T>::load1(y_true + i);
-    VT<T>::store1(dy + i, -(log_target ? dv_exp(t) : t) * scale);
+    VT<T>::store1(dy + i, -(log_target ? kl_exp<T>(t) : t) * scale);
   }
 }
 
@@ -103,21 +108,26 @@ dv_sum_scale_kernel(const float* __restrict__ rows, int64_t n, float factor, flo
 //   else     : m = beta p + (1 - beta) q;  loss = beta p (y - log m) + (1 - beta) q (x - log m),
 //              dx = (1 - beta) q (x - log m)
 // (dx here is before the division by the number of non-ignored rows.)
+// PRECISE (fp32 data): library expf / logf, so that the fp32 tolerance of 1e-5 has margin where
+// x - log m nearly cancels; 16-bit data uses the approximate ex2 / lg2 units.
 struct JsdTerm { float loss, dx; };
+template <bool PRECISE>
 __device__ __forceinline__ JsdTerm jsd_term(float x, float y, float beta, int mode) {
+  auto ex = [](float v) { return PRECISE ? expf(v) : dv_exp(v); };
+  auto lg = [](float v) { return PRECISE ? logf(v) : dv_log(v); };
   JsdTerm r;
   if (mode == 0) {
-    const float p = dv_exp(y);
+    const float p = ex(y);
     r.loss = p * (y - x);
     r.dx = -p;
   } else if (mode == 1) {
-    const float q = dv_exp(x);
+    const float q = ex(x);
     r.loss = q * (x - y);
     r.dx = q * (x - y + 1.0f);
   } else {
-    const float q = dv_exp(x), p = dv_exp(y);
+    const float q = ex(x), p = ex(y);
     const float m = beta * p + (1.0f - beta) * q;
-    const float log_m = m > 0.f ? dv_log(m) : 0.f;  // both probabilities underflowed: the terms are 0, not 0 * inf
+    const float log_m = m > 0.f ? lg(m) : 0.f;  // both probabilities underflowed: the terms are 0, not 0 * inf
     const float qs = (1.0f - beta) * q * (x - log_m);
     r.loss = beta * p * (y - log_m) + qs;
     r.dx = qs;
@@ -151,23 +161,40 @@ jsd_rows_kernel(const T* __restrict__ X, const T* __restrict__ Y, T* __restrict_
         const uint4 z = make_uint4(0, 0, 0, 0);
         for (int64_t v = threadIdx.x; v < n_vec; v += DV_THREADS) st16_stream(d + v * VEC, z);
       } else {
-        for (int64_t v = threadIdx.x; v < n_vec; v += DV_THREADS) {
+        // two vectors of each operand in flight per thread and iteration
+        for (int64_t v = threadIdx.x; v < n_vec; v += 2 * DV_THREADS) {
+          const int64_t v2 = v + DV_THREADS;
+          const bool has2 = v2 < n_vec;
+          const uint4 xa = ld16_stream(x + v * VEC), ya = ld16_stream(y + v * VEC);
+          const uint4 xb = has2 ? ld16_stream(x + v2 * VEC) : make_uint4(0, 0, 0, 0);
+          const uint4 yb = has2 ? ld16_stream(y + v2 * VEC) : make_uint4(0, 0, 0, 0);
           float xf[VEC], yf[VEC];
-          VT<T>::unpack(ld16_stream(x + v * VEC), xf);
-          VT<T>::unpack(ld16_stream(y + v * VEC), yf);
+          VT<T>::unpack(xa, xf);
+          VT<T>::unpack(ya, yf);
 #pragma unroll
           for (int j = 0; j < VEC; ++j) {
-            const JsdTerm t = jsd_term(xf[j], yf[j], beta, mode);
+            const JsdTerm t = jsd_term<sizeof(T) == 4>(xf[j], yf[j], beta, mode);
             acc += t.loss;
             xf[j] = t.dx * inv_n;
           }
           st16_stream(d + v * VEC, VT<T>::pack(xf));
+          if (has2) {
+            VT<T>::unpack(xb, xf);
+            VT<T>::unpack(yb, yf);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) {
+              const JsdTerm t = jsd_term<sizeof(T) == 4>(xf[j], yf[j], beta, mode);
+              acc += t.loss;
+              xf[j] = t.dx * inv_n;
+            }
+            st16_stream(d + v2 * VEC, VT<T>::pack(xf));
+          }
         }
       }
     } else {
       for (int64_t c = threadIdx.x; c < V; c += DV_THREADS) {
         if (ignored) { VT<T>::store1(d + c, 0.f); continue; }
-        const JsdTerm t = jsd_term(VT<T>::load1(x + c), VT<T>::load1(y + c), beta, mode);
+        const JsdTerm t = jsd_term<sizeof(T) == 4>(VT<T>::load1(x + c), VT<T>::load1(y + c), beta, mode);
         acc += t.loss;
         VT<T>::store1(d + c, t.dx * inv_n);
       }
@@ -214,7 +241,7 @@ fljsd_rows_kernel(T* __restrict__ S, const T* __restrict__ Tt, int64_t pitch, co
 #pragma unroll
       for (int j = 0; j < VEC; ++j) {
         if (v * VEC + j < V) {
-          const JsdTerm e = jsd_term(fmaf(sf[j], inv_temp, -lse_s), fmaf(tf[j], inv_temp, -lse_t), beta, mode);
+          const JsdTerm e = jsd_term<sizeof(T) == 4>(fmaf(sf[j], inv_temp, -lse_s), fmaf(tf[j], inv_temp, -lse_t), beta, mode);
           acc_loss += e.loss;
           acc_dx += e.dx;
         }
@@ -230,7 +257,7 @@ fljsd_rows_kernel(T* __restrict__ S, const T* __restrict__ Tt, int64_t pitch, co
 #pragma unroll
       for (int j = 0; j < VEC; ++j) {
         const float x = fmaf(sf[j], inv_temp, -lse_s);
-        const JsdTerm e = jsd_term(x, fmaf(tf[j], inv_temp, -lse_t), beta, mode);
+        const JsdTerm e = jsd_term<sizeof(T) == 4>(x, fmaf(tf[j], inv_temp, -lse_t), beta, mode);
         sf[j] = (v * VEC + j < V) ? (e.dx - dv_exp(x) * acc_dx) * g : 0.f;
       }
       st16(s + v * VEC, VT<T>::pack(sf));

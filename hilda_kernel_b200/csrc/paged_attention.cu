@@ -20,7 +20,7 @@ namespace hilda {
 constexpr int PA_HEAD_DIM = 128;
 constexpr int PA_THREADS = 128;          // 4 warps x 4 tokens per step
 constexpr int PA_TOKENS_PER_STEP = 16;
-constexpr int PA_UNROLL = 2;             // steps whose loads are in flight together
+constexpr int PA_UNROLL = 2;             // steps whose loads are in flight together (4 measured slower)
 constexpr int PA_PARTIAL = PA_HEAD_DIM + 2;  // per (sequence, head, split): m, l, 128 unnormalised sums
 
 struct PaParams {

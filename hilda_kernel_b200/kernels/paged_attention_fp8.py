@@ -13,46 +13,47 @@ from .. import _lib as L
 from .._lib import device_guard
 
 
-def _normalize_query_shape(q):
-    if q.ndim == 4:
-        if q.shape[1] != 1:
-            raise ValueError(f'decode query must have shape [batch, 1, heads, dim], got {tuple(q.shape)}')
+def _as_decode_query(q):
+    """[batch, heads, dim] view of a decode query given as that or as [batch, 1, heads, dim];
+    the flag says whether the length-1 sequence axis has to be put back on the result."""
+    if q.ndim == 3:
+        return q, False
+    if q.ndim == 4 and q.shape[1] == 1:
         return q[:, 0], True
-    if q.ndim != 3:
-        raise ValueError(f'decode query must have shape [batch, heads, dim], got {tuple(q.shape)}')
-    return q, False
+    raise ValueError(f"a decode query is [batch, heads, dim] or [batch, 1, heads, dim]; got {tuple(q.shape)}")
 
 
-def _validate_inputs(q, k_cache, v_cache, block_tables, context_lens):
-    q_3d, restore_seq_dim = _normalize_query_shape(q)
-    if q_3d.dtype != torch.bfloat16:
-        raise TypeError(f'q must be bfloat16, got {q_3d.dtype}')
-    if k_cache.dtype != torch.float8_e4m3fn or v_cache.dtype != torch.float8_e4m3fn:
-        raise TypeError('k_cache and v_cache must use torch.float8_e4m3fn')
-    if k_cache.shape != v_cache.shape:
-        raise ValueError('k_cache and v_cache must have the same shape')
-    if k_cache.ndim != 4:
-        raise ValueError(f'k_cache must be [num_blocks, block_size, num_kv_heads, head_dim], got {tuple(k_cache.shape)}')
-    if block_tables.ndim != 2:
-        raise ValueError(f'block_tables must be [batch, max_num_blocks], got {tuple(block_tables.shape)}')
-    if context_lens.ndim != 1:
-        raise ValueError(f'context_lens must be [batch], got {tuple(context_lens.shape)}')
-    if not (q_3d.is_cuda and k_cache.is_cuda and v_cache.is_cuda and block_tables.is_cuda and context_lens.is_cuda):
-        raise ValueError('all tensors must be on CUDA')
-    batch, num_heads, head_dim = q_3d.shape
-    _, _, num_kv_heads, cache_head_dim = k_cache.shape
-    if batch != block_tables.shape[0] or batch != context_lens.shape[0]:
-        raise ValueError('batch dimension mismatch between q, block_tables and context_lens')
-    if head_dim != 128 or cache_head_dim != 128:
-        raise ValueError('this kernel currently requires head_dim=128')
-    if num_heads % num_kv_heads != 0:
-        raise ValueError('num_heads must be divisible by num_kv_heads for GQA')
-    return q_3d, restore_seq_dim
+def _check_decode_inputs(q, k_cache, v_cache, block_tables, context_lens):
+    """Same acceptance rules and exception types as the reference (paged_attention_fp8.py:104-137):
+    TypeError for dtypes, ValueError for shapes and devices."""
+    q3, had_seq_axis = _as_decode_query(q)
+    if q3.dtype is not torch.bfloat16:
+        raise TypeError(f"the query must be bfloat16, not {q3.dtype}")
+    for name, cache in (("k_cache", k_cache), ("v_cache", v_cache)):
+        if cache.dtype is not torch.float8_e4m3fn:
+            raise TypeError(f"{name} must be float8_e4m3fn, not {cache.dtype}")
+        if cache.ndim != 4:
+            raise ValueError(f"{name} is [blocks, block_size, kv_heads, head_dim]; got {tuple(cache.shape)}")
+    if v_cache.shape != k_cache.shape:
+        raise ValueError(f"k_cache {tuple(k_cache.shape)} and v_cache {tuple(v_cache.shape)} differ in shape")
+    if block_tables.ndim != 2 or context_lens.ndim != 1:
+        raise ValueError("block_tables is [batch, max_blocks] and context_lens is [batch]")
+    if not all(t.is_cuda for t in (q3, k_cache, v_cache, block_tables, context_lens)):
+        raise ValueError("every tensor has to live on a CUDA device")
+    n_seq, n_heads, dim = q3.shape
+    n_kv, cache_dim = k_cache.shape[2], k_cache.shape[3]
+    if block_tables.shape[0] != n_seq or context_lens.shape[0] != n_seq:
+        raise ValueError("q, block_tables and context_lens disagree on the batch size")
+    if (dim, cache_dim) != (128, 128):
+        raise ValueError("only head_dim = 128 is supported, as in the reference kernel")
+    if n_heads % n_kv:
+        raise ValueError("the number of query heads must be a multiple of the number of kv heads")
+    return q3, had_seq_axis
 
 
 @torch.inference_mode()
 def hilda_paged_attention_fp8_decode(q, k_cache, v_cache, block_tables, context_lens, scale):
-    q_3d, restore_seq_dim = _validate_inputs(q, k_cache, v_cache, block_tables, context_lens)
+    q_3d, restore_seq_dim = _check_decode_inputs(q, k_cache, v_cache, block_tables, context_lens)
     dev = q_3d.device
     if q_3d.stride(-1) != 1:
         q_3d = q_3d.contiguous()
@@ -84,19 +85,18 @@ def hilda_paged_attention_fp8_decode(q, k_cache, v_cache, block_tables, context_
 
 @torch.inference_mode()
 def reference_paged_attention_decode(q, k_cache, v_cache, block_tables, context_lens, scale):
-    """The plain PyTorch evaluation the reference exports beside its kernel
-    (paged_attention_fp8.py:191-221); runs on whatever device the tensors are on."""
-    q_3d, restore_seq_dim = _normalize_query_shape(q)
-    batch, num_heads, head_dim = q_3d.shape
-    _, block_size, num_kv_heads, _ = k_cache.shape
-    kv_of_head = torch.arange(num_heads, device=q_3d.device) // (num_heads // num_kv_heads)
-    out = torch.empty((batch, num_heads, head_dim), device=q_3d.device, dtype=torch.bfloat16)
-    for b in range(batch):
-        n_ctx = int(context_lens[b])
-        n_blk = -(-n_ctx // block_size)
-        ids = block_tables[b, :n_blk].long()
-        k = k_cache.index_select(0, ids).reshape(-1, num_kv_heads, head_dim)[:n_ctx].float().index_select(1, kv_of_head)
-        v = v_cache.index_select(0, ids).reshape(-1, num_kv_heads, head_dim)[:n_ctx].float().index_select(1, kv_of_head)
-        probs = (torch.einsum('hd,thd->ht', q_3d[b].float(), k) * scale).softmax(dim=-1)
-        out[b] = torch.einsum('ht,thd->hd', probs, v).to(torch.bfloat16)
-    return out.unsqueeze(1) if restore_seq_dim else out
+    """Plain PyTorch evaluation of the same quantity, exported beside the kernel as in the reference
+    (paged_attention_fp8.py:191-221): per sequence, gather its blocks, dequantise to fp32, softmax
+    attention of every query head over its kv head, result in bfloat16. Runs wherever the tensors are."""
+    q3, had_seq_axis = _as_decode_query(q)
+    n_seq, n_heads, dim = q3.shape
+    block_size, n_kv = k_cache.shape[1], k_cache.shape[2]
+    head_to_kv = torch.arange(n_heads, device=q3.device) // (n_heads // n_kv)
+    result = q3.new_empty((n_seq, n_heads, dim), dtype=torch.bfloat16)
+    for s_idx, n_ctx in enumerate(context_lens.tolist()):
+        blocks = block_tables[s_idx, : -(-n_ctx // block_size)].long()
+        keys = k_cache[blocks].reshape(-1, n_kv, dim)[:n_ctx].float()[:, head_to_kv]
+        vals = v_cache[blocks].reshape(-1, n_kv, dim)[:n_ctx].float()[:, head_to_kv]
+        weights = torch.softmax(torch.einsum('hd,thd->ht', q3[s_idx].float(), keys) * scale, dim=-1)
+        result[s_idx] = torch.einsum('ht,thd->hd', weights, vals).to(torch.bfloat16)
+    return result.unsqueeze(1) if had_seq_axis else result

@@ -123,7 +123,7 @@ int hilda_scale_rows(const void* in, void* out, const float* scale, int per_row,
  * device: hidden [BT, H], W [V, H], targets [BT] int64; bf16 or fp16; H % 8 == 0. reduction 0
  * none (per-row loss in loss_rows), 1 mean, 2 sum (fp32 scalar loss_out). dh [BT, H] and dw [V, H]
  * (both or neither) receive the gradients for a unit upstream gradient. Rows are processed in
- * chunks of chunk_rows (<= 0: library default, scratch <= 1 GiB); the chunk's logits live in the
+ * chunks of chunk_rows (<= 0: library default, scratch <= 1.25 GiB); the chunk's logits live in the
  * workspace, the full [BT, V] logits never exist. The call only enqueues work; afterwards the
  * int at workspace[0] is non-zero if a bounded device-side wait ran out (HILDA_ERR_DEVICE). */
 int64_t hilda_flce_default_chunk_rows(int64_t BT, int64_t H, int64_t V);

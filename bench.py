@@ -664,7 +664,29 @@ def run_ours(args):
     achieved = flops_rank * args.steps / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
     chunk_rows = FL.CHUNK_ROWS or int(lib.hilda_flce_default_chunk_rows(rows_alg, H, v1 - v0))
     n_chunks = -(-rows_alg // chunk_rows)
-    launches_per_step = 2 + 6 * n_chunks
+    # this library's kernels per step: count_valid, sum_rows, six per row chunk (logits GEMM, row_stats,
+    # finalize, dlogits, d-hidden GEMM, d-W GEMM), and the gather / scatter of the valid rows
+    compacted = FL.SKIP_IGNORED_ROWS and 0 < n_valid < BT
+    launches_per_step = 2 + 6 * n_chunks + (2 if compacted else 0)
+    # DRAM traffic per GEMM launch (average over the step's launches), scaled from the ncu capture of a
+    # smaller case (profiles/tcgen05_gemm_small_case_full.md): the logits and d-W GEMMs moved 1.10x and
+    # 1.05x their algorithmic bytes there, in proportion to the units; the d-hidden GEMM streams its
+    # dlogits operand once per wave of output tiles (1340 MB measured for 3.5 waves x 250 MB + W there),
+    # so it is modelled as waves x dlogits + W + output.
+    v_loc = v1 - v0
+    v_pad = -(-v_loc // 256) * 256
+    traffic_total, rows_left = 0.0, rows_alg
+    pair_tiles_n = -(-H // 256)
+    for c in range(n_chunks):
+        r = min(chunk_rows, rows_left)
+        rows_left -= r
+        scratch = r * v_pad * 2
+        traffic_total += 1.10 * (r * H * 2 + v_loc * H * 2 + scratch)                       # logits
+        waves = -(-(-(-r // 256) * pair_tiles_n) // 74)
+        traffic_total += waves * scratch + v_loc * H * 2 + r * H * 2                         # d hidden
+        dw_bytes = v_loc * H * (2 if n_chunks == 1 else (4 if c == 0 else (6 if c == n_chunks - 1 else 8)))
+        traffic_total += 1.05 * (scratch + r * H * 2 + dw_bytes)                             # d W
+    traffic_per_launch = traffic_total / (3 * n_chunks)
     result = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
@@ -685,7 +707,9 @@ def run_ours(args):
                      "gemm_ms_per_step": gemm_ms / args.steps, "gemm_launches_per_step": gemm_launches / args.steps,
                      "per_kind_ms_per_step": {"logits": ms_kind[0] / args.steps, "d_hidden": ms_kind[1] / args.steps,
                                               "d_weight": ms_kind[2] / args.steps},
-                     "traffic": None},
+                     "traffic": traffic_per_launch,
+                     "traffic_note": "bytes per GEMM launch, averaged over the step's launches; scaled from the ncu "
+                                     "capture of a smaller case (see profiles/tcgen05_gemm_small_case_full.md)"},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "input_pipelining": "double buffer: step i+1's inputs are copied on a second stream while step i computes",
                 "h2d_bytes_per_step": BT * H * 2 + BT * 8,
                 "d2h_bytes_per_step": 4, "steps": e2e_steps},

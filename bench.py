@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-ops]
 
-Workload (BASELINE config 4): hidden bf16 [16384, 4096] ~N(0,1); lm_head W bf16 [128256, 4096]
+Workload (the reference's FusedLinearCE benchmark shape): hidden bf16 [16384, 4096] ~N(0,1); lm_head W bf16 [128256, 4096]
 ~N(0, 0.02^2); targets uniform with 5 % ignore_index; mean reduction; gradients for hidden and W.
 Synthetic, seeded. One step = one forward+backward pass of the operator over the whole batch.
 With N > 1 (launched under torchrun) W is sharded by vocabulary rows over the ranks, hidden and
@@ -162,7 +162,7 @@ def run_reference(args):
 
 # ------------------------------------------------------------------------------------------------
 def per_op_table(device, pk, only=None, small=False):
-    """Device-timed GB/s of the six HBM-bound operators at their BASELINE configs (N = 1).
+    """Device-timed GB/s of the HBM-bound operators at the reference's benchmark shapes (N = 1).
     `only` restricts to one operator; `small` divides the row counts by 8 (for profiler captures)."""
     import hilda_kernel_b200._lib as L
     from hilda_kernel_b200.kernels import (cross_entropy as CE, fused_add_rms_norm as FA, grpo_loss as GR,
@@ -373,7 +373,7 @@ def per_op_table(device, pk, only=None, small=False):
 
 def sharded_ops_table(device, world, pk):
     """Row-sharded operators at N > 1 (every rank calls this): each rank runs the ordinary operator on
-    its 1/N of the BASELINE rows, plus the one small exchange the operator needs (parallel.py). Device
+    its 1/N of the benchmark rows, plus the one small exchange the operator needs (parallel.py). Device
     time, max over ranks; GB/s is the whole job's algorithmic bytes over that time (weak in rows per
     second, the batch is fixed so per-rank work shrinks with N)."""
     import torch.distributed as dist
@@ -762,8 +762,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-ops", action="store_true", help="skip the per-operator table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--bt", type=int, default=BT, help="tokens (default: the BASELINE workload)")
-    ap.add_argument("--vocab", type=int, default=V, help="vocabulary size (default: the BASELINE workload)")
+    ap.add_argument("--bt", type=int, default=BT, help="tokens (default: the headline workload)")
+    ap.add_argument("--vocab", type=int, default=V, help="vocabulary size (default: the headline workload)")
     ap.add_argument("--hidden", type=int, default=H)
     ap.add_argument("--no-skip-ignored", action="store_true",
                     help="run the GEMMs over ignored tokens too (default: their rows are compacted away)")

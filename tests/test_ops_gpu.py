@@ -51,7 +51,7 @@ def test_rms_norm_fwd_bwd(shape, dtype):
 
 
 def test_rms_norm_config1_fp32():
-    """BASELINE config 1: x [4096,4096] fp32 ~N(0,1), w = 1 + N(0,0.1), eps 1e-6, dY ~N(0,1), seed 0."""
+    """The reference's RMSNorm benchmark configuration: x [4096,4096] fp32 ~N(0,1), w = 1 + N(0,0.1), eps 1e-6, dY ~N(0,1), seed 0."""
     hk = ops()
     g = gen(0)
     x = torch.randn(4096, 4096, generator=g)

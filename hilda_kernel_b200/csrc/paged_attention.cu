@@ -6,7 +6,7 @@
 // HBM-bound on the KV cache, which is read ONCE per kv head: a CTA serves all query heads of one
 // (sequence, kv head) (the reference launches one program per query head and re-reads K / V for
 // every head of a GQA group) over a slice of the context (split-KV: slices are merged by a second
-// small kernel when there is more than one). Eight lanes share a token: each loads 16 bytes
+// small kernel when there is more than one). One warp per kv head; eight lanes share a token: each loads 16 bytes
 // (16 fp8) of its K row and its V row, so a warp touches four whole 128-byte rows per load; the
 // dot product is reduced over the eight lanes with three shuffles; every lane group keeps its own
 // online-softmax state (max, sum, 16 output dims per head), merged at the end.
@@ -18,8 +18,8 @@
 namespace hilda {
 
 constexpr int PA_HEAD_DIM = 128;
-constexpr int PA_THREADS = 128;          // 4 warps x 4 tokens per step
-constexpr int PA_TOKENS_PER_STEP = 16;
+constexpr int PA_MAX_WARPS = 8;          // head groups (kv head x pass) per CTA, one warp each
+constexpr int PA_TOKENS_PER_STEP = 4;    // tokens a warp takes per step (eight lanes each)
 constexpr int PA_UNROLL = 2;             // steps whose loads are in flight together (4 measured slower)
 constexpr int PA_PARTIAL = PA_HEAD_DIM + 2;  // per (sequence, head, split): m, l, 128 unnormalised sums
 
@@ -65,16 +65,22 @@ __device__ __forceinline__ void fma_pv(uint32_t v, uint32_t pp, float& acc0, flo
       : "+f"(acc0), "+f"(acc1) : "r"(v), "r"(pp));
 }
 
-// G query heads of one kv head per pass; grid (kv_heads * passes, batch, splits).
+// G query heads of one kv head per pass. Grid (CTAs of head groups, batch, context splits); one
+// WARP per head group (kv head x pass) and all the head groups of a sequence side by side in a
+// CTA: the warps of a CTA walk the same tokens at the same pace, so the 128-byte rows of the
+// different kv heads of a token (adjacent in the cache) are requested together and DRAM sees
+// kilobyte-sized pieces instead of isolated 128-byte ones.
 template <int G>
-__global__ void __launch_bounds__(PA_THREADS, G <= 2 ? 4 : 2)
+__global__ void __launch_bounds__(PA_MAX_WARPS * 32, G <= 2 ? 2 : 1)
 paged_attention_fp8_kernel(const PaParams p) {
   const int passes = p.group / G;
-  const int kv_head = blockIdx.x / passes, pass = blockIdx.x % passes;
-  const int b = blockIdx.y, split = blockIdx.z;
-  const int head0 = kv_head * p.group + pass * G;  // first query head of this CTA
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int sub = lane >> 3, part = lane & 7;      // token within the warp's step, 16-dim slice
+  const int hg = blockIdx.x * (blockDim.x >> 5) + warp;     // head group of this warp
+  if (hg >= p.n_kv_heads * passes) return;                   // no block-wide barrier below
+  const int kv_head = hg / passes, pass = hg % passes;
+  const int b = blockIdx.y, split = blockIdx.z;
+  const int head0 = kv_head * p.group + pass * G;  // first query head of this warp
+  const int sub = lane >> 3, part = lane & 7;      // token within the step, 16-dim slice
   int ctx = p.context_lens[b];
   if (ctx > p.max_blocks * p.block_size) ctx = p.max_blocks * p.block_size;  // never index past the block table
   const int t_begin = split * p.tokens_per_split;
@@ -101,21 +107,27 @@ paged_attention_fp8_kernel(const PaParams p) {
     for (int d = 0; d < 16; ++d) acc[g][d] = 0.f;
   }
   const int32_t* table = p.block_tables + (int64_t)b * p.bt_sb;
-  // PA_UNROLL steps of loads are issued before any of them is used: the kernel is bound by how many
-  // bytes it keeps in flight, not by arithmetic
-  for (int t0 = t_begin + warp * 4; t0 < t_end; t0 += PA_TOKENS_PER_STEP * PA_UNROLL) {
-    uint4 kraw[PA_UNROLL], vraw[PA_UNROLL];
+  // Software pipeline: the loads of the NEXT iteration (PA_UNROLL steps) are issued before this
+  // iteration's values are used, so that every warp always has loads in flight; the kernel is
+  // bound by the bytes it keeps in flight, not by arithmetic.
+  auto load_steps = [&](int t0, uint4* kr, uint4* vr) {
 #pragma unroll
     for (int u = 0; u < PA_UNROLL; ++u) {
       const int t = t0 + u * PA_TOKENS_PER_STEP + sub;
-      kraw[u] = make_uint4(0, 0, 0, 0); vraw[u] = make_uint4(0, 0, 0, 0);
+      kr[u] = make_uint4(0, 0, 0, 0); vr[u] = make_uint4(0, 0, 0, 0);
       if (t < t_end) {
         const int64_t blk = table[t / p.block_size];
         const int64_t tok = t % p.block_size;
-        kraw[u] = ld16_stream(p.k + blk * p.k_sblk + tok * p.k_stok + (int64_t)kv_head * p.k_sh + part * 16);
-        vraw[u] = ld16_stream(p.v + blk * p.v_sblk + tok * p.v_stok + (int64_t)kv_head * p.v_sh + part * 16);
+        kr[u] = ld16_stream(p.k + blk * p.k_sblk + tok * p.k_stok + (int64_t)kv_head * p.k_sh + part * 16);
+        vr[u] = ld16_stream(p.v + blk * p.v_sblk + tok * p.v_stok + (int64_t)kv_head * p.v_sh + part * 16);
       }
     }
+  };
+  constexpr int PA_ITER = PA_TOKENS_PER_STEP * PA_UNROLL;
+  uint4 kraw[PA_UNROLL], vraw[PA_UNROLL], knext[PA_UNROLL], vnext[PA_UNROLL];
+  load_steps(t_begin, kraw, vraw);
+  for (int t0 = t_begin; t0 < t_end; t0 += PA_ITER) {
+    load_steps(t0 + PA_ITER, knext, vnext);  // past t_end: nothing is loaded
 #pragma unroll
     for (int u = 0; u < PA_UNROLL; ++u) {
       const bool valid = t0 + u * PA_TOKENS_PER_STEP + sub < t_end;
@@ -147,6 +159,8 @@ paged_attention_fp8_kernel(const PaParams p) {
         }
       }
     }
+#pragma unroll
+    for (int u = 0; u < PA_UNROLL; ++u) { kraw[u] = knext[u]; vraw[u] = vnext[u]; }
   }
   // merge the four lane groups of the warp (lanes with the same 16-dim slice)
 #pragma unroll
@@ -167,37 +181,22 @@ paged_attention_fp8_kernel(const PaParams p) {
       m[g] = m_new;
     }
   }
-  // merge the warps through shared memory; warp 0 finishes
-  __shared__ float sm_acc[PA_THREADS / 32][G][PA_HEAD_DIM];
-  __shared__ float sm_ml[PA_THREADS / 32][G][2];
+  // lanes 0-7 hold the warp's result for their 16 dims
   if (sub == 0) {
 #pragma unroll
     for (int g = 0; g < G; ++g) {
+      const int head = head0 + g;
+      if (p.splits == 1) {
+        const float inv = l[g] > 0.f ? 1.0f / l[g] : 0.f;
+        __nv_bfloat16* dst = p.out + (int64_t)b * p.o_sb + (int64_t)head * p.o_sh + part * 16;
 #pragma unroll
-      for (int d = 0; d < 16; ++d) sm_acc[warp][g][part * 16 + d] = acc[g][d];
-      if (part == 0) { sm_ml[warp][g][0] = m[g]; sm_ml[warp][g][1] = l[g]; }
-    }
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < G * PA_HEAD_DIM; idx += PA_THREADS) {
-    const int g = idx / PA_HEAD_DIM, d = idx % PA_HEAD_DIM;
-    float mt = -INFINITY;
+        for (int d = 0; d < 16; ++d) dst[d] = __float2bfloat16_rn(acc[g][d] * inv);
+      } else {
+        float* dst = p.partial + (((int64_t)b * p.n_heads + head) * p.splits + split) * PA_PARTIAL;
 #pragma unroll
-    for (int w = 0; w < PA_THREADS / 32; ++w) mt = fmaxf(mt, sm_ml[w][g][0]);
-    float lt = 0.f, at = 0.f;
-#pragma unroll
-    for (int w = 0; w < PA_THREADS / 32; ++w) {
-      const float c = mt == -INFINITY ? 0.f : __expf(sm_ml[w][g][0] - mt);
-      lt += sm_ml[w][g][1] * c;
-      at += sm_acc[w][g][d] * c;
-    }
-    const int head = head0 + g;
-    if (p.splits == 1) {
-      p.out[(int64_t)b * p.o_sb + (int64_t)head * p.o_sh + d] = __float2bfloat16_rn(lt > 0.f ? at / lt : 0.f);
-    } else {
-      float* dst = p.partial + (((int64_t)b * p.n_heads + head) * p.splits + split) * PA_PARTIAL;
-      dst[2 + d] = at;
-      if (d == 0) { dst[0] = mt; dst[1] = lt; }
+        for (int d = 0; d < 16; ++d) dst[2 + part * 16 + d] = acc[g][d];
+        if (part == 0) { dst[0] = m[g]; dst[1] = l[g]; }
+      }
     }
   }
 }
@@ -219,18 +218,29 @@ paged_attention_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* _
   out[(int64_t)b * o_sb + (int64_t)head * o_sh + d] = __float2bfloat16_rn(lt > 0.f ? at / lt : 0.f);
 }
 
-// Split-KV plan: about eight CTAs per SM (two to four waves of resident CTAs, so that a partly
-// filled last wave costs little), slices of at least 256 tokens and a multiple of the tokens a CTA
-// takes per loop iteration.
-static void pa_plan(int64_t batch, int64_t n_kv_heads, int64_t passes, int64_t max_ctx, int* splits, int* tokens_per_split) {
-  const int64_t base = batch * n_kv_heads * passes;
-  int64_t want = (8 * (int64_t)sm_count() + base - 1) / (base > 0 ? base : 1);
-  const int64_t max_splits = (max_ctx + 255) / 256;
-  if (want > max_splits) want = max_splits;
-  if (want > 64) want = 64;
-  if (want < 1) want = 1;
-  int64_t tps = (max_ctx + want - 1) / want;
+// Split-KV plan: the number of context slices is the one (up to 64, slices of at least 256 tokens)
+// that best fills whole waves of resident CTAs (ctas_per_sm per SM, what the kernel's launch bounds
+// allow); more slices win ties above two waves, fewer below. tokens_per_split is a multiple of the
+// tokens a CTA takes per loop iteration.
+static void pa_plan(int64_t batch, int64_t n_kv_heads, int64_t passes, int64_t max_ctx, int ctas_per_sm, int* splits,
+                    int* tokens_per_split) {
   constexpr int64_t quantum = PA_TOKENS_PER_STEP * PA_UNROLL;
+  const int64_t hg_ctas = (n_kv_heads * passes + PA_MAX_WARPS - 1) / PA_MAX_WARPS;
+  const int64_t base = batch * hg_ctas > 0 ? batch * hg_ctas : 1;
+  const int64_t slots = (int64_t)sm_count() * ctas_per_sm;
+  int64_t max_splits = max_ctx / 256;
+  if (max_splits > 64) max_splits = 64;
+  if (max_splits < 1) max_splits = 1;
+  int64_t best = 1;
+  double best_score = -1.0;
+  for (int64_t s = 1; s <= max_splits; ++s) {
+    const int64_t ctas = base * s;
+    const int64_t waves = (ctas + slots - 1) / slots;
+    // efficiency of the wave fill, with a small preference for fewer slices (less merge work)
+    const double score = (double)ctas / (double)(waves * slots) - 0.002 * (double)s;
+    if (score > best_score) { best_score = score; best = s; }
+  }
+  int64_t tps = (max_ctx + best - 1) / best;
   tps = (tps + quantum - 1) / quantum * quantum;
   if (tps < quantum) tps = quantum;
   *splits = (int)((max_ctx + tps - 1) / tps);
@@ -251,7 +261,8 @@ int64_t hilda_paged_attention_fp8_workspace_bytes(int64_t batch, int64_t n_heads
   if (batch <= 0 || n_heads <= 0 || n_kv_heads <= 0 || max_blocks <= 0 || block_size <= 0 || n_heads % n_kv_heads) return 256;
   const int group = (int)(n_heads / n_kv_heads);
   int splits, tps;
-  pa_plan(batch, n_kv_heads, group / pa_group_unit(group), max_blocks * block_size, &splits, &tps);
+  const int unit = pa_group_unit(group);
+  pa_plan(batch, n_kv_heads, group / unit, max_blocks * block_size, unit <= 2 ? 2 : 1, &splits, &tps);
   return splits > 1 ? batch * n_heads * splits * PA_PARTIAL * 4 + 256 : 256;
 }
 
@@ -282,7 +293,7 @@ int hilda_paged_attention_fp8_decode(const void* q, int64_t q_sb, int64_t q_sh, 
   p.block_size = (int)block_size; p.max_blocks = (int)max_blocks;
   const int G = pa_group_unit(p.group);
   const int passes = p.group / G;
-  pa_plan(batch, n_kv_heads, passes, max_blocks * block_size, &p.splits, &p.tokens_per_split);
+  pa_plan(batch, n_kv_heads, passes, max_blocks * block_size, G <= 2 ? 2 : 1, &p.splits, &p.tokens_per_split);
   if (max_blocks == 0) { p.splits = 1; p.tokens_per_split = PA_TOKENS_PER_STEP; }
   p.partial = nullptr;
   if (p.splits > 1) {
@@ -290,10 +301,12 @@ int hilda_paged_attention_fp8_decode(const void* q, int64_t q_sb, int64_t q_sh, 
     p.partial = reinterpret_cast<float*>(workspace);
   }
   cudaStream_t st = (cudaStream_t)stream;
-  const dim3 grid((unsigned)(n_kv_heads * passes), (unsigned)batch, (unsigned)p.splits);
-  if (G == 4) paged_attention_fp8_kernel<4><<<grid, PA_THREADS, 0, st>>>(p);
-  else if (G == 2) paged_attention_fp8_kernel<2><<<grid, PA_THREADS, 0, st>>>(p);
-  else paged_attention_fp8_kernel<1><<<grid, PA_THREADS, 0, st>>>(p);
+  const int head_groups = (int)n_kv_heads * passes;
+  const int warps = head_groups < PA_MAX_WARPS ? head_groups : PA_MAX_WARPS;
+  const dim3 grid((unsigned)((head_groups + warps - 1) / warps), (unsigned)batch, (unsigned)p.splits);
+  if (G == 4) paged_attention_fp8_kernel<4><<<grid, warps * 32, 0, st>>>(p);
+  else if (G == 2) paged_attention_fp8_kernel<2><<<grid, warps * 32, 0, st>>>(p);
+  else paged_attention_fp8_kernel<1><<<grid, warps * 32, 0, st>>>(p);
   HILDA_LAUNCH_CHECK();
   if (p.splits > 1) {
     paged_attention_merge_kernel<<<dim3((unsigned)n_heads, (unsigned)batch), PA_HEAD_DIM, 0, st>>>(p.partial, p.out, o_sb, o_sh,

@@ -66,10 +66,11 @@ __device__ __forceinline__ void fma_pv(uint32_t v, uint32_t pp, float& acc0, flo
 }
 
 // G query heads of one kv head per pass. Grid (CTAs of head groups, batch, context splits); one
-// WARP per head group (kv head x pass) and all the head groups of a sequence side by side in a
-// CTA: the warps of a CTA walk the same tokens at the same pace, so the 128-byte rows of the
-// different kv heads of a token (adjacent in the cache) are requested together and DRAM sees
-// kilobyte-sized pieces instead of isolated 128-byte ones.
+// WARP per head group (kv head x pass), no cross-warp merge, and all the head groups of a sequence
+// side by side in a CTA, so that the 128-byte rows of the different kv heads of a token (adjacent
+// in the cache) are requested at about the same time. Measured against one CTA of four warps per
+// kv head with a shared-memory merge: 87 instead of 105 us at batch 32 x 4096 tokens; letting one
+// warp cover four adjacent kv heads of a single token (512 contiguous bytes per load) was slower.
 template <int G>
 __global__ void __launch_bounds__(PA_MAX_WARPS * 32, G <= 2 ? 2 : 1)
 paged_attention_fp8_kernel(const PaParams p) {

@@ -156,13 +156,15 @@ norm_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __r
     for (int j = 0; j < VEC; ++j) dw[i][j] = 0.f;
 
   for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
-    uint4 dyv[VPT], xv[VPT];
+    // all of the row's loads (dS too) are issued before the reduction: one DRAM round trip per row
+    uint4 dyv[VPT], xv[VPT], dsv[VPT];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = tid + i * THREADS;
       const bool ok = v < n_vec;
       dyv[i] = (ok && dY) ? ld16_stream(dY + row * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
       xv[i] = ok ? ld16_stream(X + row * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
+      dsv[i] = (ok && dS) ? ld16_stream(dS + row * n_cols + (int64_t)v * VEC) : make_uint4(0, 0, 0, 0);
     }
     const float rstd = RSTD[row];
     float acc = 0.f;
@@ -195,7 +197,7 @@ norm_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __r
         }
         if (dS != nullptr) {
           float ds[VEC];
-          VT<T>::unpack(ld16_stream(dS + row * n_cols + (int64_t)v * VEC), ds);
+          VT<T>::unpack(dsv[i], ds);
 #pragma unroll
           for (int j = 0; j < VEC; ++j) dx[j] += ds[j];
         }

@@ -373,9 +373,8 @@ def per_op_table(device, pk, only=None, small=False):
 
 def sharded_ops_table(device, world, pk):
     """Row-sharded operators at N > 1 (every rank calls this): each rank runs the ordinary operator on
-    its 1/N of the benchmark rows, plus the one small exchange the operator needs (parallel.py). Device
-    time, max over ranks; GB/s is the whole job's algorithmic bytes over that time (weak in rows per
-    second, the batch is fixed so per-rank work shrinks with N)."""
+    its shard of the rows, plus the one small exchange the operator needs (parallel.py). Device time,
+    max over ranks; GB/s is the whole job's algorithmic bytes over that time."""
     import torch.distributed as dist
     from hilda_kernel_b200 import parallel as P
     from hilda_kernel_b200.kernels import fused_add_rms_norm as FA
@@ -403,40 +402,47 @@ def sharded_ops_table(device, world, pk):
         out[name] = {"us": round(ms * 1e3, 1), "GB/s_whole_job": round(gbs), "GB/s_per_gpu": round(gbs / world),
                      "frac_of_measured_hbm_per_gpu": round(gbs / world / pk["hbm"], 3)}
 
-    # CrossEntropy, rows sharded: [8192 / N, 128256] per rank; exchange = (sum loss, n_valid)
-    n, v = 8192 // world, 128256
-    logits = (2 * rn(n, v)).bfloat16()
-    t = torch.randint(0, v, (n,), device=device, generator=g)
-    t[torch.randperm(n, device=device, generator=g)[: n // 10]] = -100
-    nv = torch.tensor([float((t != -100).sum())], device=device)
-    dist.all_reduce(nv)
-    add("cross_entropy_bf16_rows_sharded", timed(lambda: P.sharded_cross_entropy(logits, t)),
-        (float(nv[0]) + n * world) * v * 2)
-    del logits
-    # GRPO, sequences sharded: [16 / N, 1024, 151936] per rank; exchange = 4 floats
-    B, Lc, v = max(16 // world, 1), 1023, 151936
-    logits = (2 * rn(B, Lc + 1, v)).bfloat16()
-    ids = torch.randint(0, v, (B, Lc), device=device, generator=g)
-    lens = torch.randint(256, 1025, (B,), device=device, generator=g).clamp(max=Lc)
-    mask = (torch.arange(Lc, device=device)[None] < lens[:, None]).int()
-    old = rn(B, Lc) * 0.05 - 12
-    A = torch.tensor([float(mask.sum())], device=device)
-    dist.all_reduce(A)
-    add("grpo_bf16_sequences_sharded",
-        timed(lambda: P.sharded_grpo_loss(logits, ids, rn(B), old, old + 0.1, mask, 1.0, 0.1, 0.2, 0.2), iters=3),
-        (float(A[0]) + B * world * (Lc + 1)) * v * 2)
-    del logits
-    # FusedAddRMSNorm backward, rows sharded, dW all-reduced
-    rows = 16384 // world
-    x, r, w = rn(rows, 4096).bfloat16(), rn(rows, 4096).bfloat16(), (1 + 0.1 * rn(4096)).bfloat16()
-    dy, ds = rn(rows, 4096).bfloat16(), rn(rows, 4096).bfloat16()
-    _, s_, rstd = FA.fused_add_rms_norm_forward(x, r, w)
+    # Two partitionings of each operator: "strong" splits the benchmark's rows over the ranks (a rank
+    # holds 1/N of a fixed problem, so at N = 8 launch gaps and the small all-reduces weigh in),
+    # "weak" gives every rank a full benchmark-size shard of an N times larger batch (rows are
+    # independent: this is how the operators are sharded in data-parallel training).
+    for tag, div in (("", world), ("_weak", 1)):
+        # CrossEntropy, rows sharded: exchange = one int before the kernel, one float after
+        n, v = 8192 // div, 128256
+        logits = (2 * rn(n, v)).bfloat16()
+        t = torch.randint(0, v, (n,), device=device, generator=g)
+        t[torch.randperm(n, device=device, generator=g)[: n // 10]] = -100
+        nv = torch.tensor([float((t != -100).sum())], device=device)
+        dist.all_reduce(nv)
+        add("cross_entropy_bf16_rows_sharded" + tag, timed(lambda: P.sharded_cross_entropy(logits, t)),
+            (float(nv[0]) + n * world) * v * 2)
+        del logits
+        # GRPO, sequences sharded: exchange = 4 floats
+        B, Lc, v = max(16 // div, 1), 1023, 151936
+        logits = (2 * rn(B, Lc + 1, v)).bfloat16()
+        ids = torch.randint(0, v, (B, Lc), device=device, generator=g)
+        lens = torch.randint(256, 1025, (B,), device=device, generator=g).clamp(max=Lc)
+        mask = (torch.arange(Lc, device=device)[None] < lens[:, None]).int()
+        old = rn(B, Lc) * 0.05 - 12
+        adv = rn(B)
+        A = torch.tensor([float(mask.sum())], device=device)
+        dist.all_reduce(A)
+        add("grpo_bf16_sequences_sharded" + tag,
+            timed(lambda: P.sharded_grpo_loss(logits, ids, adv, old, old + 0.1, mask, 1.0, 0.1, 0.2, 0.2), iters=3),
+            (float(A[0]) + B * world * (Lc + 1)) * v * 2)
+        del logits
+        # FusedAddRMSNorm forward + backward, rows sharded, dW all-reduced
+        rows = 16384 // div
+        x, r, w = rn(rows, 4096).bfloat16(), rn(rows, 4096).bfloat16(), (1 + 0.1 * rn(4096)).bfloat16()
+        dy, ds = rn(rows, 4096).bfloat16(), rn(rows, 4096).bfloat16()
+        _, s_, rstd = FA.fused_add_rms_norm_forward(x, r, w)
 
-    def fa_step():
-        FA.fused_add_rms_norm_forward(x, r, w)
-        _, _, dw = FA.fused_add_rms_norm_backward(dy, ds, s_, w, rstd)
-        return P.allreduce_weight_grad(dw)
-    add("fused_add_rms_norm_bf16_rows_sharded_fwd+bwd", timed(fa_step), 8 * 16384 * 4096 * 2)
+        def fa_step():
+            FA.fused_add_rms_norm_forward(x, r, w)
+            _, _, dw = FA.fused_add_rms_norm_backward(dy, ds, s_, w, rstd)
+            return P.allreduce_weight_grad(dw)
+        add("fused_add_rms_norm_bf16_rows_sharded_fwd+bwd" + tag, timed(fa_step), 8 * rows * world * 4096 * 2)
+        del x, r, dy, ds, s_
     return out
 
 

@@ -561,7 +561,7 @@ def run_ours(args):
     w_local = weight[v0:v1].contiguous() if world > 1 else weight
     if world > 1:
         del weight
-    vp = VocabParallelFLCE(comm_dtype=torch.bfloat16) if world > 1 else None
+    vp = VocabParallelFLCE(comm_dtype=torch.bfloat16, overlap_sms=args.overlap_sms) if world > 1 else None
 
     def step():
         if world == 1:
@@ -699,7 +699,9 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "loss": loss,
         "config": {"workload": f"FusedLinearCE fwd+bwd, hidden [{BT},{H}] bf16, W [{V},{H}] bf16, 5% ignored, mean, "
                                f"grads for hidden and W", "BT": BT, "H": H, "V": V,
-                   "sharding": "single GPU" if world == 1 else f"W vocab-sharded over {world} ranks, hidden replicated",
+                   "sharding": "single GPU" if world == 1 else f"W vocab-sharded over {world} ranks, hidden replicated; "
+                   f"d(hidden) all-reduce beside the d(W) GEMM on {args.overlap_sms} SMs" if args.overlap_sms else
+                   f"W vocab-sharded over {world} ranks, hidden replicated",
                    "ignored_rows": f"compacted away before the GEMMs ({n_valid} of {BT} rows computed)"
                    if FL.SKIP_IGNORED_ROWS else "computed like any other row",
                    "row_chunks": n_chunks, "chunk_rows": chunk_rows, "l2": "inputs (1.05 GB W per pass) exceed the 126 MB L2; no flush needed"},
@@ -775,9 +777,14 @@ def main():
                     help="run the GEMMs over ignored tokens too (default: their rows are compacted away)")
     ap.add_argument("--only-op", default=None, help="time one operator of the per-op table and exit")
     ap.add_argument("--small", action="store_true", help="with --only-op: 1/8 of the rows (profiler captures)")
+    ap.add_argument("--overlap-sms", type=int, default=-1,
+                    help="N > 1: SMs the d(W) GEMM leaves to the d(hidden) all-reduce running beside it "
+                         "(0 = no overlap; default: 16 from 4 GPUs up, where the all-reduce is a visible share of the step)")
     ap.add_argument("--gemm-roles", action="store_true",
                     help="cycle counters of the tcgen05 GEMM roles on the FLCE shapes, beside cuBLAS, and exit")
     args = ap.parse_args()
+    if args.overlap_sms < 0:
+        args.overlap_sms = 16 if args.gpus >= 4 else 0
     BT, V, H = args.bt, args.vocab, args.hidden
     EMIT = _protect_stdout()
     if args.gemm_roles:

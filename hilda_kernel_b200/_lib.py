@@ -73,6 +73,7 @@ SIGNATURES = {
     "hilda_scatter_rows": (_i32, [_p, _p, _p, _i64, _i64, _i64, _p]),
     "hilda_gemm_set_pair": (None, [_i32]),
     "hilda_gemm_get_pair": (_i32, []),
+    "hilda_gemm_set_sm_limit": (None, [_i32]),
     "hilda_debug_gemm_set_order": (None, [_i32]),
     "hilda_gemm_set_probe": (None, [_p, _i32]),
     "hilda_debug_gemm": (_i32, [_p, _i64, _p, _i64, _p, _p, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _p, _p]),

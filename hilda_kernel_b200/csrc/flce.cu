@@ -132,6 +132,7 @@ move_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, const i
 static int g_debug_mfast = 1;
 static long long* g_gemm_probe = nullptr;
 static int g_gemm_dry = 0;
+static int g_gemm_sm_limit = 0;
 static int g_gemm_pair = []() {
   const char* e = getenv("HILDA_GEMM_PAIR");
   return e ? (atoi(e) & 7) : 7;
@@ -140,7 +141,7 @@ static int g_gemm_pair = []() {
 template <bool A_MN, bool B_MN, int EPI>
 static int run_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, GemmParams p, cudaStream_t st,
                     int kind_bit = 7) {
-  p.probe = g_gemm_probe; p.dry = g_gemm_dry;
+  p.probe = g_gemm_probe; p.dry = g_gemm_dry; p.sm_limit = g_gemm_sm_limit;
   if (g_gemm_pair & kind_bit) return launch_gemm2<A_MN, B_MN, EPI>(A, lda, B, ldb, p, st);
   return launch_gemm<A_MN, B_MN, EPI>(A, lda, B, ldb, p, st);
 }
@@ -509,6 +510,9 @@ int hilda_scatter_rows(const void* src, const int64_t* idx, void* dst, int64_t n
 // Select the GEMM variant per use: bit 0 = logits, bit 1 = d(hidden), bit 2 = d(W) run on CTA pairs
 // (cta_group::2, 256 x 256 tiles); a clear bit = single CTAs. hilda_debug_gemm uses pairs if any bit is set.
 void hilda_gemm_set_pair(int mask) { g_gemm_pair = mask & 7; }
+// The FLCE GEMMs launch on at most `sms` SMs (0 = all of them) until set back: a caller that runs a
+// collective on another stream beside a GEMM leaves it a few SMs this way.
+void hilda_gemm_set_sm_limit(int sms) { g_gemm_sm_limit = sms > 0 ? sms : 0; }
 // Tile walk order used by hilda_debug_gemm (1 = M first, 0 = N first).
 void hilda_debug_gemm_set_order(int m_fast) { g_debug_mfast = m_fast ? 1 : 0; }
 // Cycle counters of the single-CTA GEMM's role loops: device buffer of [sm_count][8] int64

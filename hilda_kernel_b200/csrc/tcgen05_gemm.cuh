@@ -48,6 +48,7 @@ struct GemmParams {
   float stat_scale;  // EPI_LOGITS_STATS: factor on the rounded logits before the base-2 (max, sum-exp)
   int* status;       // device word; non-zero = a bounded wait ran out
   uint32_t mn_lbo, mn_sbo;  // descriptor byte offsets for MN-major operands (8192, 1024)
+  int sm_limit;      // use at most this many SMs (0 = all): leaves room for a concurrent collective
   long long* probe;  // optional [gridDim.x][8] cycle counters of the role loops (null = off)
   int dry;           // measurement only: the producer signals "full" without loading (results are garbage)
 };
@@ -520,6 +521,7 @@ static int launch_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, G
   const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
   if (tiles > 0x7fffffffLL) return HILDA_ERR_SIZE;
   int grid = sm_count();
+  if (p.sm_limit > 0 && p.sm_limit < grid) grid = p.sm_limit;
   if (tiles < grid) grid = (int)tiles;
   kern<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(tmA, tmB, p);
   HILDA_LAUNCH_CHECK();

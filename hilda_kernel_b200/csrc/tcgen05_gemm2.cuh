@@ -301,6 +301,7 @@ static int launch_gemm2(const void* A, int64_t lda, const void* B, int64_t ldb, 
   const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
   if (tiles > 0x7fffffffLL) return HILDA_ERR_SIZE;
   int pairs = sm_count() / 2;
+  if (p.sm_limit > 0 && p.sm_limit / 2 < pairs) pairs = p.sm_limit / 2 > 0 ? p.sm_limit / 2 : 1;
   if (tiles < pairs) pairs = (int)tiles;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(pairs * 2), 1, 1);

@@ -107,10 +107,24 @@ class VocabParallelFLCE:
     """Vocab-parallel fused linear + cross entropy. Every rank holds ``weight_shard`` = rows
     [vocab_start, vocab_start + V_local) of the lm_head and the full hidden / targets."""
 
-    def __init__(self, group=None, comm_dtype=torch.float32):
+    def __init__(self, group=None, comm_dtype=torch.float32, overlap_sms=0):
         self.group = group
         self.comm_dtype = comm_dtype  # dtype of the d(hidden) all-reduce
+        # > 0: reduce each chunk's d(hidden) rows on a second stream beside that chunk's d(W) GEMM,
+        # which then leaves this many SMs to the collective (needs comm_dtype == the data dtype)
+        self.overlap_sms = int(overlap_sms)
         self.last_status = None
+        self._side = {}
+
+    def _side_stream(self, dev):
+        key = torch.device(dev).index
+        if key not in self._side:
+            self._side[key] = torch.cuda.Stream(device=dev)
+        return self._side[key]
+
+    @staticmethod
+    def _sm_count(dev):
+        return torch.cuda.get_device_properties(dev).multi_processor_count
 
     def __call__(self, hidden, weight_shard, targets, vocab_start, ignore_index=-100, reduction='mean',
                  compute_grad=True, chunk_rows=None, skip_ignored=None):
@@ -163,10 +177,14 @@ class VocabParallelFLCE:
             head = torch.zeros(2, dtype=torch.int32, device=dev)  # [status, n_valid]
             status_p, n_valid_p = head.data_ptr(), head.data_ptr() + 4
             L.check(lib.hilda_count_valid(L.ptr(targets), BT, int(ignore_index), n_valid_p, st), "count_valid")
-            dh32 = torch.empty(BT, H, dtype=torch.float32, device=dev) if (compute_grad and world > 1) else None
+            # partial sums of d(hidden) over the vocabulary shards: fp32 when they are reduced in fp32,
+            # otherwise written by the GEMM directly in the 16-bit dtype they are reduced in
+            reduce32 = compute_grad and world > 1 and self.comm_dtype == torch.float32
+            dh32 = torch.empty(BT, H, dtype=torch.float32, device=dev) if reduce32 else None
             dh = torch.empty_like(hidden) if compute_grad else None
             dw = torch.empty_like(weight_shard) if compute_grad else None
             dw32 = torch.empty(V, H, dtype=torch.float32, device=dev) if (compute_grad and n_chunks > 1) else None
+            reduced_rows = 0
             for c in range(n_chunks):
                 r0 = c * chunk_rows
                 rows = min(chunk_rows, BT - r0)
@@ -188,7 +206,7 @@ class VocabParallelFLCE:
                 L.check(lib.hilda_flce_dlogits(L.ptr(scratch), L.ptr(lse), L.ptr(tc), int(ignore_index),
                                                n_valid_p if reduction == 'mean' else None, rows, V, int(vocab_start),
                                                dt, st), "flce_dlogits")
-                if world > 1:
+                if reduce32:
                     L.check(lib.hilda_flce_grad_hidden(L.ptr(scratch), L.ptr(weight_shard), None,
                                                        dh32.data_ptr() + 4 * r0 * H, rows, H, V, dt, status_p, st),
                             "flce_grad_hidden")
@@ -197,12 +215,35 @@ class VocabParallelFLCE:
                                                        dh.data_ptr() + 2 * r0 * H, None, rows, H, V, dt, status_p, st),
                             "flce_grad_hidden")
                 mode = 3 if n_chunks == 1 else (0 if c == 0 else (2 if c == n_chunks - 1 else 1))
-                L.check(lib.hilda_flce_grad_weight(L.ptr(scratch), L.ptr(hc), L.ptr(dw32), L.ptr(dw), mode, rows, H, V,
-                                                   dt, status_p, st), "flce_grad_weight")
-            if compute_grad and world > 1:
-                buf = dh32 if self.comm_dtype == torch.float32 else dh32.to(self.comm_dtype)
-                dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=self.group)
-                dh.copy_(buf)
+                overlap = world > 1 and self.overlap_sms > 0 and not reduce32 and self.comm_dtype == dh.dtype
+                if overlap:
+                    # this chunk's rows of d(hidden) are complete: reduce them over the ranks on a
+                    # second stream while the d(W) GEMM runs here on all but `overlap_sms` SMs
+                    side = self._side_stream(dev)
+                    side.wait_stream(torch.cuda.current_stream(dev))
+                    with torch.cuda.stream(side):
+                        dist.all_reduce(dh[r0:r0 + rows], op=dist.ReduceOp.SUM, group=self.group)
+                    lib.hilda_gemm_set_sm_limit(self._sm_count(dev) - self.overlap_sms)
+                try:
+                    L.check(lib.hilda_flce_grad_weight(L.ptr(scratch), L.ptr(hc), L.ptr(dw32), L.ptr(dw), mode, rows, H,
+                                                       V, dt, status_p, st), "flce_grad_weight")
+                finally:
+                    if overlap:
+                        lib.hilda_gemm_set_sm_limit(0)
+                if overlap:
+                    reduced_rows = r0 + rows
+            if compute_grad and world > 1 and reduced_rows == BT:
+                torch.cuda.current_stream(dev).wait_stream(self._side_stream(dev))
+            elif compute_grad and world > 1:
+                if reduce32:
+                    dist.all_reduce(dh32, op=dist.ReduceOp.SUM, group=self.group)
+                    dh.copy_(dh32)
+                elif self.comm_dtype == dh.dtype:
+                    dist.all_reduce(dh, op=dist.ReduceOp.SUM, group=self.group)  # in place, no extra pass
+                else:
+                    buf = dh.to(self.comm_dtype)
+                    dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=self.group)
+                    dh.copy_(buf)
         self.last_status = head
         n_valid = head[1]
         if reduction == 'none':

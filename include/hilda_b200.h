@@ -189,6 +189,9 @@ int hilda_scatter_rows(const void* src, const int64_t* idx, void* dst, int64_t n
  * pairs when any bit is set. Initial value: environment HILDA_GEMM_PAIR, else the built-in default. */
 void hilda_gemm_set_pair(int mask);
 int hilda_gemm_get_pair(void);
+/* The FLCE GEMMs launch on at most `sms` SMs (0 = all) until set back; used to leave a few SMs to a
+ * collective that runs on another stream beside a GEMM. No counterpart in the reference. */
+void hilda_gemm_set_sm_limit(int sms);
 /* Tile walk order hilda_debug_gemm uses (1 = M first, 0 = N first); no counterpart in the reference. */
 void hilda_debug_gemm_set_order(int m_fast);
 /* Cycle counters of the GEMM kernels' role loops, written by every launch while set: device

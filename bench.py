@@ -333,10 +333,19 @@ def per_op_table(device, pk, only=None, small=False):
             bt = torch.randperm(batch * per_seq, device=device, generator=g).int().view(batch, per_seq)
             cl = torch.full((batch,), ctx, device=device, dtype=torch.int32)
             sets.append((q, kc, vc, bt, cl))
-        ms = timed([(lambda q=q, kc=kc, vc=vc, bt=bt, cl=cl: hilda_paged_attention_fp8_decode(q, kc, vc, bt, cl, 128 ** -0.5))
-                    for q, kc, vc, bt, cl in sets])
-        add("paged_attention_fp8_decode", ms, 2 * batch * ctx * nkv * 128, batch)
-        del sets
+        fns = [(lambda q=q, kc=kc, vc=vc, bt=bt, cl=cl: hilda_paged_attention_fp8_decode(q, kc, vc, bt, cl, 128 ** -0.5))
+               for q, kc, vc, bt, cl in sets]
+        add("paged_attention_fp8_decode", timed(fns), 2 * batch * ctx * nkv * 128, batch)
+        # the other of the two kernels behind the same entry point, for comparison
+        import hilda_kernel_b200._lib as L
+        default_path = L.lib().hilda_paged_attention_set_path(-1)
+        L.lib().hilda_paged_attention_set_path(1 - default_path)
+        try:
+            add("paged_attention_fp8_decode_" + ("cuda_core_kernel" if default_path == 1 else "tensor_core_kernel"),
+                timed(fns), 2 * batch * ctx * nkv * 128, batch)
+        finally:
+            L.lib().hilda_paged_attention_set_path(default_path)
+        del sets, fns
     # ---- the divergence losses (reference bench shapes: bench_kl_div.py:158, bench_jsd.py:175,
     # bench_fused_linear_jsd.py:165, in bf16)
     if want("kl_div"):

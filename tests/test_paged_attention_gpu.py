@@ -10,6 +10,15 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
+@pytest.fixture(params=[0, 1], ids=["cuda_core", "tensor_core"], autouse=True)
+def kernel_path(request):
+    """Every test runs on both kernels behind the entry point (hilda_paged_attention_set_path)."""
+    import hilda_kernel_b200._lib as L
+    old = L.lib().hilda_paged_attention_set_path(request.param)
+    yield request.param
+    L.lib().hilda_paged_attention_set_path(old)
+
+
 def gen(seed):
     return torch.Generator().manual_seed(seed)
 
@@ -41,7 +50,8 @@ def _check(q, kc, vc, bt, ctx, scale):
 @pytest.mark.parametrize("cfg", [
     (1, 16, 8, [512], 256), (8, 16, 8, [1024] * 8, 256), (4, 16, 8, [4096, 3000, 17, 1], 256),   # bench shapes (:47-49)
     (3, 8, 2, [37, 16, 5], 16), (2, 32, 8, [700, 300], 64), (2, 8, 8, [129, 128], 128), (2, 24, 8, [100, 260], 32),
-    (1, 5, 1, [1000], 16), (2, 12, 4, [0, 50], 16), (1, 64, 8, [333], 16)])
+    (1, 5, 1, [1000], 16), (2, 12, 4, [0, 50], 16), (1, 64, 8, [333], 16),
+    (2, 8, 2, [45, 9], 8), (2, 6, 2, [100, 31], 24), (1, 80, 8, [200], 32), (2, 7, 7, [15, 16], 16)])
 def test_paged_attention_decode(cfg):
     batch, n_heads, n_kv, ctx, bs = cfg
     q, kc, vc, bt, cl = _inputs(batch, n_heads, n_kv, ctx, bs)

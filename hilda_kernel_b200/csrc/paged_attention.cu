@@ -3,13 +3,16 @@
 // sequence, q [batch, heads, 128] bf16, K / V cache [blocks, block_size, kv_heads, 128] fp8, a block
 // table and a context length per sequence, output bf16.
 //
-// HBM-bound on the KV cache, which is read ONCE per kv head: a CTA serves all query heads of one
+// HBM-bound on the KV cache, which is read ONCE per kv head: a warp serves all query heads of one
 // (sequence, kv head) (the reference launches one program per query head and re-reads K / V for
 // every head of a GQA group) over a slice of the context (split-KV: slices are merged by a second
-// small kernel when there is more than one). One warp per kv head; eight lanes share a token: each loads 16 bytes
-// (16 fp8) of its K row and its V row, so a warp touches four whole 128-byte rows per load; the
-// dot product is reduced over the eight lanes with three shuffles; every lane group keeps its own
-// online-softmax state (max, sum, 16 output dims per head), merged at the end.
+// small kernel when there is more than one). Two kernels sit behind the entry point:
+//  * the tensor-core kernel (default, second half of this file): q.k and p.v as mma.sync over 16
+//    tokens x up to 8 query heads, K / V staged through shared memory with cp.async;
+//  * the CUDA-core kernel: eight lanes share a token, each loads 16 bytes (16 fp8) of its K row and
+//    its V row, so a warp touches four whole 128-byte rows per load; the dot product is reduced
+//    over the eight lanes with three shuffles; every lane group keeps its own online-softmax state
+//    (max, sum, 16 output dims per head), merged at the end. One FMA per (query head, element).
 #include <cuda_fp8.h>
 
 #include <cstdlib>
@@ -236,9 +239,12 @@ constexpr int PM_STAGES = 3;                         // steps in flight per warp
 constexpr int PM_STAGE_BYTES = 8 * 32 * 16;          // eight 16-byte pieces per lane
 constexpr int PM_WARP_SMEM = PM_STAGES * PM_STAGE_BYTES;
 
+// .ca, not .cg: with .cg (L1 bypassed) every lane's 16 bytes went to L2 as a sector request of its
+// own, two per 32-byte sector (measured: 16.8 M sectors for 8.4 M sectors of cache, 67 instead of
+// 58 us); through L1 the two halves of a sector are one request.
 __device__ __forceinline__ void pm_cp_async16(uint32_t smem_dst, const void* gsrc, bool valid) {
   const int n = valid ? 16 : 0;  // 0: the 16 bytes are zero-filled and nothing is read
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(n) : "memory");
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(n) : "memory");
 }
 __device__ __forceinline__ void pm_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -319,7 +325,11 @@ paged_attention_fp8_mma_kernel(const PaParams p) {
   const bool block16 = p.block_size % PM_STEP == 0;  // a step never straddles two cache blocks
 
   // Copies of step n into stage n % PM_STAGES (nothing past the slice's end: the caller still
-  // commits a group so that the group count stays in step with n).
+  // commits a group so that the group count stays in step with n). Steps are issued in order, so
+  // the cache block of the next step is tracked incrementally (no division per step) and its
+  // block-table entry is loaded one step early: the load is not on the path of the copies.
+  int is_blk = t_begin / p.block_size, is_tok = t_begin % p.block_size;  // position of the next step to issue
+  int64_t blk_ahead = t_begin < t_end ? table[is_blk] : 0;
   auto issue = [&](int n) {
     const int t0 = t_begin + n * PM_STEP;
     if (t0 >= t_end) return;
@@ -327,8 +337,11 @@ paged_attention_fp8_mma_kernel(const PaParams p) {
     const int tk[2] = {t0 + g, t0 + g + 8};
     const int tv[4] = {t0 + 2 * j, t0 + 2 * j + 1, t0 + 2 * j + 8, t0 + 2 * j + 9};
     if (block16) {
-      const int64_t blk = table[t0 / p.block_size];
-      const int tok0 = t0 % p.block_size;
+      const int64_t blk = blk_ahead;
+      const int tok0 = is_tok;
+      is_tok += PM_STEP;
+      if (is_tok >= p.block_size) { is_tok = 0; ++is_blk; }
+      if (t0 + PM_STEP < t_end) blk_ahead = table[is_blk];  // for the next call
       const uint8_t* kb = k_lane + blk * p.k_sblk + (int64_t)tok0 * p.k_stok;
       const uint8_t* vb = v_lane + blk * p.v_sblk + (int64_t)tok0 * p.v_stok;
 #pragma unroll
@@ -367,6 +380,7 @@ paged_attention_fp8_mma_kernel(const PaParams p) {
     const int t0 = t_begin + n * PM_STEP;
     // ---- S^T = K . Q^T
     float s4[4] = {0.f, 0.f, 0.f, 0.f};
+    float s4b[4] = {0.f, 0.f, 0.f, 0.f};  // second accumulator: two chains of four dependent MMAs instead of one of eight
     {
       const uint4 k0a = *reinterpret_cast<const uint4*>(sp), k0b = *reinterpret_cast<const uint4*>(sp + 512);
       const uint4 k1a = *reinterpret_cast<const uint4*>(sp + 1024), k1b = *reinterpret_cast<const uint4*>(sp + 1536);
@@ -374,9 +388,11 @@ paged_attention_fp8_mma_kernel(const PaParams p) {
       const uint32_t w1[8] = {k1a.x, k1a.y, k1a.z, k1a.w, k1b.x, k1b.y, k1b.z, k1b.w};  // token g + 8
 #pragma unroll
       for (int s = 0; s < 8; ++s)
-        mma_16816(s4, e4m3x2_to_f16x2(w0[s]), e4m3x2_to_f16x2(w1[s]), e4m3x2_to_f16x2(w0[s] >> 16),
+        mma_16816(s & 1 ? s4b : s4, e4m3x2_to_f16x2(w0[s]), e4m3x2_to_f16x2(w1[s]), e4m3x2_to_f16x2(w0[s] >> 16),
                   e4m3x2_to_f16x2(w1[s] >> 16), qf[s][0], qf[s][1]);
     }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) s4[c] += s4b[c];
     // ---- online softmax per head over this step's tokens (fp32)
     const bool ok0 = t0 + g < t_end, ok1 = t0 + g + 8 < t_end;
     const float sA0 = ok0 ? s4[0] : -INFINITY, sB0 = ok0 ? s4[1] : -INFINITY;
@@ -494,8 +510,8 @@ static void pa_plan(int64_t batch, int64_t n_kv_heads, int64_t passes, int64_t m
 static int pa_group_unit(int group) { return group % 4 == 0 ? 4 : (group % 2 == 0 ? 2 : 1); }
 constexpr int64_t PA_QUANTUM = PA_TOKENS_PER_STEP * PA_UNROLL;
 
-// 0: CUDA-core kernel, 1: tensor-core kernel (HILDA_PA_PATH, hilda_paged_attention_set_path)
-static int g_pa_path = []() { const char* e = getenv("HILDA_PA_PATH"); return e ? atoi(e) : 0; }();
+// 0: CUDA-core kernel, 1: tensor-core kernel, the default (HILDA_PA_PATH, hilda_paged_attention_set_path)
+static int g_pa_path = []() { const char* e = getenv("HILDA_PA_PATH"); return e ? atoi(e) : 1; }();
 
 // Tensor-core kernel: warps per CTA and CTAs per SM (shared memory and the 128-register bound of
 // its launch bounds both allow sixteen warps per SM).
@@ -569,10 +585,10 @@ int hilda_paged_attention_fp8_decode(const void* q, int64_t q_sb, int64_t q_sh, 
     int warps, ctas;
     pm_shape(head_groups, &warps, &ctas);
     const int smem = warps * PM_WARP_SMEM;
-    if (cudaFuncSetAttribute(paged_attention_fp8_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return HILDA_ERR_CUDA;
+    void (*kern)(const PaParams) = paged_attention_fp8_mma_kernel;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return HILDA_ERR_CUDA;
     const dim3 grid((unsigned)((head_groups + warps - 1) / warps), (unsigned)batch, (unsigned)p.splits);
-    paged_attention_fp8_mma_kernel<<<grid, warps * 32, smem, st>>>(p);
+    kern<<<grid, warps * 32, smem, st>>>(p);
     HILDA_LAUNCH_CHECK();
     if (p.splits > 1) {
       paged_attention_merge_kernel<<<dim3((unsigned)n_heads, (unsigned)batch), PA_HEAD_DIM, 0, st>>>(p.partial, p.out, o_sb, o_sh,

@@ -241,7 +241,9 @@ constexpr int PM_WARP_SMEM = PM_STAGES * PM_STAGE_BYTES;
 
 // .ca, not .cg: with .cg (L1 bypassed) every lane's 16 bytes went to L2 as a sector request of its
 // own, two per 32-byte sector (measured: 16.8 M sectors for 8.4 M sectors of cache, 67 instead of
-// 58 us); through L1 the two halves of a sector are one request.
+// 58 us); through L1 the two halves of a sector are one request. Staging whole 128-byte rows with
+// one cp.async.bulk per lane on an mbarrier per (warp, stage) instead was measured at 79 us: the
+// copy engine's rate of 128-byte requests, not the memory system, then sets the pace.
 __device__ __forceinline__ void pm_cp_async16(uint32_t smem_dst, const void* gsrc, bool valid) {
   const int n = valid ? 16 : 0;  // 0: the 16 bytes are zero-filled and nothing is read
   asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(n) : "memory");

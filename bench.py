@@ -788,12 +788,12 @@ def main():
     ap.add_argument("--small", action="store_true", help="with --only-op: 1/8 of the rows (profiler captures)")
     ap.add_argument("--overlap-sms", type=int, default=-1,
                     help="N > 1: SMs the d(W) GEMM leaves to the d(hidden) all-reduce running beside it "
-                         "(0 = no overlap; default: 16 from 4 GPUs up, where the all-reduce is a visible share of the step)")
+                         "(0 = no overlap; default: 16 at 8 GPUs, where the all-reduce's share of the step exceeds what the narrower GEMM costs)")
     ap.add_argument("--gemm-roles", action="store_true",
                     help="cycle counters of the tcgen05 GEMM roles on the FLCE shapes, beside cuBLAS, and exit")
     args = ap.parse_args()
     if args.overlap_sms < 0:
-        args.overlap_sms = 16 if args.gpus >= 4 else 0
+        args.overlap_sms = 16 if args.gpus >= 8 else 0
     BT, V, H = args.bt, args.vocab, args.hidden
     EMIT = _protect_stdout()
     if args.gemm_roles:

@@ -57,6 +57,7 @@ SIGNATURES = {
                                                 _p, _i64, _p, _p, _f32, _i64, _i64, _i64, _i64, _i64, _i64, _p]),
 
     "hilda_attn_res_fwd": (_i32, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _p]),
+    "hilda_attn_res_set_path": (_i32, [_i32]),
     "hilda_attn_res_bwd_workspace_bytes": (_i64, [_i64, _i64]),
     "hilda_attn_res_bwd": (_i32, [_p] * 10 + [_i64, _i64, _i64, _i32, _i32, _i32, _p]),
     "hilda_fljsd_dlogits": (_i32, [_p, _p, _p, _p, _p, _i64, _p, _i64, _p, _i64, _i64, _f32, _f32, _i32, _p]),

@@ -12,6 +12,8 @@
 // float atomics).
 #include <type_traits>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "hilda_b200.h"
 
@@ -542,6 +544,189 @@ attn_res_fwd_staged_kernel(const T* __restrict__ V, const void* __restrict__ w_q
   cp_async_wait<0>();
 }
 
+// ---- forward with the two reductions over D on the tensor cores (16-bit data and weights)
+// The staged kernel above spends most of its issue slots on the per-element work of the two
+// reductions over D (sum of squares; w_query . key) and on their warp reductions. Both are
+// contractions over D with the blocks as rows, so here they are mma.sync m16n8k16 (16-bit inputs,
+// fp32 accumulators; products of two 16-bit values are exact in fp32):
+//   Gram diagonal:  C[i][i] = sum_d v_i[d] v_i[d]     with A = B^T = the block rows,
+//   scores:         C[i][i] = sum_d key_i[d] wq[d]     with A = the keys, every column of B = w_query.
+// Lane (g, j) (g = lane / 4, j = lane % 4) reads row g (block g) of the staged token, 16 bytes at
+// a time; an MMA's contraction index may be any permutation of the dims, and because only the
+// diagonal C[g][g] is used (column g of B comes from the same lanes (g, .) as row g of A) the
+// permutation may even differ between rows: odd rows take the two 64-byte halves of a 128-byte
+// chunk in the opposite order, which keeps the eight lanes of a quarter warp on different banks.
+// The four registers of a 16-byte piece go into the A operand as they are (no register moves):
+// its words 0 and 2 are then row g of A, words 1 and 3 row g + 8, so a piece takes two MMAs, one
+// whose B holds the partners of words (0, 2) and whose rows 0-7 are kept, one with the partners of
+// words (1, 3) whose rows 8-15 are kept; the other half of each result is discarded.
+// The diagonal element of row g sits in lane (g, g / 2). The weighted sum over the blocks stays on
+// the CUDA cores, one 16-byte piece of every row per thread as above. Needs n_blocks <= 8,
+// D % 64 == 0, w_query and w_norm in the data's own 16-bit type (staged in shared memory).
+template <typename T> struct ArMma;
+template <> struct ArMma<__nv_bfloat16> {
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint4& a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
+  }
+  // bf16(bf16(v * rstd) * wn) for a pair, the reference's two roundings
+  static __device__ __forceinline__ uint32_t key_pair(uint32_t v, float rstd, uint32_t wn) {
+    const __nv_bfloat162 n = __floats2bfloat162_rn(__uint_as_float(v << 16) * rstd, __uint_as_float(v & 0xffff0000u) * rstd);
+    const __nv_bfloat162 k = __hmul2(n, *reinterpret_cast<const __nv_bfloat162*>(&wn));
+    return *reinterpret_cast<const uint32_t*>(&k);
+  }
+};
+template <> struct ArMma<__half> {
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint4& a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ uint32_t key_pair(uint32_t v, float rstd, uint32_t wn) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v));
+    const __half2 k = __hmul2(__floats2half2_rn(f.x * rstd, f.y * rstd), *reinterpret_cast<const __half2*>(&wn));
+    return *reinterpret_cast<const uint32_t*>(&k);
+  }
+};
+
+template <typename T, int THREADS, int VPT, int STAGES>
+__global__ void __launch_bounds__(THREADS, 1024 / THREADS)
+attn_res_fwd_mma_kernel(const T* __restrict__ V, const T* __restrict__ w_query, const T* __restrict__ w_norm,
+                        T* __restrict__ out, float* __restrict__ alpha, float* __restrict__ rstd_out, int n_blocks,
+                        int64_t n_tokens, int D, float eps) {
+  constexpr int VEC = VT<T>::N;  // 8
+  constexpr int NW = THREADS / 32;
+  extern __shared__ __align__(16) uint8_t ar_smem[];
+  __shared__ float part[NW][2 * AR_MAX_BLOCKS];
+  __shared__ float tot[2 * AR_MAX_BLOCKS];
+  T* stage0 = reinterpret_cast<T*>(ar_smem);
+  const int64_t stage_elems = (int64_t)n_blocks * D;
+  T* wq_s = stage0 + STAGES * stage_elems;  // the two weight vectors, after the stages
+  T* wn_s = wq_s + D;
+  const int n_vec = D / VEC;
+  const int n_chunks = D / 64;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int g = lane >> 2, j = lane & 3;
+  const bool row_ok = g < n_blocks;
+  const float inv_d = 1.0f / (float)D;
+  for (int v = threadIdx.x; v < n_vec; v += THREADS) {
+    *reinterpret_cast<uint4*>(wq_s + (int64_t)v * VEC) = *reinterpret_cast<const uint4*>(w_query + (int64_t)v * VEC);
+    *reinterpret_cast<uint4*>(wn_s + (int64_t)v * VEC) = *reinterpret_cast<const uint4*>(w_norm + (int64_t)v * VEC);
+  }
+  const int64_t blk_stride = n_tokens * (int64_t)D;
+  auto issue = [&](int64_t tok, int st) {  // pointers advance row by row: no 64-bit multiply per piece
+    if (tok < n_tokens) {
+      uint32_t dst = (uint32_t)__cvta_generic_to_shared(stage0 + st * stage_elems) + threadIdx.x * 16u;
+      const T* src = V + tok * D + (int64_t)threadIdx.x * VEC;
+#pragma unroll 8
+      for (int i = 0; i < n_blocks; ++i) {
+#pragma unroll
+        for (int jj = 0; jj < VPT; ++jj)
+          if (threadIdx.x + jj * THREADS < n_vec)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + jj * THREADS * 16u), "l"(src + jj * THREADS * VEC) : "memory");
+        dst += (uint32_t)D * (uint32_t)sizeof(T);
+        src += blk_stride;
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) issue((int64_t)blockIdx.x + (int64_t)s * gridDim.x, s);
+  int st = 0;
+  for (int64_t tok = blockIdx.x; tok < n_tokens; tok += gridDim.x) {
+    issue(tok + (int64_t)(STAGES - 1) * gridDim.x, (st + STAGES - 1) % STAGES);
+    cp_async_wait<STAGES - 1>();
+    __syncthreads();  // the reductions read pieces that other threads copied (and the weights, the first time)
+    const T* stage = stage0 + st * stage_elems;
+    const T* my_row = stage + (int64_t)(row_ok ? g : 0) * D;
+    // ---- all N sums of squares: the diagonal of the Gram matrix of this warp's chunks
+    {
+      float c02[4] = {0.f, 0.f, 0.f, 0.f}, c13[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int ch = wid; ch < n_chunks; ch += NW) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint4 r = make_uint4(0u, 0u, 0u, 0u);
+          if (row_ok) r = *reinterpret_cast<const uint4*>(my_row + ch * 64 + 8 * (j + 4 * ((g & 1) ^ c)));
+          ArMma<T>::mma(c02, r, r.x, r.z);
+          ArMma<T>::mma(c13, r, r.y, r.w);
+        }
+      }
+      if (row_ok && j == (g >> 1)) part[wid][g] = (g & 1) ? c02[1] + c13[3] : c02[0] + c13[2];
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < n_blocks) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) s += part[w][threadIdx.x];
+      tot[threadIdx.x] = rsqrtf(s * inv_d + eps);  // rstd of block threadIdx.x
+    }
+    __syncthreads();
+    // ---- all N scores: keys (two 16-bit roundings) against w_query
+    {
+      const float rstd = row_ok ? tot[g] : 0.f;
+      float c02[4] = {0.f, 0.f, 0.f, 0.f}, c13[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int ch = wid; ch < n_chunks; ch += NW) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int off = ch * 64 + 8 * (j + 4 * ((g & 1) ^ c));
+          uint4 r = make_uint4(0u, 0u, 0u, 0u);
+          if (row_ok) r = *reinterpret_cast<const uint4*>(my_row + off);
+          const uint4 n4 = *reinterpret_cast<const uint4*>(wn_s + off);
+          const uint4 q4 = *reinterpret_cast<const uint4*>(wq_s + off);  // A operand as loaded; the keys are B
+          ArMma<T>::mma(c02, q4, ArMma<T>::key_pair(r.x, rstd, n4.x), ArMma<T>::key_pair(r.z, rstd, n4.z));
+          ArMma<T>::mma(c13, q4, ArMma<T>::key_pair(r.y, rstd, n4.y), ArMma<T>::key_pair(r.w, rstd, n4.w));
+        }
+      }
+      if (row_ok && j == (g >> 1)) part[wid][AR_MAX_BLOCKS + g] = (g & 1) ? c02[1] + c13[3] : c02[0] + c13[2];
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {  // softmax over the blocks by one warp: alpha replaces the scores
+      float sc = -INFINITY;
+      if (lane < n_blocks) {
+        sc = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) sc += part[w][AR_MAX_BLOCKS + lane];
+      }
+      const float mx = warp_max(sc);
+      const float ex = lane < n_blocks ? __expf(sc - mx) : 0.f;
+      const float a = ex / warp_sum(ex);
+      if (lane < n_blocks) {
+        tot[AR_MAX_BLOCKS + lane] = a;
+        alpha[(int64_t)lane * n_tokens + tok] = a;
+        rstd_out[(int64_t)lane * n_tokens + tok] = tot[lane];
+      }
+    }
+    __syncthreads();
+    // ---- weighted sum over the blocks: this thread's 16-byte piece of every row
+    const T* rows = stage + (int64_t)threadIdx.x * VEC;
+    float acc[VPT][VEC];
+#pragma unroll
+    for (int jj = 0; jj < VPT; ++jj)
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[jj][e] = 0.f;
+#pragma unroll 8
+    for (int i = 0; i < n_blocks; ++i, rows += D) {
+      const float a = tot[AR_MAX_BLOCKS + i];
+#pragma unroll
+      for (int jj = 0; jj < VPT; ++jj) {
+        if (threadIdx.x + jj * THREADS < n_vec) {
+          float vf[VEC];
+          VT<T>::unpack(*reinterpret_cast<const uint4*>(rows + jj * THREADS * VEC), vf);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) acc[jj][e] += a * vf[e];
+        }
+      }
+    }
+#pragma unroll
+    for (int jj = 0; jj < VPT; ++jj) {
+      const int v = threadIdx.x + jj * THREADS;
+      if (v < n_vec) st16_stream(out + tok * D + (int64_t)v * VEC, VT<T>::pack(acc[jj]));
+    }
+    __syncthreads();  // part / tot are rewritten by the next token
+    st = (st + 1) % STAGES;
+  }
+  cp_async_wait<0>();
+}
+
 template <typename T, int THREADS, int VPT, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1024 / THREADS)
 attn_res_bwd_staged_kernel(const T* __restrict__ dOut, const T* __restrict__ V, const void* __restrict__ w_query, int wq_dt,
@@ -708,17 +893,21 @@ static ArPlan ar_plan(int D, int vec, bool aligned) {
 // Shared-memory plan of the staged kernels: `stages` stages of `rows` rows of D elements. Two CTAs per SM with two stages each when that fits,
 // otherwise one CTA with as many stages (at most 2) as fit; stages == 0: does not fit at all.
 struct ArStagePlan { int stages, ctas_per_sm; size_t smem; };
-static ArStagePlan ar_stage_plan(int rows, int D, int elem) {
+static ArStagePlan ar_stage_plan(int rows, int D, int elem, size_t extra = 0) {  // extra: bytes beside the stages
   const size_t cap = 227 * 1024 - 16 * 1024;  // leave room for the static shared memory and the per-CTA reserve
   const size_t stage = (size_t)rows * D * elem;
   ArStagePlan p{0, 1, 0};
-  if (2 * stage <= cap / 2) { p.stages = 2; p.ctas_per_sm = 2; }       // two CTAs per SM, double-buffered
-  else if (stage <= cap / 2) { p.stages = 1; p.ctas_per_sm = 2; }      // two CTAs per SM overlap each other
-  else if (2 * stage <= cap) { p.stages = 2; }
-  else if (stage <= cap) { p.stages = 1; }
-  p.smem = (size_t)p.stages * stage;
+  if (2 * stage + extra <= cap / 2) { p.stages = 2; p.ctas_per_sm = 2; }       // two CTAs per SM, double-buffered
+  else if (stage + extra <= cap / 2) { p.stages = 1; p.ctas_per_sm = 2; }      // two CTAs per SM overlap each other
+  else if (2 * stage + extra <= cap) { p.stages = 2; }
+  else if (stage + extra <= cap) { p.stages = 1; }
+  p.smem = (size_t)p.stages * stage + extra;
   return p;
 }
+
+// 0: forward reductions on the CUDA cores, 1: on the tensor cores where the shapes and dtypes allow
+// (HILDA_AR_PATH, hilda_attn_res_set_path)
+static int g_ar_path = []() { const char* e = getenv("HILDA_AR_PATH"); return e ? atoi(e) : 0; }();
 
 #define AR_DISPATCH_STAGED(T, CALL)                                                            \
   switch (plan.threads * 8 + plan.vpt) {                                                       \
@@ -745,6 +934,37 @@ static int ar_fwd_t(const void* V, const void* wq, int wq_dt, const void* wn, in
                                                          n_tokens, D, eps);
     HILDA_LAUNCH_CHECK();
     return HILDA_OK;
+  }
+  if constexpr (sizeof(T) == 2) {
+    const int dt = std::is_same<T, __nv_bfloat16>::value ? HILDA_BF16 : HILDA_F16;
+    ArStagePlan sp = ar_stage_plan(n_blocks, D, (int)sizeof(T), (size_t)2 * D * sizeof(T));
+    static const int force2 = []() { const char* e = getenv("HILDA_AR_STAGES"); return e ? atoi(e) : 0; }();
+    if (force2 == 2 && sp.stages == 1 && sp.ctas_per_sm == 2) {
+      sp.stages = 2; sp.ctas_per_sm = 1;
+      sp.smem = (size_t)2 * n_blocks * D * sizeof(T) + (size_t)2 * D * sizeof(T);
+    }
+    bool staged = g_ar_path == 1 && wq_dt == dt && wn_dt == dt && n_blocks <= 8 && D % 64 == 0 && aligned16(wq) &&
+                  aligned16(wn) && sp.stages > 0 && plan.threads >= 256;
+    if (staged) {
+      int64_t g = (int64_t)sm_count() * sp.ctas_per_sm;
+      if (g > n_tokens) g = n_tokens;
+#define AR_FWD_MMA(TT, TH, VP)                                                                                       \
+  do {                                                                                                                \
+    auto k1 = attn_res_fwd_mma_kernel<TT, TH, VP, 1>;                                                                 \
+    auto k2 = attn_res_fwd_mma_kernel<TT, TH, VP, 2>;                                                                 \
+    auto kern = sp.stages == 2 ? k2 : k1;                                                                             \
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sp.smem) != cudaSuccess)         \
+      return HILDA_ERR_CUDA;                                                                                          \
+    kern<<<(unsigned)g, TH, sp.smem, st>>>((const TT*)V, (const TT*)wq, (const TT*)wn, (TT*)out, alpha, rstd, n_blocks, \
+                                           n_tokens, D, eps);                                                         \
+  } while (0)
+      AR_DISPATCH_STAGED(T, AR_FWD_MMA)
+#undef AR_FWD_MMA
+      if (staged) {
+        HILDA_LAUNCH_CHECK();
+        return HILDA_OK;
+      }
+    }
   }
   const ArStagePlan sp = ar_stage_plan(n_blocks, D, (int)sizeof(T));
   bool staged = sp.stages > 0 && plan.threads >= 256;
@@ -872,6 +1092,15 @@ int hilda_attn_res_bwd(const void* d_out, const void* V, const void* w_query, co
     case HILDA_F16: return ar_bwd_t<__half>(d_out, V, w_query, wq_dtype, w_norm, wn_dtype, alpha, rstd, dV, dw_query, dw_norm, ws, (int)n_blocks, n_tokens, (int)D, st);
     default: return HILDA_ERR_DTYPE;
   }
+}
+
+// Forward kernel choice: 0 = reductions on the CUDA cores, 1 = on the tensor cores (16-bit data with
+// weights of the same type, at most 8 blocks, D a multiple of 64; other cases take 0). Returns the
+// previous choice.
+int hilda_attn_res_set_path(int path) {
+  const int old = g_ar_path;
+  if (path == 0 || path == 1) g_ar_path = path;
+  return old;
 }
 
 }  // extern "C"

@@ -250,6 +250,11 @@ int hilda_attn_res_bwd(const void* d_out, const void* V, const void* w_query, co
                        int64_t n_blocks, int64_t n_tokens, int64_t D, int dtype, int wq_dtype, int wn_dtype,
                        void* stream);
 
+/* Forward kernel of hilda_attn_res_fwd: 0 = the two reductions over D on the CUDA cores, 1 = on
+ * the tensor cores (mma.sync; 16-bit data with both weights in the same type, n_blocks <= 8,
+ * D % 64 == 0; anything else runs kernel 0). Environment: HILDA_AR_PATH. Returns the previous choice. */
+int hilda_attn_res_set_path(int path);
+
 /* ---- Paged FP8 decode attention ----------------------------------------------------------- */
 /* Replaces hilda_paged_attention_fp8_decode (kernels/paged_attention_fp8.py:141-188): one query
  * token per sequence. q [batch, n_heads, 128] bf16 (element strides q_sb, q_sh), k_cache / v_cache

@@ -11,6 +11,16 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
+@pytest.fixture(params=[0, 1], ids=["cuda_core_fwd", "tensor_core_fwd"], autouse=True)
+def forward_path(request):
+    """Every test runs with both forward kernels (hilda_attn_res_set_path); shapes and dtypes the
+    tensor-core kernel does not take fall back to the other inside the library."""
+    import hilda_kernel_b200._lib as L
+    old = L.lib().hilda_attn_res_set_path(request.param)
+    yield request.param
+    L.lib().hilda_attn_res_set_path(old)
+
+
 def gen(seed):
     return torch.Generator().manual_seed(seed)
 
@@ -34,7 +44,7 @@ def _oracle(V, wq, wn, dh):
 
 
 @pytest.mark.parametrize("dims", [(4, 2, 64, 4096), (8, 2, 64, 4096), (8, 1, 40, 8192), (16, 2, 9, 4096), (32, 1, 5, 1024),
-                                  (1, 2, 3, 512), (5, 2, 7, 256), (3, 1, 4, 100), (6, 2, 5, 33), (7, 1, 3, 20000)])
+                                  (1, 2, 3, 512), (5, 2, 7, 256), (3, 1, 4, 100), (6, 2, 5, 33), (7, 1, 3, 20000), (8, 1, 300, 2048), (3, 2, 50, 1600)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 def test_attn_res_fwd_bwd(dims, dtype):
     import hilda_kernel_b200 as hk

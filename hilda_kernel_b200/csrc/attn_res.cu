@@ -727,6 +727,159 @@ attn_res_fwd_mma_kernel(const T* __restrict__ V, const T* __restrict__ w_query, 
   cp_async_wait<0>();
 }
 
+// ---- backward with its two dot products over D on the tensor cores (16-bit data)
+// Per block i the backward needs da_i = <dh, v_i> and c_i = <w_query * w_norm, v_i>. Here both come
+// from one pair of MMAs per 16-byte piece: A = the block rows (row g of A = block g, the piece's
+// four registers as loaded), B's columns 0, 1, 2 = dh and the high and low 16-bit halves of
+// w_query * w_norm (split so that the product keeps fp32 accuracy), supplied by lane groups 0, 1, 2.
+// The elementwise pass needs only S[d] = sum over tokens and blocks of (ds_i rstd_i) v_i[d] for the
+// weight gradients (d w_query = w_norm * S, d w_norm = w_query * S), one FMA per element instead
+// of two products and two accumulators.
+template <typename T>
+__device__ __forceinline__ void ar_split16(float x, T& hi, T& lo) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    hi = __float2bfloat16_rn(x);
+    lo = __float2bfloat16_rn(x - __bfloat162float(hi));
+  } else {
+    hi = __float2half_rn(x);
+    lo = __float2half_rn(x - __half2float(hi));
+  }
+}
+
+template <typename T, int THREADS, int VPT, int STAGES>
+__global__ void __launch_bounds__(THREADS, 1024 / THREADS)
+attn_res_bwd_mma_kernel(const T* __restrict__ dOut, const T* __restrict__ V, const void* __restrict__ w_query, int wq_dt,
+                        const void* __restrict__ w_norm, int wn_dt, const float* __restrict__ alpha,
+                        const float* __restrict__ rstd_in, T* __restrict__ dV, float* __restrict__ partial, int n_blocks,
+                        int64_t n_tokens, int D) {
+  constexpr int VEC = VT<T>::N;  // 8
+  constexpr int NW = THREADS / 32;
+  extern __shared__ __align__(16) uint8_t ar_smem[];
+  __shared__ float part[NW][2 * AR_MAX_BLOCKS];
+  __shared__ float tot[2 * AR_MAX_BLOCKS];
+  __shared__ float ds_sh[AR_MAX_BLOCKS], a_sh[AR_MAX_BLOCKS], r_sh[AR_MAX_BLOCKS];
+  T* stage0 = reinterpret_cast<T*>(ar_smem);
+  const int64_t stage_elems = (int64_t)(n_blocks + 1) * D;  // N rows, then dh
+  // halves of w_query * w_norm; the first starts 64 bytes off a 128-byte boundary so that lane
+  // groups 0 (dh) and 1 (high halves) of a quarter warp read different banks
+  T* g_hi = stage0 + STAGES * stage_elems + 32;
+  T* g_lo = g_hi + D + 32;
+  const int n_vec = D / VEC;
+  const int n_chunks = D / 64;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int g = lane >> 2, j = lane & 3;
+  const bool row_ok = g < n_blocks;
+  const float inv_d = 1.0f / (float)D;
+  float g_w[VPT][VEC], S[VPT][VEC];
+#pragma unroll
+  for (int jj = 0; jj < VPT; ++jj) {
+    const int v = threadIdx.x + jj * THREADS;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      g_w[jj][e] = v < n_vec ? load_any(w_query, wq_dt, (int64_t)v * VEC + e) * load_any(w_norm, wn_dt, (int64_t)v * VEC + e) : 0.f;
+      S[jj][e] = 0.f;
+      if (v < n_vec) ar_split16<T>(g_w[jj][e], g_hi[(int64_t)v * VEC + e], g_lo[(int64_t)v * VEC + e]);
+    }
+  }
+  const int64_t blk_stride = n_tokens * (int64_t)D;
+  auto issue = [&](int64_t tok, int st) {
+    if (tok < n_tokens) {
+      T* dst = stage0 + st * stage_elems;
+      for (int i = 0; i <= n_blocks; ++i) {
+        const T* src = i < n_blocks ? V + (int64_t)i * blk_stride + tok * D : dOut + tok * D;
+#pragma unroll
+        for (int jj = 0; jj < VPT; ++jj) {
+          const int v = threadIdx.x + jj * THREADS;
+          if (v < n_vec) cp_async16(dst + (int64_t)i * D + (int64_t)v * VEC, src + (int64_t)v * VEC);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) issue((int64_t)blockIdx.x + (int64_t)s * gridDim.x, s);
+  int st = 0;
+  for (int64_t tok = blockIdx.x; tok < n_tokens; tok += gridDim.x) {
+    issue(tok + (int64_t)(STAGES - 1) * gridDim.x, (st + STAGES - 1) % STAGES);
+    if ((int)threadIdx.x < n_blocks) {
+      a_sh[threadIdx.x] = alpha[(int64_t)threadIdx.x * n_tokens + tok];
+      r_sh[threadIdx.x] = rstd_in[(int64_t)threadIdx.x * n_tokens + tok];
+    }
+    cp_async_wait<STAGES - 1>();
+    __syncthreads();  // the dot products read pieces that other threads copied (and g_hi / g_lo, the first time)
+    const T* rows = stage0 + st * stage_elems;
+    // ---- da_i and c_i for all blocks
+    {
+      const T* a_row = rows + (int64_t)(row_ok ? g : 0) * D;
+      const T* b_vec = g == 0 ? rows + (int64_t)n_blocks * D : (g == 1 ? g_hi : g_lo);  // this lane group's column of B
+      float c02[4] = {0.f, 0.f, 0.f, 0.f}, c13[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int ch = wid; ch < n_chunks; ch += NW) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int off = ch * 64 + 8 * (j + 4 * c);
+          uint4 r = make_uint4(0u, 0u, 0u, 0u), bv = make_uint4(0u, 0u, 0u, 0u);
+          if (row_ok) r = *reinterpret_cast<const uint4*>(a_row + off);
+          if (g < 3) bv = *reinterpret_cast<const uint4*>(b_vec + off);
+          ArMma<T>::mma(c02, r, bv.x, bv.z);  // rows 0-7: words 0 and 2 of the piece
+          ArMma<T>::mma(c13, r, bv.y, bv.w);  // rows 8-15: words 1 and 3
+        }
+      }
+      // lane (g, 0): columns 0 (da) and 1 (high half); lane (g, 1): column 2 (low half)
+      const float col_even = c02[0] + c13[2], col_odd = c02[1] + c13[3];
+      const float low = __shfl_down_sync(0xffffffffu, col_even, 1);
+      if (row_ok && j == 0) { part[wid][2 * g] = col_even; part[wid][2 * g + 1] = col_odd + low; }
+    }
+    reduce_parts<NW>(part, tot, 2 * n_blocks);
+    if (threadIdx.x < 32) {
+      const float a = lane < n_blocks ? a_sh[lane] : 0.f;
+      const float da = lane < n_blocks ? tot[2 * lane] : 0.f;
+      const float sum_a_da = warp_sum(a * da);
+      if (lane < n_blocks) ds_sh[lane] = a * (da - sum_a_da);
+    }
+    __syncthreads();
+    // ---- dV and the running sum for the weight gradients: this thread's piece of every row
+    float dh[VPT][VEC];
+#pragma unroll
+    for (int jj = 0; jj < VPT; ++jj) {
+      const int v = threadIdx.x + jj * THREADS;
+      VT<T>::unpack(v < n_vec ? *reinterpret_cast<const uint4*>(rows + (int64_t)n_blocks * D + (int64_t)v * VEC)
+                              : make_uint4(0, 0, 0, 0), dh[jj]);
+    }
+    for (int i = 0; i < n_blocks; ++i) {
+      const float a = a_sh[i], rstd = r_sh[i], ds = ds_sh[i];
+      const float coef_v = rstd * rstd * rstd * (ds * tot[2 * i + 1] * inv_d);
+      const float coef_g = rstd * ds;
+#pragma unroll
+      for (int jj = 0; jj < VPT; ++jj) {
+        const int v = threadIdx.x + jj * THREADS;
+        if (v >= n_vec) continue;
+        float vf[VEC], o[VEC];
+        VT<T>::unpack(*reinterpret_cast<const uint4*>(rows + (int64_t)i * D + (int64_t)v * VEC), vf);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          o[e] = a * dh[jj][e] + coef_g * g_w[jj][e] - coef_v * vf[e];
+          S[jj][e] += coef_g * vf[e];
+        }
+        st16_stream(dV + (int64_t)i * blk_stride + tok * D + (int64_t)v * VEC, VT<T>::pack(o));
+      }
+    }
+    __syncthreads();  // part / tot / ds_sh / a_sh / r_sh and (one stage) the rows are rewritten for the next token
+    st = (st + 1) % STAGES;
+  }
+  cp_async_wait<0>();
+  float* prow = partial + (int64_t)blockIdx.x * 2 * D;
+#pragma unroll
+  for (int jj = 0; jj < VPT; ++jj) {
+    const int v = threadIdx.x + jj * THREADS;
+    if (v >= n_vec) continue;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      prow[(int64_t)v * VEC + e] = load_any(w_norm, wn_dt, (int64_t)v * VEC + e) * S[jj][e];
+      prow[D + (int64_t)v * VEC + e] = load_any(w_query, wq_dt, (int64_t)v * VEC + e) * S[jj][e];
+    }
+  }
+}
+
 template <typename T, int THREADS, int VPT, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1024 / THREADS)
 attn_res_bwd_staged_kernel(const T* __restrict__ dOut, const T* __restrict__ V, const void* __restrict__ w_query, int wq_dt,
@@ -905,9 +1058,9 @@ static ArStagePlan ar_stage_plan(int rows, int D, int elem, size_t extra = 0) { 
   return p;
 }
 
-// 0: forward reductions on the CUDA cores, 1: on the tensor cores where the shapes and dtypes allow
+// 0: forward reductions on the CUDA cores, 1 (default): on the tensor cores where the shapes and dtypes allow
 // (HILDA_AR_PATH, hilda_attn_res_set_path)
-static int g_ar_path = []() { const char* e = getenv("HILDA_AR_PATH"); return e ? atoi(e) : 0; }();
+static int g_ar_path = []() { const char* e = getenv("HILDA_AR_PATH"); return e ? atoi(e) : 1; }();
 
 #define AR_DISPATCH_STAGED(T, CALL)                                                            \
   switch (plan.threads * 8 + plan.vpt) {                                                       \
@@ -937,12 +1090,7 @@ static int ar_fwd_t(const void* V, const void* wq, int wq_dt, const void* wn, in
   }
   if constexpr (sizeof(T) == 2) {
     const int dt = std::is_same<T, __nv_bfloat16>::value ? HILDA_BF16 : HILDA_F16;
-    ArStagePlan sp = ar_stage_plan(n_blocks, D, (int)sizeof(T), (size_t)2 * D * sizeof(T));
-    static const int force2 = []() { const char* e = getenv("HILDA_AR_STAGES"); return e ? atoi(e) : 0; }();
-    if (force2 == 2 && sp.stages == 1 && sp.ctas_per_sm == 2) {
-      sp.stages = 2; sp.ctas_per_sm = 1;
-      sp.smem = (size_t)2 * n_blocks * D * sizeof(T) + (size_t)2 * D * sizeof(T);
-    }
+    const ArStagePlan sp = ar_stage_plan(n_blocks, D, (int)sizeof(T), (size_t)2 * D * sizeof(T));
     bool staged = g_ar_path == 1 && wq_dt == dt && wn_dt == dt && n_blocks <= 8 && D % 64 == 0 && aligned16(wq) &&
                   aligned16(wn) && sp.stages > 0 && plan.threads >= 256;
     if (staged) {
@@ -1008,6 +1156,27 @@ static int ar_bwd_t(const void* dOut, const void* V, const void* wq, int wq_dt, 
     attn_res_bwd_generic_kernel<T><<<grid, 256, 0, st>>>((const T*)dOut, (const T*)V, wq, wq_dt, wn, wn_dt, alpha, rstd,
                                                          (T*)dV, workspace, n_blocks, n_tokens, D);
     done = true;
+  }
+  if constexpr (sizeof(T) == 2) {
+    const ArStagePlan sp = ar_stage_plan(n_blocks + 1, D, (int)sizeof(T), (size_t)(2 * D + 64) * sizeof(T));
+    bool staged = !done && g_ar_path == 1 && n_blocks <= 8 && D % 64 == 0 && sp.stages > 0 && plan.threads >= 256;
+    if (staged) {
+      int64_t g = (int64_t)sm_count() * sp.ctas_per_sm;  // never more than the workspace rows (2 per SM)
+      if (g > grid) g = grid;
+#define AR_BWD_MMA(TT, TH, VP)                                                                                        \
+  do {                                                                                                                \
+    auto k1 = attn_res_bwd_mma_kernel<TT, TH, VP, 1>;                                                                 \
+    auto k2 = attn_res_bwd_mma_kernel<TT, TH, VP, 2>;                                                                 \
+    auto kern = sp.stages == 2 ? k2 : k1;                                                                             \
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sp.smem) != cudaSuccess)         \
+      return HILDA_ERR_CUDA;                                                                                          \
+    kern<<<(unsigned)g, TH, sp.smem, st>>>((const TT*)dOut, (const TT*)V, wq, wq_dt, wn, wn_dt, alpha, rstd, (TT*)dV,   \
+                                           workspace, n_blocks, n_tokens, D);                                         \
+  } while (0)
+      AR_DISPATCH_STAGED(T, AR_BWD_MMA)
+#undef AR_BWD_MMA
+      if (staged) { grid = (int)g; done = true; }
+    }
   }
   const ArStagePlan sp = ar_stage_plan(n_blocks + 1, D, (int)sizeof(T));
   bool staged = !done && sp.stages > 0 && plan.threads >= 256;
@@ -1094,9 +1263,9 @@ int hilda_attn_res_bwd(const void* d_out, const void* V, const void* w_query, co
   }
 }
 
-// Forward kernel choice: 0 = reductions on the CUDA cores, 1 = on the tensor cores (16-bit data with
-// weights of the same type, at most 8 blocks, D a multiple of 64; other cases take 0). Returns the
-// previous choice.
+// Kernel choice: 0 = reductions over D on the CUDA cores, 1 = on the tensor cores (16-bit data, at
+// most 8 blocks, D a multiple of 64, for the forward weights of the data's type; other cases take
+// 0). Returns the previous choice.
 int hilda_attn_res_set_path(int path) {
   const int old = g_ar_path;
   if (path == 0 || path == 1) g_ar_path = path;

@@ -250,9 +250,10 @@ int hilda_attn_res_bwd(const void* d_out, const void* V, const void* w_query, co
                        int64_t n_blocks, int64_t n_tokens, int64_t D, int dtype, int wq_dtype, int wn_dtype,
                        void* stream);
 
-/* Forward kernel of hilda_attn_res_fwd: 0 = the two reductions over D on the CUDA cores, 1 = on
- * the tensor cores (mma.sync; 16-bit data with both weights in the same type, n_blocks <= 8,
- * D % 64 == 0; anything else runs kernel 0). Environment: HILDA_AR_PATH. Returns the previous choice. */
+/* Kernels of hilda_attn_res_fwd / _bwd: 0 = the reductions over D on the CUDA cores, 1 (default) =
+ * on the tensor cores (mma.sync; 16-bit data, n_blocks <= 8, D % 64 == 0, and for the forward both
+ * weights in the data's type; anything else runs the kernels of 0). Environment: HILDA_AR_PATH.
+ * Returns the previous choice. */
 int hilda_attn_res_set_path(int path);
 
 /* ---- Paged FP8 decode attention ----------------------------------------------------------- */

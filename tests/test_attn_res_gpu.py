@@ -11,10 +11,11 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-@pytest.fixture(params=[0, 1], ids=["cuda_core_fwd", "tensor_core_fwd"], autouse=True)
-def forward_path(request):
-    """Every test runs with both forward kernels (hilda_attn_res_set_path); shapes and dtypes the
-    tensor-core kernel does not take fall back to the other inside the library."""
+@pytest.fixture(params=[0, 1], ids=["cuda_core", "tensor_core"], autouse=True)
+def kernel_path(request):
+    """Every test runs with both sets of kernels (hilda_attn_res_set_path: the reductions over D on
+    the CUDA cores or on the tensor cores); shapes and dtypes the tensor-core kernels do not take
+    fall back to the others inside the library."""
     import hilda_kernel_b200._lib as L
     old = L.lib().hilda_attn_res_set_path(request.param)
     yield request.param

@@ -588,7 +588,8 @@ template <> struct ArMma<__half> {
   }
 };
 
-template <typename T, int THREADS, int VPT, int STAGES>
+// FULL8: n_blocks == 8, every row of the MMA's A operand is a block (no predicated loads).
+template <typename T, int THREADS, int VPT, int STAGES, bool FULL8>
 __global__ void __launch_bounds__(THREADS, 1024 / THREADS)
 attn_res_fwd_mma_kernel(const T* __restrict__ V, const T* __restrict__ w_query, const T* __restrict__ w_norm,
                         T* __restrict__ out, float* __restrict__ alpha, float* __restrict__ rstd_out, int n_blocks,
@@ -606,7 +607,9 @@ attn_res_fwd_mma_kernel(const T* __restrict__ V, const T* __restrict__ w_query, 
   const int n_chunks = D / 64;
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int g = lane >> 2, j = lane & 3;
-  const bool row_ok = g < n_blocks;
+  const bool row_ok = FULL8 || g < n_blocks;
+  const int my_chunks = n_chunks > wid ? (n_chunks - wid + NW - 1) / NW : 0;  // chunks wid, wid + NW, ... of this warp
+  const int piece0 = wid * 64 + 8 * (j + 4 * (g & 1)), piece1 = wid * 64 + 8 * (j + 4 * ((g & 1) ^ 1));  // the two halves of a chunk
   const float inv_d = 1.0f / (float)D;
   for (int v = threadIdx.x; v < n_vec; v += THREADS) {
     *reinterpret_cast<uint4*>(wq_s + (int64_t)v * VEC) = *reinterpret_cast<const uint4*>(w_query + (int64_t)v * VEC);
@@ -641,11 +644,12 @@ attn_res_fwd_mma_kernel(const T* __restrict__ V, const T* __restrict__ w_query, 
     // ---- all N sums of squares: the diagonal of the Gram matrix of this warp's chunks
     {
       float c02[4] = {0.f, 0.f, 0.f, 0.f}, c13[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int ch = wid; ch < n_chunks; ch += NW) {
+#pragma unroll 4
+      for (int it = 0; it < my_chunks; ++it) {
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint4 r = make_uint4(0u, 0u, 0u, 0u);
-          if (row_ok) r = *reinterpret_cast<const uint4*>(my_row + ch * 64 + 8 * (j + 4 * ((g & 1) ^ c)));
+          if (row_ok) r = *reinterpret_cast<const uint4*>(my_row + (c ? piece1 : piece0) + it * (NW * 64));
           ArMma<T>::mma(c02, r, r.x, r.z);
           ArMma<T>::mma(c13, r, r.y, r.w);
         }
@@ -664,10 +668,11 @@ attn_res_fwd_mma_kernel(const T* __restrict__ V, const T* __restrict__ w_query, 
     {
       const float rstd = row_ok ? tot[g] : 0.f;
       float c02[4] = {0.f, 0.f, 0.f, 0.f}, c13[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int ch = wid; ch < n_chunks; ch += NW) {
+#pragma unroll 4
+      for (int it = 0; it < my_chunks; ++it) {
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          const int off = ch * 64 + 8 * (j + 4 * ((g & 1) ^ c));
+          const int off = (c ? piece1 : piece0) + it * (NW * 64);
           uint4 r = make_uint4(0u, 0u, 0u, 0u);
           if (row_ok) r = *reinterpret_cast<const uint4*>(my_row + off);
           const uint4 n4 = *reinterpret_cast<const uint4*>(wn_s + off);
@@ -746,7 +751,7 @@ __device__ __forceinline__ void ar_split16(float x, T& hi, T& lo) {
   }
 }
 
-template <typename T, int THREADS, int VPT, int STAGES>
+template <typename T, int THREADS, int VPT, int STAGES, bool FULL8>
 __global__ void __launch_bounds__(THREADS, 1024 / THREADS)
 attn_res_bwd_mma_kernel(const T* __restrict__ dOut, const T* __restrict__ V, const void* __restrict__ w_query, int wq_dt,
                         const void* __restrict__ w_norm, int wn_dt, const float* __restrict__ alpha,
@@ -768,7 +773,8 @@ attn_res_bwd_mma_kernel(const T* __restrict__ dOut, const T* __restrict__ V, con
   const int n_chunks = D / 64;
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int g = lane >> 2, j = lane & 3;
-  const bool row_ok = g < n_blocks;
+  const bool row_ok = FULL8 || g < n_blocks;
+  const int my_chunks = n_chunks > wid ? (n_chunks - wid + NW - 1) / NW : 0;  // chunks wid, wid + NW, ... of this warp
   const float inv_d = 1.0f / (float)D;
   float g_w[VPT][VEC], S[VPT][VEC];
 #pragma unroll
@@ -813,10 +819,11 @@ attn_res_bwd_mma_kernel(const T* __restrict__ dOut, const T* __restrict__ V, con
       const T* a_row = rows + (int64_t)(row_ok ? g : 0) * D;
       const T* b_vec = g == 0 ? rows + (int64_t)n_blocks * D : (g == 1 ? g_hi : g_lo);  // this lane group's column of B
       float c02[4] = {0.f, 0.f, 0.f, 0.f}, c13[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int ch = wid; ch < n_chunks; ch += NW) {
+#pragma unroll 4
+      for (int it = 0; it < my_chunks; ++it) {
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          const int off = ch * 64 + 8 * (j + 4 * c);
+          const int off = wid * 64 + 8 * (j + 4 * c) + it * (NW * 64);
           uint4 r = make_uint4(0u, 0u, 0u, 0u), bv = make_uint4(0u, 0u, 0u, 0u);
           if (row_ok) r = *reinterpret_cast<const uint4*>(a_row + off);
           if (g < 3) bv = *reinterpret_cast<const uint4*>(b_vec + off);
@@ -1098,9 +1105,10 @@ static int ar_fwd_t(const void* V, const void* wq, int wq_dt, const void* wn, in
       if (g > n_tokens) g = n_tokens;
 #define AR_FWD_MMA(TT, TH, VP)                                                                                       \
   do {                                                                                                                \
-    auto k1 = attn_res_fwd_mma_kernel<TT, TH, VP, 1>;                                                                 \
-    auto k2 = attn_res_fwd_mma_kernel<TT, TH, VP, 2>;                                                                 \
-    auto kern = sp.stages == 2 ? k2 : k1;                                                                             \
+    auto kern = sp.stages == 2 ? (n_blocks == 8 ? attn_res_fwd_mma_kernel<TT, TH, VP, 2, true>                        \
+                                                : attn_res_fwd_mma_kernel<TT, TH, VP, 2, false>)                      \
+                               : (n_blocks == 8 ? attn_res_fwd_mma_kernel<TT, TH, VP, 1, true>                        \
+                                                : attn_res_fwd_mma_kernel<TT, TH, VP, 1, false>);                     \
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sp.smem) != cudaSuccess)         \
       return HILDA_ERR_CUDA;                                                                                          \
     kern<<<(unsigned)g, TH, sp.smem, st>>>((const TT*)V, (const TT*)wq, (const TT*)wn, (TT*)out, alpha, rstd, n_blocks, \
@@ -1165,9 +1173,10 @@ static int ar_bwd_t(const void* dOut, const void* V, const void* wq, int wq_dt, 
       if (g > grid) g = grid;
 #define AR_BWD_MMA(TT, TH, VP)                                                                                        \
   do {                                                                                                                \
-    auto k1 = attn_res_bwd_mma_kernel<TT, TH, VP, 1>;                                                                 \
-    auto k2 = attn_res_bwd_mma_kernel<TT, TH, VP, 2>;                                                                 \
-    auto kern = sp.stages == 2 ? k2 : k1;                                                                             \
+    auto kern = sp.stages == 2 ? (n_blocks == 8 ? attn_res_bwd_mma_kernel<TT, TH, VP, 2, true>                        \
+                                                : attn_res_bwd_mma_kernel<TT, TH, VP, 2, false>)                      \
+                               : (n_blocks == 8 ? attn_res_bwd_mma_kernel<TT, TH, VP, 1, true>                        \
+                                                : attn_res_bwd_mma_kernel<TT, TH, VP, 1, false>);                     \
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sp.smem) != cudaSuccess)         \
       return HILDA_ERR_CUDA;                                                                                          \
     kern<<<(unsigned)g, TH, sp.smem, st>>>((const TT*)dOut, (const TT*)V, wq, wq_dt, wn, wn_dt, alpha, rstd, (TT*)dV,   \

@@ -608,6 +608,7 @@ attn_res_fwd_mma_kernel(const T* __restrict__ V, const T* __restrict__ w_query, 
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int g = lane >> 2, j = lane & 3;
   const bool row_ok = FULL8 || g < n_blocks;
+  const int nb = FULL8 ? 8 : n_blocks;  // a constant trip count unrolls the loops over the blocks
   const int my_chunks = n_chunks > wid ? (n_chunks - wid + NW - 1) / NW : 0;  // chunks wid, wid + NW, ... of this warp
   const int piece0 = wid * 64 + 8 * (j + 4 * (g & 1)), piece1 = wid * 64 + 8 * (j + 4 * ((g & 1) ^ 1));  // the two halves of a chunk
   const float inv_d = 1.0f / (float)D;
@@ -621,7 +622,7 @@ attn_res_fwd_mma_kernel(const T* __restrict__ V, const T* __restrict__ w_query, 
       uint32_t dst = (uint32_t)__cvta_generic_to_shared(stage0 + st * stage_elems) + threadIdx.x * 16u;
       const T* src = V + tok * D + (int64_t)threadIdx.x * VEC;
 #pragma unroll 8
-      for (int i = 0; i < n_blocks; ++i) {
+      for (int i = 0; i < nb; ++i) {
 #pragma unroll
         for (int jj = 0; jj < VPT; ++jj)
           if (threadIdx.x + jj * THREADS < n_vec)
@@ -709,7 +710,7 @@ attn_res_fwd_mma_kernel(const T* __restrict__ V, const T* __restrict__ w_query, 
 #pragma unroll
       for (int e = 0; e < VEC; ++e) acc[jj][e] = 0.f;
 #pragma unroll 8
-    for (int i = 0; i < n_blocks; ++i, rows += D) {
+    for (int i = 0; i < nb; ++i, rows += D) {
       const float a = tot[AR_MAX_BLOCKS + i];
 #pragma unroll
       for (int jj = 0; jj < VPT; ++jj) {
@@ -774,6 +775,7 @@ attn_res_bwd_mma_kernel(const T* __restrict__ dOut, const T* __restrict__ V, con
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int g = lane >> 2, j = lane & 3;
   const bool row_ok = FULL8 || g < n_blocks;
+  const int nb = FULL8 ? 8 : n_blocks;  // a constant trip count unrolls the loops over the blocks
   const int my_chunks = n_chunks > wid ? (n_chunks - wid + NW - 1) / NW : 0;  // chunks wid, wid + NW, ... of this warp
   const float inv_d = 1.0f / (float)D;
   float g_w[VPT][VEC], S[VPT][VEC];
@@ -791,8 +793,9 @@ attn_res_bwd_mma_kernel(const T* __restrict__ dOut, const T* __restrict__ V, con
   auto issue = [&](int64_t tok, int st) {
     if (tok < n_tokens) {
       T* dst = stage0 + st * stage_elems;
-      for (int i = 0; i <= n_blocks; ++i) {
-        const T* src = i < n_blocks ? V + (int64_t)i * blk_stride + tok * D : dOut + tok * D;
+#pragma unroll 9
+      for (int i = 0; i <= nb; ++i) {
+        const T* src = i < nb ? V + (int64_t)i * blk_stride + tok * D : dOut + tok * D;
 #pragma unroll
         for (int jj = 0; jj < VPT; ++jj) {
           const int v = threadIdx.x + jj * THREADS;
@@ -852,7 +855,8 @@ attn_res_bwd_mma_kernel(const T* __restrict__ dOut, const T* __restrict__ V, con
       VT<T>::unpack(v < n_vec ? *reinterpret_cast<const uint4*>(rows + (int64_t)n_blocks * D + (int64_t)v * VEC)
                               : make_uint4(0, 0, 0, 0), dh[jj]);
     }
-    for (int i = 0; i < n_blocks; ++i) {
+#pragma unroll 8
+    for (int i = 0; i < nb; ++i) {
       const float a = a_sh[i], rstd = r_sh[i], ds = ds_sh[i];
       const float coef_v = rstd * rstd * rstd * (ds * tot[2 * i + 1] * inv_d);
       const float coef_g = rstd * ds;

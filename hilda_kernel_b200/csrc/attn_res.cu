@@ -588,7 +588,8 @@ template <> struct ArMma<__half> {
   }
 };
 
-// FULL8: n_blocks == 8, every row of the MMA's A operand is a block (no predicated loads).
+// FULL8: n_blocks == 8 (every row of the MMA's A operand is a block: no predicated loads, constant
+// trip counts) and D == 8 * THREADS * VPT (every thread has a piece: no bounds checks).
 template <typename T, int THREADS, int VPT, int STAGES, bool FULL8>
 __global__ void __launch_bounds__(THREADS, 1024 / THREADS)
 attn_res_fwd_mma_kernel(const T* __restrict__ V, const T* __restrict__ w_query, const T* __restrict__ w_norm,
@@ -625,7 +626,7 @@ attn_res_fwd_mma_kernel(const T* __restrict__ V, const T* __restrict__ w_query, 
       for (int i = 0; i < nb; ++i) {
 #pragma unroll
         for (int jj = 0; jj < VPT; ++jj)
-          if (threadIdx.x + jj * THREADS < n_vec)
+          if (FULL8 || threadIdx.x + jj * THREADS < n_vec)
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + jj * THREADS * 16u), "l"(src + jj * THREADS * VEC) : "memory");
         dst += (uint32_t)D * (uint32_t)sizeof(T);
         src += blk_stride;
@@ -714,7 +715,7 @@ attn_res_fwd_mma_kernel(const T* __restrict__ V, const T* __restrict__ w_query, 
       const float a = tot[AR_MAX_BLOCKS + i];
 #pragma unroll
       for (int jj = 0; jj < VPT; ++jj) {
-        if (threadIdx.x + jj * THREADS < n_vec) {
+        if (FULL8 || threadIdx.x + jj * THREADS < n_vec) {
           float vf[VEC];
           VT<T>::unpack(*reinterpret_cast<const uint4*>(rows + jj * THREADS * VEC), vf);
 #pragma unroll
@@ -725,7 +726,7 @@ attn_res_fwd_mma_kernel(const T* __restrict__ V, const T* __restrict__ w_query, 
 #pragma unroll
     for (int jj = 0; jj < VPT; ++jj) {
       const int v = threadIdx.x + jj * THREADS;
-      if (v < n_vec) st16_stream(out + tok * D + (int64_t)v * VEC, VT<T>::pack(acc[jj]));
+      if (FULL8 || v < n_vec) st16_stream(out + tok * D + (int64_t)v * VEC, VT<T>::pack(acc[jj]));
     }
     __syncthreads();  // part / tot are rewritten by the next token
     st = (st + 1) % STAGES;
@@ -784,9 +785,9 @@ attn_res_bwd_mma_kernel(const T* __restrict__ dOut, const T* __restrict__ V, con
     const int v = threadIdx.x + jj * THREADS;
 #pragma unroll
     for (int e = 0; e < VEC; ++e) {
-      g_w[jj][e] = v < n_vec ? load_any(w_query, wq_dt, (int64_t)v * VEC + e) * load_any(w_norm, wn_dt, (int64_t)v * VEC + e) : 0.f;
+      g_w[jj][e] = FULL8 || v < n_vec ? load_any(w_query, wq_dt, (int64_t)v * VEC + e) * load_any(w_norm, wn_dt, (int64_t)v * VEC + e) : 0.f;
       S[jj][e] = 0.f;
-      if (v < n_vec) ar_split16<T>(g_w[jj][e], g_hi[(int64_t)v * VEC + e], g_lo[(int64_t)v * VEC + e]);
+      if (FULL8 || v < n_vec) ar_split16<T>(g_w[jj][e], g_hi[(int64_t)v * VEC + e], g_lo[(int64_t)v * VEC + e]);
     }
   }
   const int64_t blk_stride = n_tokens * (int64_t)D;
@@ -799,7 +800,7 @@ attn_res_bwd_mma_kernel(const T* __restrict__ dOut, const T* __restrict__ V, con
 #pragma unroll
         for (int jj = 0; jj < VPT; ++jj) {
           const int v = threadIdx.x + jj * THREADS;
-          if (v < n_vec) cp_async16(dst + (int64_t)i * D + (int64_t)v * VEC, src + (int64_t)v * VEC);
+          if (FULL8 || v < n_vec) cp_async16(dst + (int64_t)i * D + (int64_t)v * VEC, src + (int64_t)v * VEC);
         }
       }
     }
@@ -852,7 +853,7 @@ attn_res_bwd_mma_kernel(const T* __restrict__ dOut, const T* __restrict__ V, con
 #pragma unroll
     for (int jj = 0; jj < VPT; ++jj) {
       const int v = threadIdx.x + jj * THREADS;
-      VT<T>::unpack(v < n_vec ? *reinterpret_cast<const uint4*>(rows + (int64_t)n_blocks * D + (int64_t)v * VEC)
+      VT<T>::unpack(FULL8 || v < n_vec ? *reinterpret_cast<const uint4*>(rows + (int64_t)n_blocks * D + (int64_t)v * VEC)
                               : make_uint4(0, 0, 0, 0), dh[jj]);
     }
 #pragma unroll 8
@@ -863,7 +864,7 @@ attn_res_bwd_mma_kernel(const T* __restrict__ dOut, const T* __restrict__ V, con
 #pragma unroll
       for (int jj = 0; jj < VPT; ++jj) {
         const int v = threadIdx.x + jj * THREADS;
-        if (v >= n_vec) continue;
+        if (!FULL8 && v >= n_vec) continue;
         float vf[VEC], o[VEC];
         VT<T>::unpack(*reinterpret_cast<const uint4*>(rows + (int64_t)i * D + (int64_t)v * VEC), vf);
 #pragma unroll
@@ -882,7 +883,7 @@ attn_res_bwd_mma_kernel(const T* __restrict__ dOut, const T* __restrict__ V, con
 #pragma unroll
   for (int jj = 0; jj < VPT; ++jj) {
     const int v = threadIdx.x + jj * THREADS;
-    if (v >= n_vec) continue;
+    if (!FULL8 && v >= n_vec) continue;
 #pragma unroll
     for (int e = 0; e < VEC; ++e) {
       prow[(int64_t)v * VEC + e] = load_any(w_norm, wn_dt, (int64_t)v * VEC + e) * S[jj][e];
@@ -1109,9 +1110,10 @@ static int ar_fwd_t(const void* V, const void* wq, int wq_dt, const void* wn, in
       if (g > n_tokens) g = n_tokens;
 #define AR_FWD_MMA(TT, TH, VP)                                                                                       \
   do {                                                                                                                \
-    auto kern = sp.stages == 2 ? (n_blocks == 8 ? attn_res_fwd_mma_kernel<TT, TH, VP, 2, true>                        \
+    const bool full8 = n_blocks == 8 && D == 8 * TH * VP;                                                             \
+    auto kern = sp.stages == 2 ? (full8 ? attn_res_fwd_mma_kernel<TT, TH, VP, 2, true>                        \
                                                 : attn_res_fwd_mma_kernel<TT, TH, VP, 2, false>)                      \
-                               : (n_blocks == 8 ? attn_res_fwd_mma_kernel<TT, TH, VP, 1, true>                        \
+                               : (full8 ? attn_res_fwd_mma_kernel<TT, TH, VP, 1, true>                        \
                                                 : attn_res_fwd_mma_kernel<TT, TH, VP, 1, false>);                     \
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sp.smem) != cudaSuccess)         \
       return HILDA_ERR_CUDA;                                                                                          \
@@ -1177,9 +1179,10 @@ static int ar_bwd_t(const void* dOut, const void* V, const void* wq, int wq_dt, 
       if (g > grid) g = grid;
 #define AR_BWD_MMA(TT, TH, VP)                                                                                        \
   do {                                                                                                                \
-    auto kern = sp.stages == 2 ? (n_blocks == 8 ? attn_res_bwd_mma_kernel<TT, TH, VP, 2, true>                        \
+    const bool full8 = n_blocks == 8 && D == 8 * TH * VP;                                                             \
+    auto kern = sp.stages == 2 ? (full8 ? attn_res_bwd_mma_kernel<TT, TH, VP, 2, true>                        \
                                                 : attn_res_bwd_mma_kernel<TT, TH, VP, 2, false>)                      \
-                               : (n_blocks == 8 ? attn_res_bwd_mma_kernel<TT, TH, VP, 1, true>                        \
+                               : (full8 ? attn_res_bwd_mma_kernel<TT, TH, VP, 1, true>                        \
                                                 : attn_res_bwd_mma_kernel<TT, TH, VP, 1, false>);                     \
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sp.smem) != cudaSuccess)         \
       return HILDA_ERR_CUDA;                                                                                          \

@@ -550,7 +550,8 @@ attn_res_fwd_staged_kernel(const T* __restrict__ V, const void* __restrict__ w_q
 // contractions over D with the blocks as rows, so here they are mma.sync m16n8k16 (16-bit inputs,
 // fp32 accumulators; products of two 16-bit values are exact in fp32):
 //   Gram diagonal:  C[i][i] = sum_d v_i[d] v_i[d]     with A = B^T = the block rows,
-//   scores:         C[i][i] = sum_d key_i[d] wq[d]     with A = the keys, every column of B = w_query.
+//   scores:         C[i][i] = sum_d wq[d] key_i[d]     with w_query in every row of A and the keys
+//                                                      of block i as column i of B.
 // Lane (g, j) (g = lane / 4, j = lane % 4) reads row g (block g) of the staged token, 16 bytes at
 // a time; an MMA's contraction index may be any permutation of the dims, and because only the
 // diagonal C[g][g] is used (column g of B comes from the same lanes (g, .) as row g of A) the
@@ -560,7 +561,7 @@ attn_res_fwd_staged_kernel(const T* __restrict__ V, const void* __restrict__ w_q
 // its words 0 and 2 are then row g of A, words 1 and 3 row g + 8, so a piece takes two MMAs, one
 // whose B holds the partners of words (0, 2) and whose rows 0-7 are kept, one with the partners of
 // words (1, 3) whose rows 8-15 are kept; the other half of each result is discarded.
-// The diagonal element of row g sits in lane (g, g / 2). The weighted sum over the blocks stays on
+// The diagonal element of row g (and of row g + 8) sits in lane (g, g / 2). The weighted sum over the blocks stays on
 // the CUDA cores, one 16-byte piece of every row per thread as above. Needs n_blocks <= 8,
 // D % 64 == 0, w_query and w_norm in the data's own 16-bit type (staged in shared memory).
 template <typename T> struct ArMma;

@@ -96,3 +96,20 @@ def test_exported_names_match_reference_api():
     assert list(sig.parameters) == ["logits", "completion_ids", "advantages", "old_logp", "ref_logp",
                                     "completion_mask", "temperature", "beta", "eps_low", "eps_high"]
     assert inspect.signature(hk.RMSNorm.__init__).parameters["hidden_dim"] is not None
+
+
+def test_kernel_choice_setters_and_split_plan_without_a_gpu():
+    """The kernel-choice setters round-trip (tensor-core kernels are the default) and the paged
+    attention workspace covers one partial result (m, l, 128 sums) per sequence, head and context
+    slice of the plan; host-side arithmetic only, no launch."""
+    import hilda_kernel_b200._lib as L
+    lib = L.lib()
+    for setter in (lib.hilda_paged_attention_set_path, lib.hilda_attn_res_set_path):
+        assert setter(-1) == 1          # out of range: unchanged, returns the current choice
+        assert setter(0) == 1 and setter(-1) == 0
+        assert setter(1) == 0 and setter(-1) == 1
+    part = (128 + 2) * 4
+    big = lib.hilda_paged_attention_fp8_workspace_bytes(32, 16, 8, 16, 256)
+    assert (big - 256) % (32 * 16 * part) == 0 and 2 <= (big - 256) // (32 * 16 * part) <= 64
+    assert lib.hilda_paged_attention_fp8_workspace_bytes(4096, 16, 8, 1, 16) == 256   # one slice: no partials
+    assert lib.hilda_paged_attention_fp8_workspace_bytes(0, 16, 8, 16, 256) == 256

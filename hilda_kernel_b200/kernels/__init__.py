@@ -25,9 +25,30 @@ _EXPORTS = {
 }
 
 __all__ = []
-for _module, _names in _EXPORTS.items():
-    _m = import_module(f".{_module}", __name__)
-    for _n in _names:
-        globals()[_n] = getattr(_m, _n)
+if __package__ == "kernels":
+    # Imported as the top-level package ``kernels`` (this package's parent directory is on sys.path,
+    # the way the reference's bench scripts put ``triton-kernels/`` there, benchmarks/bench_rms_norm.py:17-19):
+    # alias the real package and its sub-modules, so that ``from kernels.rope import rope_forward`` works
+    # and there is a single copy of every class however it was imported.
+    import os as _os
+    import sys as _sys
+    _root = _os.path.dirname(_os.path.dirname(_os.path.dirname(_os.path.abspath(__file__))))
+    if _root not in _sys.path:
+        _sys.path.append(_root)
+    _real = import_module("hilda_kernel_b200.kernels")
+    for _module in _EXPORTS:
+        _m = import_module(f"hilda_kernel_b200.kernels.{_module}")
+        _sys.modules[f"{__name__}.{_module}"] = _m
+        globals()[_module] = _m
+    for _n in _real.__all__:
+        globals()[_n] = getattr(_real, _n)
         __all__.append(_n)
-del _module, _names, _m, _n
+    del _os, _sys, _root, _real
+else:
+    for _module, _names in _EXPORTS.items():
+        _m = import_module(f".{_module}", __name__)
+        for _n in _names:
+            globals()[_n] = getattr(_m, _n)
+            __all__.append(_n)
+    del _names
+del _module, _m, _n

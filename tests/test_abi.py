@@ -113,3 +113,32 @@ def test_kernel_choice_setters_and_split_plan_without_a_gpu():
     assert (big - 256) % (32 * 16 * part) == 0 and 2 <= (big - 256) // (32 * 16 * part) <= 64
     assert lib.hilda_paged_attention_fp8_workspace_bytes(4096, 16, 8, 1, 16) == 256   # one slice: no partials
     assert lib.hilda_paged_attention_fp8_workspace_bytes(0, 16, 8, 16, 256) == 256
+
+
+def test_top_level_kernels_package_like_the_reference_benches():
+    """hilda-kernel's bench scripts put their package's parent directory first on sys.path and import
+    ``kernels.<op>`` (benchmarks/bench_rms_norm.py:17-19, bench_rope.py:19, bench_grpo.py:6-8). With
+    ``hilda_kernel_b200/`` in that place the same statements must resolve to this library, from a
+    working directory that is not the repository, in a fresh interpreter."""
+    import subprocess
+    import sys
+    import tempfile
+    code = (
+        "import sys\n"
+        f"sys.path.insert(0, {os.path.join(ROOT, 'hilda_kernel_b200')!r})\n"
+        "from kernels.rms_norm import hilda_rms_norm, RMSNorm\n"
+        "from kernels.fused_add_rms_norm import hilda_fused_add_rms_norm\n"
+        "from kernels.rope import hilda_rope, rope_forward, rope_backward\n"
+        "from kernels.swiglu import hilda_swiglu\n"
+        "from kernels.cross_entropy import hilda_cross_entropy\n"
+        "from kernels.fused_linear_cross_entropy import hilda_fused_linear_cross_entropy\n"
+        "from kernels.grpo_loss import hilda_grpo_loss, fused_selective_log_softmax\n"
+        "from kernels import RMSNorm as R2, FusedLinearCrossEntropyLoss, GRPOLoss\n"
+        "import kernels, hilda_kernel_b200.kernels.rms_norm as real\n"
+        "assert kernels.rms_norm is real and RMSNorm is real.RMSNorm is R2\n"
+        "assert RMSNorm(8).weight.shape == (8,)\n"
+        "print('dropin ok')\n")
+    env = {k: v for k, v in os.environ.items() if k != "PYTHONPATH"}
+    with tempfile.TemporaryDirectory() as tmp:
+        r = subprocess.run([sys.executable, "-c", code], cwd=tmp, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "dropin ok" in r.stdout, r.stderr[-2000:]

@@ -12,6 +12,9 @@ import torch
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libhilda_b200.so")
+# HILDA_DEBUG=1 prefers the library built with -DHILDA_DEBUG (python -m hilda_kernel_b200._build --debug)
+if os.environ.get("HILDA_DEBUG", "0") not in ("", "0") and os.path.exists(os.path.join(_PKG, "libhilda_b200_debug.so")):
+    LIB_PATH = os.path.join(_PKG, "libhilda_b200_debug.so")
 
 F32, BF16, F16 = 0, 1, 2
 _DT = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
@@ -20,6 +23,12 @@ _ERR = {
     -1: "unsupported dtype", -2: "misaligned pointer", -3: "unsupported size", -4: "CUDA launch/runtime error",
     -5: "null pointer", -6: "device status: a bounded wait ran out", -7: "inconsistent arguments",
 }
+
+# Device status words (written by kernels, never read on the default path because reading one is a
+# host synchronisation). HILDA_DEBUG=1 in the environment, or DEBUG = True here, makes every operator
+# that has a status word read it after the call and raise.
+DEBUG = os.environ.get("HILDA_DEBUG", "0") not in ("", "0")
+_STATUS = {31: "a target / token id outside [0, V)"}
 
 _p, _i64, _i32, _f32 = C.c_void_p, C.c_int64, C.c_int, C.c_float
 
@@ -47,7 +56,7 @@ SIGNATURES = {
     "hilda_flce_logits_pitch": (_i64, [_i64]),
     "hilda_flce_padded_rows": (_i64, [_i64]),
     "hilda_flce_stat_tiles": (_i64, [_i64]),
-    "hilda_flce_logits": (_i32, [_p, _p, _p, _p, _i64, _i64, _i64, _i32, _p, _p]),
+    "hilda_flce_logits": (_i32, [_p, _p, _p, _p, _i64, _i64, _i64, _i32, _p, _p, _i64, _p]),
     "hilda_flce_logits_scaled": (_i32, [_p, _p, _p, _p, _i64, _i64, _i64, _f32, _i32, _p, _p]),
     "hilda_kl_div_fwd": (_i32, [_p, _p, _p, _p, _i64, _i64, _i32, _i32, _f32, _i32, _p]),
     "hilda_kl_div_bwd": (_i32, [_p, _p, _p, _i64, _i64, _i32, _i32, _i32, _p]),
@@ -61,14 +70,19 @@ SIGNATURES = {
     "hilda_attn_res_bwd_workspace_bytes": (_i64, [_i64, _i64]),
     "hilda_attn_res_bwd": (_i32, [_p] * 10 + [_i64, _i64, _i64, _i32, _i32, _i32, _p]),
     "hilda_fljsd_dlogits": (_i32, [_p, _p, _p, _p, _p, _i64, _p, _i64, _p, _i64, _i64, _f32, _f32, _i32, _p]),
-    "hilda_flce_row_stats": (_i32, [_p, _p, _p, _p, _i64, _i64, _i64, _i32, _p]),
-    "hilda_flce_finalize": (_i32, [_p, _p, _i64, _p, _p, _i64, _p]),
-    "hilda_flce_dlogits": (_i32, [_p, _p, _p, _i64, _p, _i64, _i64, _i64, _i32, _p]),
-    "hilda_flce_grad_hidden": (_i32, [_p, _p, _p, _p, _i64, _i64, _i64, _i32, _p, _p]),
-    "hilda_flce_grad_weight": (_i32, [_p, _p, _p, _p, _i32, _i64, _i64, _i64, _i32, _p, _p]),
+    "hilda_flce_row_stats": (_i32, [_p, _p, _p, _p, _i64, _i64, _i64, _i32, _p, _i64, _p]),
+    "hilda_flce_finalize": (_i32, [_p, _i32, _p, _i64, _p, _p, _i64, _p, _i64, _p]),
+    "hilda_flce_dlogits": (_i32, [_p, _p, _p, _i64, _p, _i64, _i64, _i64, _i32, _p, _i64, _p]),
+    "hilda_flce_grad_hidden": (_i32, [_p, _p, _p, _p, _i64, _i64, _i64, _i32, _p, _p, _i64, _p]),
+    "hilda_flce_grad_weight": (_i32, [_p, _p, _p, _p, _i32, _i64, _i64, _i64, _i32, _p, _p, _i64, _p]),
+    "hilda_flce_sum_loss": (_i32, [_p, _i64, _p, _i32, _p, _p, _p]),
+    "hilda_flce_compact": (_i32, [_p, _i64, _i64, _p, _p, _p, _p, _p]),
+    "hilda_gather_valid_rows": (_i32, [_p, _p, _p, _p, _i64, _i64, _p]),
+    "hilda_scatter_valid_rows": (_i32, [_p, _p, _p, _i64, _i64, _p]),
+    "hilda_scatter_valid_f32": (_i32, [_p, _p, _p, _i64, _p]),
     "hilda_flce_default_chunk_rows": (_i64, [_i64, _i64, _i64]),
-    "hilda_flce_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64, _i32]),
-    "hilda_fused_linear_cross_entropy_fwd": (_i32, [_p] * 8 + [_i64, _i64, _i64, _i64, _i32, _i64, _i32, _p]),
+    "hilda_flce_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64, _i32, _i32]),
+    "hilda_fused_linear_cross_entropy_fwd": (_i32, [_p] * 8 + [_i64, _i64, _i64, _i64, _i32, _i64, _i32, _i32, _p]),
     "hilda_flce_profile": (None, [_i32]),
     "hilda_flce_profile_collect": (_i32, [_p, _p]),
     "hilda_gather_rows": (_i32, [_p, _p, _p, _i64, _i64, _p]),
@@ -76,6 +90,7 @@ SIGNATURES = {
     "hilda_gemm_set_pair": (None, [_i32]),
     "hilda_gemm_get_pair": (_i32, []),
     "hilda_gemm_set_sm_limit": (None, [_i32]),
+    "hilda_gemm_set_wait_cap": (None, [C.c_uint]),
     "hilda_debug_gemm_set_order": (None, [_i32]),
     "hilda_gemm_set_probe": (None, [_p, _i32]),
     "hilda_debug_gemm": (_i32, [_p, _i64, _p, _i64, _p, _p, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _p, _p]),
@@ -119,6 +134,16 @@ def stream(device) -> int:
 def check(rc: int, what: str) -> None:
     if rc != 0:
         raise RuntimeError(f"hilda_kernel_b200.{what} failed: {_ERR.get(rc, 'error')} (code {rc})")
+
+
+def check_status(word: torch.Tensor, what: str, force: bool = False) -> None:
+    """Read a device status word (synchronises) when DEBUG or force; raise if it is non-zero."""
+    if not (DEBUG or force):
+        return
+    code = int(word)
+    if code != 0:
+        why = _STATUS.get(code, "a bounded device-side wait ran out")
+        raise RuntimeError(f"hilda_kernel_b200.{what}: device status {code} ({why})")
 
 
 def require_cuda(*tensors: torch.Tensor | None) -> torch.device:

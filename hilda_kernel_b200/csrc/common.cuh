@@ -5,6 +5,9 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
+#ifdef HILDA_DEBUG
+#include <cstdio>
+#endif
 
 // ---- status codes returned by every extern "C" entry point -----------------
 #define HILDA_OK 0
@@ -39,11 +42,25 @@ static inline int sm_count() {
   return cached[dev];
 }
 
+#ifdef HILDA_DEBUG
+// Debug build: wait for the launch and report a fault from the entry point that caused it (a
+// release build would see it at some later call). Not usable while a stream is being captured.
+#define HILDA_LAUNCH_CHECK()                                                                  \
+  do {                                                                                        \
+    cudaError_t e__ = cudaGetLastError();                                                     \
+    if (e__ == cudaSuccess) e__ = cudaDeviceSynchronize();                                    \
+    if (e__ != cudaSuccess) {                                                                 \
+      fprintf(stderr, "hilda_b200: %s at %s:%d\n", cudaGetErrorString(e__), __FILE__, __LINE__); \
+      return HILDA_ERR_CUDA;                                                                  \
+    }                                                                                         \
+  } while (0)
+#else
 #define HILDA_LAUNCH_CHECK()                                   \
   do {                                                         \
     cudaError_t e__ = cudaGetLastError();                      \
     if (e__ != cudaSuccess) return HILDA_ERR_CUDA;             \
   } while (0)
+#endif
 
 // ---- dtype traits: VEC elements per 16-byte vector --------------------------
 template <typename T> struct VT;

@@ -89,7 +89,7 @@ scale_rows_kernel(const T* in, T* out, const float* __restrict__ scale, int per_
 // ---------------------------------------------------------------- GRPO
 struct GRPOOp {
   const int64_t* ids;        // [B, L]
-  const int32_t* mask;       // [B, L] or null
+  const float* mask;         // [B, L] or null: weight of the token; 0 = inactive
   const float* advantages;   // [B]
   const float* old_logp;     // [B, L] or null
   const float* ref_logp;     // [B, L] or null (required when beta != 0)
@@ -107,7 +107,7 @@ struct GRPOOp {
     const int64_t b = row / (L + 1), l = row - b * (L + 1);
     if (l == L) return false;
     const int64_t i = b * L + l;
-    if (mask && mask[i] == 0) return false;
+    if (mask && mask[i] == 0.f) return false;
     target = ids[i];
     return true;
   }
@@ -130,7 +130,7 @@ struct GRPOOp {
     if (beta != 0.f) p.ref = ref_logp[i];
     p.adv = advantages[b];
     // upstream scale for a unit loss gradient: mask / (seq_len_b * B), then 1/T
-    const float mval = mask ? (float)mask[i] : 1.0f;
+    const float mval = mask ? mask[i] : 1.0f;
     p.gscale = (mval / (seq_len[b] * b_norm)) * inv_t;
     return p;
   }
@@ -171,11 +171,11 @@ struct GRPOOp {
 
 // seq_len[b] = max(sum_l mask[b,l], 1)  (L when there is no mask)
 __global__ void __launch_bounds__(256)
-grpo_seq_len_kernel(const int32_t* __restrict__ mask, int64_t L, float* __restrict__ seq_len) {
+grpo_seq_len_kernel(const float* __restrict__ mask, int64_t L, float* __restrict__ seq_len) {
   __shared__ float red[33];
   const int64_t b = blockIdx.x;
   float acc = 0.f;
-  if (mask) for (int64_t l = threadIdx.x; l < L; l += 256) acc += (float)mask[b * L + l];
+  if (mask) for (int64_t l = threadIdx.x; l < L; l += 256) acc += mask[b * L + l];
   else acc = (threadIdx.x == 0) ? (float)L : 0.f;
   acc = block_sum<256>(acc, red);
   if (threadIdx.x == 0) seq_len[b] = fmaxf(acc, 1.0f);
@@ -185,7 +185,7 @@ grpo_seq_len_kernel(const int32_t* __restrict__ mask, int64_t L, float* __restri
 // out[2] = sum(clipped*mask)/max(sum mask,1). One CTA, one warp per sequence at a time.
 __global__ void __launch_bounds__(1024)
 grpo_reduce_kernel(const float* __restrict__ loss, const float* __restrict__ kl, const float* __restrict__ clipped,
-                   const int32_t* __restrict__ mask, const float* __restrict__ seq_len, int64_t B, int64_t L,
+                   const float* __restrict__ mask, const float* __restrict__ seq_len, int64_t B, int64_t L,
                    float b_norm, float* __restrict__ out) {
   __shared__ float red[4][33];
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -194,7 +194,7 @@ grpo_reduce_kernel(const float* __restrict__ loss, const float* __restrict__ kl,
     float sl = 0.f, sk = 0.f, sc = 0.f, sm = 0.f;
     for (int64_t l = lane; l < L; l += 32) {
       const int64_t i = b * L + l;
-      const float mv = mask ? (float)mask[i] : 1.0f;
+      const float mv = mask ? mask[i] : 1.0f;
       sl += loss[i] * mv; sc += clipped[i] * mv; sm += mv;
       if (kl) sk += kl[i] * mv;
     }
@@ -294,14 +294,15 @@ int hilda_scale_rows(const void* in, void* out, const float* scale, int per_row,
 
 int64_t hilda_grpo_workspace_bytes(int64_t B) { return 16 + (B > 0 ? B : 0) * 4; }
 
-// logits [B, L+1, V] contiguous; ids [B, L] int64; mask [B, L] int32 or null; advantages [B] fp32;
+// logits [B, L+1, V] contiguous; ids [B, L] int64; mask [B, L] fp32 or null (0 = token skipped, any other
+// value = its weight in the reductions, as the reference's completion_mask.float()); advantages [B] fp32;
 // old_logp / ref_logp [B, L] fp32 or null. Per-token outputs loss/kl/clipped/lse [B, L] fp32
 // (kl may be null when beta == 0). scalars_out[4] = {loss, kl_mean, clip_ratio, sum(mask)}. B_total > 0: the
 // loss and the gradient are normalised by B_total sequences instead of B (sequences sharded over ranks).
 // grad: [B, L+1, V] in the logits dtype (gradient for a unit upstream loss gradient) or null.
 // workspace: hilda_grpo_workspace_bytes(B); seq_len[b] lives at byte 16.
 int hilda_grpo_loss_fwd(const void* logits, const int64_t* ids, const float* advantages, const float* old_logp,
-                        const float* ref_logp, const int32_t* mask, void* grad, float* loss, float* kl, float* clipped,
+                        const float* ref_logp, const float* mask, void* grad, float* loss, float* kl, float* clipped,
                         float* lse, float* scalars_out, void* workspace, int64_t B, int64_t L, int64_t V,
                         int64_t B_total, float temperature, float beta, float eps_low, float eps_high, int dtype,
                         void* stream) {
@@ -336,7 +337,7 @@ int hilda_grpo_loss_fwd(const void* logits, const int64_t* ids, const float* adv
 }
 
 // logp[b,l] = logits[b,l,ids[b,l]]/T - logsumexp(logits[b,l,:]/T); masked positions give 0.
-int hilda_selective_log_softmax(const void* logits, const int64_t* ids, const int32_t* mask, float* logp, int64_t B,
+int hilda_selective_log_softmax(const void* logits, const int64_t* ids, const float* mask, float* logp, int64_t B,
                                 int64_t L, int64_t V, float temperature, int dtype, void* stream) {
   if (!logits || !ids || !logp) return HILDA_ERR_NULL;
   if (B < 0 || L < 0 || V <= 0 || !(temperature > 0.f)) return HILDA_ERR_SIZE;

@@ -27,6 +27,12 @@ __device__ __forceinline__ void cluster_arrive_release() {
 __device__ __forceinline__ void cluster_wait_acquire() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+}
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
   uint32_t r;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
@@ -136,6 +142,7 @@ __device__ __forceinline__ float vec_exp_inplace(uint4& v, float k, float m) {
 }
 
 constexpr int ROW_THREADS_DEFAULT = 256;
+constexpr int ROW_STATUS_TARGET_RANGE = 31;  // status word: a target / token id outside [0, V)
 
 // Register-resident, cluster-per-row kernel. Requires V % VEC == 0 and 16-byte aligned rows.
 // CTAs per SM the register budget is held to (the row slice itself takes 4*NV registers).
@@ -145,7 +152,7 @@ constexpr int row_min_blocks(int threads, int nv) {
 
 template <typename T, int ROW_THREADS, int NV, int CLUSTER, class Op>
 __global__ void __launch_bounds__(ROW_THREADS, row_min_blocks(ROW_THREADS, NV))
-row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V, Op op) {
+row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V, Op op, int* __restrict__ status) {
   constexpr int VEC = VT<T>::N;
   __shared__ float red[33];
   __shared__ float xchg[2 * CLUSTER];
@@ -171,6 +178,13 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
     if (writer) op.inactive(row);
     return;
   }
+  // "I have started": a peer may write into this CTA's shared memory only once it knows that, so
+  // every CTA of an active row arrives here and waits for the others right before its remote
+  // stores; the wait has the whole row load and two reductions to hide under.
+  if constexpr (CLUSTER > 1) cluster_arrive_relaxed();
+  // A target outside [0, V) is not "ignored": the row takes part with no target logit and no
+  // one-hot term, and the status word tells the host (the reference reads out of bounds there).
+  if (writer && status && (target < 0 || target >= V)) atomicCAS(status, 0, ROW_STATUS_TARGET_RANGE);
 
   // per-thread base pointers: vector i of this thread sits at a compile-time offset from them
   const int my_vec = v1 - v0;  // vectors in this CTA's slice
@@ -206,6 +220,7 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
 
   float M = m, S = s;
   if constexpr (CLUSTER > 1) {
+    cluster_wait();  // every CTA of the cluster is running: its shared memory may be written
     if (tid < CLUSTER) {
       const uint32_t base = (uint32_t)__cvta_generic_to_shared(xchg);
       const uint32_t remote = map_to_cta(base, (uint32_t)tid);
@@ -248,7 +263,7 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
 // Any V / alignment: one CTA per row, scalar access, row read twice (second read from L2).
 template <typename T, class Op>
 __global__ void __launch_bounds__(512)
-row_softmax_generic_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V, Op op) {
+row_softmax_generic_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V, Op op, int* __restrict__ status) {
   __shared__ float red[33];
   const int tid = threadIdx.x;
   const int64_t row = blockIdx.x;
@@ -264,6 +279,7 @@ row_softmax_generic_kernel(const T* __restrict__ logits, T* __restrict__ grad, i
     if (writer) op.inactive(row);
     return;
   }
+  if (writer && status && (target < 0 || target >= V)) atomicCAS(status, 0, ROW_STATUS_TARGET_RANGE);
   const float inv_t = op.inv_temperature();
   const float k = inv_t * LOG2E;
   float x_t = 0.f;
@@ -318,7 +334,7 @@ static inline RowPlan plan_row(int64_t V, int vec, bool aligned, int force_nv, i
 }
 
 template <typename T, int THREADS, int NV, int CLUSTER, class Op>
-static int launch_row_cfg(const T* logits, T* grad, int64_t n_rows, int64_t V, const Op& op, cudaStream_t st) {
+static int launch_row_cfg(const T* logits, T* grad, int64_t n_rows, int64_t V, const Op& op, int* status, cudaStream_t st) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(n_rows * CLUSTER), 1, 1);
   cfg.blockDim = dim3(THREADS, 1, 1);
@@ -331,7 +347,7 @@ static int launch_row_cfg(const T* logits, T* grad, int64_t n_rows, int64_t V, c
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, row_softmax_kernel<T, THREADS, NV, CLUSTER, Op>, logits, grad, V, op);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, row_softmax_kernel<T, THREADS, NV, CLUSTER, Op>, logits, grad, V, op, status);
   return e == cudaSuccess ? HILDA_OK : HILDA_ERR_CUDA;
 }
 
@@ -346,16 +362,15 @@ static int launch_rows(const void* logits_v, void* grad_v, int64_t n_rows, int64
   if (n_rows == 0) return HILDA_OK;
   if (n_rows * 8 > 0x7fffffffLL) return HILDA_ERR_SIZE;
   const bool al = aligned16(logits) && (!grad || aligned16(grad)) && op.rows_aligned(V, VT<T>::N);
-  (void)status;
   const RowPlan p = plan_row(V, VT<T>::N, al, g_row_force_nv, g_row_force_cluster);
   if (p.generic) {
-    row_softmax_generic_kernel<T, Op><<<(unsigned)n_rows, 512, 0, st>>>(logits, grad, V, op);
+    row_softmax_generic_kernel<T, Op><<<(unsigned)n_rows, 512, 0, st>>>(logits, grad, V, op, status);
     HILDA_LAUNCH_CHECK();
     return HILDA_OK;
   }
 #define ROW_CFG(TH_, NV_, CL_) \
   if (p.threads == TH_ && p.nv == NV_ && p.cluster == CL_)  \
-    return launch_row_cfg<T, TH_, NV_, CL_, Op>(logits, grad, n_rows, V, op, st);
+    return launch_row_cfg<T, TH_, NV_, CL_, Op>(logits, grad, n_rows, V, op, status, st);
   ROW_CFG(256, 1, 1) ROW_CFG(256, 2, 1) ROW_CFG(256, 4, 1) ROW_CFG(256, 8, 1) ROW_CFG(256, 8, 2) ROW_CFG(256, 8, 4)
   ROW_CFG(256, 8, 8) ROW_CFG(256, 10, 8) ROW_CFG(256, 12, 8) ROW_CFG(256, 16, 8) ROW_CFG(256, 16, 4)
   ROW_CFG(256, 16, 2) ROW_CFG(320, 8, 8) ROW_CFG(384, 8, 8) ROW_CFG(512, 8, 8) ROW_CFG(512, 4, 8)

@@ -26,7 +26,7 @@ constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int GEMM_SMEM_BYTES = GEMM_STAGES * STAGE_BYTES + 1024;  // + slack for 1024-byte alignment
 constexpr int GEMM_THREADS = 224;  // warp 0: TMA of A, warp 1: MMA, warps 2-5: epilogue, warp 6: TMA of B
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t WAIT_CAP = 1u << 22;  // bounded spin: try_wait attempts before giving up
+constexpr uint32_t WAIT_CAP = 1u << 22;  // bounded spin: default number of try_wait attempts before giving up
 
 enum GemmEpilogue {
   EPI_STORE16 = 0,      // C16 = acc
@@ -50,8 +50,30 @@ struct GemmParams {
   uint32_t mn_lbo, mn_sbo;  // descriptor byte offsets for MN-major operands (8192, 1024)
   int sm_limit;      // use at most this many SMs (0 = all): leaves room for a concurrent collective
   long long* probe;  // optional [gridDim.x][8] cycle counters of the role loops (null = off)
-  int dry;           // measurement only: the producer signals "full" without loading (results are garbage)
+  int dry;           // 1, measurement only: the producer signals "full" without loading (results are garbage);
+                     // 2, test of the bounded waits: the producer loads nothing and signals nothing
+  uint32_t wait_cap; // try_wait attempts before a wait gives up
+  // Row count known only on the device (ignored tokens compacted away without a host round trip):
+  // rows = clamp(*dyn_rows - dyn_off, 0, extent) replaces M (dyn_dim 1: tiles beyond it are skipped)
+  // or K (dyn_dim 2: k-blocks beyond it are skipped; rows between it and the next multiple of 64
+  // must hold zeros). dyn_dim 0: off.
+  const int* dyn_rows; int dyn_off; int dyn_dim;
 };
+
+// (m_tiles, k_blocks) after the device-side row count; TILE_M = rows per output tile.
+template <int TILE_M>
+__device__ __forceinline__ void gemm_dynamic_extent(const GemmParams& p, int& m_tiles, int& k_blocks) {
+  m_tiles = p.m_tiles; k_blocks = p.k_blocks;
+  if (p.dyn_dim == 0) return;
+  int r = *p.dyn_rows - p.dyn_off;
+  if (p.dyn_dim == 1) {
+    r = r < 0 ? 0 : (r > p.M ? p.M : r);
+    m_tiles = (r + TILE_M - 1) / TILE_M;
+  } else {
+    r = r < 0 ? 0 : (r > p.K ? p.K : r);
+    k_blocks = (r + BK - 1) / BK;
+  }
+}
 
 // ---- PTX wrappers -------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -75,8 +97,9 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 // Bounded wait. Returns false if the wait ran out or another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-  for (uint32_t it = 0; it < WAIT_CAP; ++it) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                          uint32_t cap) {
+  for (uint32_t it = 0; it < cap; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 255u && *abort_flag) return false;
   }
@@ -194,7 +217,8 @@ __device__ __forceinline__ float ex2_fast(float x) {
 // Epilogue of one 128 x 256 accumulator tile for the calling thread (thread = TMEM lane = row).
 // taddr0: TMEM address of column 0 of the accumulator in this warp's lane quadrant.
 template <int EPI>
-__device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t taddr0, int64_t row, int col0, int nt) {
+__device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t taddr0, int64_t row, int col0, int nt,
+                                                   bool zero_acc = false) {
   float run_m = -INFINITY, run_s = 0.f;
   const float stat_scale = p.stat_scale;  // log2(e) / temperature: the statistics are of logits / temperature
 #pragma unroll 1
@@ -202,6 +226,10 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t
     uint32_t r[32];
     tmem_ld32(taddr0 + c * 32, r);
     tmem_ld_wait();
+    if (zero_acc) {  // no k-block ran (a device-side row count of zero): the product is zero
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[j] = 0u;
+    }
     const int cbase = col0 + c * 32;
     if constexpr (EPI == EPI_STORE16 || EPI == EPI_LOGITS_STATS) {
       uint32_t h[16];
@@ -312,7 +340,10 @@ tcgen05_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
 
-  const int total_tiles = p.m_tiles * p.n_tiles;
+  int m_tiles_d, k_blocks_d;
+  gemm_dynamic_extent<BM>(p, m_tiles_d, k_blocks_d);
+  const int total_tiles = m_tiles_d * p.n_tiles;
+  const uint32_t wait_cap = p.wait_cap;
 
   if (warp == 0 || warp == 6) {
     // ------------------------------------------------------------------ TMA producers
@@ -327,12 +358,13 @@ tcgen05_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       bool ok = true;
       long long w_empty = 0;
       const long long t_begin = clock64();
-      const bool probing = p.probe != nullptr, dry = p.dry != 0;
-      const int k_blocks = p.k_blocks;
+      const bool probing = p.probe != nullptr;
+      const int dry = p.dry;
+      const int k_blocks = k_blocks_d;
       const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int mt = p.m_fast ? tile % p.m_tiles : tile / p.n_tiles;
-        const int nt = p.m_fast ? tile / p.m_tiles : tile % p.n_tiles;
+        const int mt = p.m_fast ? tile % m_tiles_d : tile / p.n_tiles;
+        const int nt = p.m_fast ? tile / m_tiles_d : tile % p.n_tiles;
         const int m0 = mt * BM, n0 = nt * BN;
         for (int kb = 0, kc = 0; kb < k_blocks; ++kb, kc += BK) {
           const uint32_t fb = full0 + stage * 8u, eb = empty0 + stage * 8u;
@@ -341,8 +373,9 @@ tcgen05_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const uint32_t want = phase ^ 1u;
           if (++stage == GEMM_STAGES) { stage = 0; phase ^= 1u; }
           const long long t0 = probing ? clock64() : 0;
-          if (!mbar_wait(eb, want, abortp, p.status, 1)) { ok = false; break; }
+          if (!mbar_wait(eb, want, abortp, p.status, 1, wait_cap)) { ok = false; break; }
           if (probing) w_empty += clock64() - t0;
+          if (dry == 2) continue;  // test hook: nothing is loaded or signalled, so the issuer's wait runs out
           if (is_a) {
             if (dry) { mbar_arrive(fb); continue; }
             if constexpr (!A_MN) {
@@ -375,7 +408,7 @@ tcgen05_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       // everything the loop needs, in registers: this thread's instruction latency per k-block
       // has to stay under the 4 x 128 cycles the tensor pipe takes for it
       const bool probing = p.probe != nullptr;
-      const int k_blocks = p.k_blocks;
+      const int k_blocks = k_blocks_d;
       const uint32_t idesc = p.idesc;
       const uint32_t a_hi = smem_desc_hi(A_MN ? p.mn_sbo : 1024u), b_hi = smem_desc_hi(B_MN ? p.mn_sbo : 1024u);
       const uint32_t a_lo0 = smem_desc_lo(stage_base, A_MN ? p.mn_lbo : 0u);
@@ -385,7 +418,7 @@ tcgen05_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t ready = 0;  // set when the peek of the previous k-block already saw this slot full
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const long long t1 = probing ? clock64() : 0;
-        if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1u, abortp, p.status, 2)) break;
+        if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1u, abortp, p.status, 2, wait_cap)) break;
         if (probing) w_tempty += clock64() - t1;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -394,7 +427,7 @@ tcgen05_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!ready) {
             const long long t0 = probing ? clock64() : 0;
-            if (!mbar_wait(full0 + stage * 8u, phase, abortp, p.status, 3)) { ok = false; break; }
+            if (!mbar_wait(full0 + stage * 8u, phase, abortp, p.status, 3, wait_cap)) { ok = false; break; }
             if (probing) w_full += clock64() - t0;
           }
           tc_fence_after();
@@ -424,17 +457,17 @@ tcgen05_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t acc = 0, acc_phase = 0;
     long long w_tfull = 0, t_epi = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-      const int mt = p.m_fast ? tile % p.m_tiles : tile / p.n_tiles;
-      const int nt = p.m_fast ? tile / p.m_tiles : tile % p.n_tiles;
+      const int mt = p.m_fast ? tile % m_tiles_d : tile / p.n_tiles;
+      const int nt = p.m_fast ? tile / m_tiles_d : tile % p.n_tiles;
       const long long t0 = p.probe ? clock64() : 0;
-      if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase, abortp, p.status, 4)) break;
+      if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase, abortp, p.status, 4, wait_cap)) break;
       const long long t1 = p.probe ? clock64() : 0;
       w_tfull += t1 - t0;
       tc_fence_after();
       const int64_t row = (int64_t)mt * BM + row_in_tile;
       const int col0 = nt * BN;
       const uint32_t taddr0 = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
-      gemm_epilogue_tile<EPI>(p, taddr0, row, col0, nt);
+      gemm_epilogue_tile<EPI>(p, taddr0, row, col0, nt, k_blocks_d == 0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));

@@ -134,7 +134,10 @@ tcgen05_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
 
-  const int total_tiles = p.m_tiles * p.n_tiles;  // m_tiles counts 256-row tiles here
+  int m_tiles_d, k_blocks_d;  // m_tiles counts 256-row tiles here
+  gemm_dynamic_extent<2 * BM>(p, m_tiles_d, k_blocks_d);
+  const int total_tiles = m_tiles_d * p.n_tiles;
+  const uint32_t wait_cap = p.wait_cap;
 
   if (warp == 0 || warp == 6) {
     // ------------------------------------------------------------------ TMA producers (both CTAs)
@@ -147,13 +150,14 @@ tcgen05_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       bool ok = true;
       long long w_empty = 0;
       const long long t_begin = clock64();
-      const bool probing = p.probe != nullptr, dry = p.dry != 0;
-      const int k_blocks = p.k_blocks;
+      const bool probing = p.probe != nullptr;
+      const int dry = p.dry;
+      const int k_blocks = k_blocks_d;
       const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
       const uint32_t full0_leader = g2_map_rank(full0, 0);  // the leader's barriers, 8 bytes apart like ours
       for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
-        const int mt = p.m_fast ? tile % p.m_tiles : tile / p.n_tiles;
-        const int nt = p.m_fast ? tile / p.m_tiles : tile % p.n_tiles;
+        const int mt = p.m_fast ? tile % m_tiles_d : tile / p.n_tiles;
+        const int nt = p.m_fast ? tile / m_tiles_d : tile % p.n_tiles;
         const int m0 = mt * (2 * BM) + (int)rank * BM;        // this CTA's 128 rows of A
         const int n0 = nt * BN + (int)rank * G2_B_ROWS;        // this CTA's 128 columns of B
         for (int kb = 0, kc = 0; kb < k_blocks; ++kb, kc += BK) {
@@ -163,8 +167,9 @@ tcgen05_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           const uint32_t want = phase ^ 1u;
           if (++stage == G2_STAGES) { stage = 0; phase ^= 1u; }
           const long long t0 = probing ? clock64() : 0;
-          if (!mbar_wait(eb, want, abortp, p.status, 21)) { ok = false; break; }
+          if (!mbar_wait(eb, want, abortp, p.status, 21, wait_cap)) { ok = false; break; }
           if (probing) w_empty += clock64() - t0;
+          if (dry == 2) continue;  // test hook: nothing is loaded or signalled, so the issuer's wait runs out
           if (is_a) {
             if (dry) {
               if (leader) mbar_arrive(fb_local);
@@ -198,7 +203,7 @@ tcgen05_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       long long w_full = 0, w_tempty = 0;
       const long long t_begin = clock64();
       const bool probing = p.probe != nullptr;
-      const int k_blocks = p.k_blocks;
+      const int k_blocks = k_blocks_d;
       const uint32_t idesc = p.idesc;
       const uint32_t a_hi = smem_desc_hi(A_MN ? p.mn_sbo : 1024u), b_hi = smem_desc_hi(B_MN ? p.mn_sbo : 1024u);
       const uint32_t a_lo0 = smem_desc_lo(stage_base, A_MN ? p.mn_lbo : 0u);
@@ -208,7 +213,7 @@ tcgen05_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       uint32_t ready = 0;  // set when the peek of the previous k-block already saw this slot full
       for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
         const long long t1 = probing ? clock64() : 0;
-        if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1u, abortp, p.status, 22)) break;
+        if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1u, abortp, p.status, 22, wait_cap)) break;
         if (probing) w_tempty += clock64() - t1;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -217,7 +222,7 @@ tcgen05_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!ready) {
             const long long t0 = probing ? clock64() : 0;
-            if (!mbar_wait(full0 + stage * 8u, phase, abortp, p.status, 23)) { ok = false; break; }
+            if (!mbar_wait(full0 + stage * 8u, phase, abortp, p.status, 23, wait_cap)) { ok = false; break; }
             if (probing) w_full += clock64() - t0;
           }
           tc_fence_after();
@@ -245,16 +250,16 @@ tcgen05_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     uint32_t acc = 0, acc_phase = 0;
     long long w_tfull = 0, t_epi = 0;
     for (int tile = pair; tile < total_tiles; tile += n_pairs) {
-      const int mt = p.m_fast ? tile % p.m_tiles : tile / p.n_tiles;
-      const int nt = p.m_fast ? tile / p.m_tiles : tile % p.n_tiles;
+      const int mt = p.m_fast ? tile % m_tiles_d : tile / p.n_tiles;
+      const int nt = p.m_fast ? tile / m_tiles_d : tile % p.n_tiles;
       const long long t0 = p.probe ? clock64() : 0;
-      if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase, abortp, p.status, 24)) break;
+      if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase, abortp, p.status, 24, wait_cap)) break;
       const long long t1 = p.probe ? clock64() : 0;
       w_tfull += t1 - t0;
       tc_fence_after();
       const int64_t row = (int64_t)mt * (2 * BM) + (int64_t)rank * BM + row_in_tile;
       const uint32_t taddr0 = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
-      gemm_epilogue_tile<EPI>(p, taddr0, row, nt * BN, nt);
+      gemm_epilogue_tile<EPI>(p, taddr0, row, nt * BN, nt, k_blocks_d == 0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) g2_mbar_arrive_remote(g2_map_rank(smem_u32(&tempty_bar[acc]), 0));

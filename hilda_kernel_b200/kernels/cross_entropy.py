@@ -46,6 +46,7 @@ def cross_entropy_forward(logits, targets, ignore_index=-100, reduction='mean', 
                                          L.ptr(loss_out), L.ptr(ws), L.ptr(n_valid_global), n_rows, n_cols, int(ignore_index),
                                          _RED[reduction], L.dt(logits), L.stream(dev))
     L.check(rc, "cross_entropy_fwd")
+    L.check_status(ws[2], "cross_entropy_fwd")
     n_valid = ws[0]
     aux = grad if needs_grad else lse
     if reduction == 'none':

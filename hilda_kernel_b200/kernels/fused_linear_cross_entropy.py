@@ -23,16 +23,12 @@ CHUNK_ROWS = int(os.environ["HILDA_FLCE_CHUNK_ROWS"]) if os.environ.get("HILDA_F
 # Set True to synchronise after each call and raise if a device-side bounded wait ran out.
 CHECK_STATUS = False
 # Ignored tokens contribute nothing to the loss or to either gradient, so by default their rows are
-# compacted away before the three GEMMs run (their d(hidden) rows come back as zeros). Building
-# the row list costs one host synchronisation, the same one the reference pays for n_valid
-# (fused_linear_cross_entropy.py:121). Set False to keep the call free of host synchronisation.
+# compacted away before the three GEMMs run (their d(hidden) rows come back as zeros). The index
+# lists, the gather, the GEMM extents and the scatter all follow a count that stays on the device:
+# the call makes no host synchronisation (the reference pays one for n_valid,
+# fused_linear_cross_entropy.py:121). Set False to run the GEMMs over ignored rows too.
 SKIP_IGNORED_ROWS = True
-
-
-def _move_rows(fn_name, src, idx, dst, *extra):
-    with device_guard(src.device):
-        rc = getattr(L.lib(), fn_name)(L.ptr(src), L.ptr(idx), L.ptr(dst), idx.numel(), *extra, L.stream(src.device))
-    L.check(rc, fn_name)
+FLCE_COMPACT = 1  # HILDA_FLCE_COMPACT of the C ABI
 
 
 def fused_linear_cross_entropy_forward(hidden_states, weight, targets, ignore_index=-100, reduction='mean',
@@ -40,26 +36,6 @@ def fused_linear_cross_entropy_forward(hidden_states, weight, targets, ignore_in
     """Returns (loss, grad_input, grad_weight, n_valid); n_valid is a device scalar."""
     if skip_ignored is None:
         skip_ignored = SKIP_IGNORED_ROWS
-    if skip_ignored and hidden_states.is_cuda and hidden_states.dim() == 2 and targets.dim() == 1:
-        keep = (targets != ignore_index).nonzero().squeeze(1)  # the one host sync (size of the result)
-        BT = targets.shape[0]
-        if 0 < keep.numel() < BT:
-            H = hidden_states.shape[1]
-            hs = hidden_states.contiguous()
-            h_c = torch.empty(keep.numel(), H, dtype=hs.dtype, device=hs.device)
-            _move_rows("hilda_gather_rows", hs, keep, h_c, H * hs.element_size())
-            t_c = targets.contiguous()[keep]
-            loss, dh_c, dw, n_valid = fused_linear_cross_entropy_forward(
-                h_c, weight, t_c, ignore_index, reduction, compute_grad, chunk_rows, skip_ignored=False)
-            dh = None
-            if compute_grad:
-                dh = torch.empty_like(hs)
-                _move_rows("hilda_scatter_rows", dh_c, keep, dh, BT, H * hs.element_size())
-            if reduction == 'none':
-                full = torch.zeros(BT, dtype=loss.dtype, device=loss.device)
-                full[keep] = loss
-                loss = full
-            return loss, dh, dw, n_valid
     if reduction not in _RED:
         raise ValueError(f"reduction must be one of {list(_RED)}, got {reduction!r}")
     dev = L.require_cuda(hidden_states, weight, targets)
@@ -79,24 +55,24 @@ def fused_linear_cross_entropy_forward(hidden_states, weight, targets, ignore_in
     if targets.dtype != torch.int64:
         targets = targets.long()
     chunk = chunk_rows if chunk_rows is not None else (CHUNK_ROWS or 0)
-    loss_rows = torch.empty(BT, dtype=torch.float32, device=dev)
+    flags = FLCE_COMPACT if skip_ignored else 0
+    loss_rows = torch.empty(BT, dtype=torch.float32, device=dev) if reduction == 'none' else None
     loss_out = torch.empty((), dtype=torch.float32, device=dev)
     grad_input = torch.empty_like(hidden_states) if compute_grad else None
     grad_weight = torch.empty_like(weight) if compute_grad else None
     with device_guard(dev):
         lib = L.lib()
-        nbytes = lib.hilda_flce_workspace_bytes(BT, H, V, chunk, 1 if compute_grad else 0)
+        nbytes = lib.hilda_flce_workspace_bytes(BT, H, V, chunk, 1 if compute_grad else 0, flags)
         ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         rc = lib.hilda_fused_linear_cross_entropy_fwd(
             L.ptr(hidden_states), L.ptr(weight), L.ptr(targets), L.ptr(loss_out), L.ptr(loss_rows),
             L.ptr(grad_input), L.ptr(grad_weight), L.ptr(ws), BT, H, V, int(ignore_index), _RED[reduction],
-            chunk, L.dt(hidden_states), L.stream(dev))
+            chunk, L.dt(hidden_states), flags, L.stream(dev))
     L.check(rc, "fused_linear_cross_entropy_fwd")
     head = ws[:8].view(torch.int32)
-    if CHECK_STATUS:
-        code = int(head[0])
-        if code != 0:
-            raise RuntimeError(f"fused_linear_cross_entropy: device-side bounded wait ran out (code {code})")
+    # a bounded device-side wait that ran out leaves a code here and makes a mean / sum loss NaN;
+    # reading the word is a host synchronisation, so only on request
+    L.check_status(head[0], "fused_linear_cross_entropy_fwd", force=CHECK_STATUS)
     n_valid = head[1]
     loss = loss_rows if reduction == 'none' else loss_out
     return loss, grad_input, grad_weight, n_valid

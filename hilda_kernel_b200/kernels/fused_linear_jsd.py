@@ -78,7 +78,7 @@ def fused_linear_jsd_forward(student_input, student_weight, teacher_input, teach
             for x, w, hdim, scr, rs in ((sc, s_w, H, s_scr, rs_s), (tc, t_w, Ht, t_scr, rs_t)):
                 L.check(lib.hilda_flce_logits_scaled(L.ptr(x), L.ptr(w), L.ptr(scr), L.ptr(stats), rows, hdim, V, inv_t,
                                                      dt, status_p, st), "flce_logits_scaled")
-                L.check(lib.hilda_flce_row_stats(L.ptr(stats), L.ptr(scr), None, L.ptr(rs), rows, V, 0, dt, st),
+                L.check(lib.hilda_flce_row_stats(L.ptr(stats), L.ptr(scr), None, L.ptr(rs), rows, V, 0, dt, None, 0, st),
                         "flce_row_stats")
             L.check(lib.hilda_fljsd_dlogits(L.ptr(s_scr), L.ptr(t_scr), L.ptr(rs_s), L.ptr(rs_t), L.ptr(lc),
                                             int(ignore_index), n_valid_p if labels is not None else None, BT,
@@ -87,11 +87,14 @@ def fused_linear_jsd_forward(student_input, student_weight, teacher_input, teach
             if not compute_grad:
                 continue
             L.check(lib.hilda_flce_grad_hidden(L.ptr(s_scr), L.ptr(s_w), dh.data_ptr() + 2 * r0 * H, None, rows, H, V,
-                                               dt, status_p, st), "flce_grad_hidden")
+                                               dt, status_p, None, 0, st), "flce_grad_hidden")
             mode = 3 if n_chunks == 1 else (0 if c == 0 else (2 if c == n_chunks - 1 else 1))
             L.check(lib.hilda_flce_grad_weight(L.ptr(s_scr), L.ptr(sc), L.ptr(dw32), L.ptr(dw), mode, rows, H, V, dt,
-                                               status_p, st), "flce_grad_weight")
-    return loss_rows.sum(), dh, dw
+                                               status_p, None, 0, st), "flce_grad_weight")
+        # one reduction kernel; the loss comes out NaN if a bounded wait inside a GEMM ran out
+        loss = torch.empty((), dtype=torch.float32, device=dev)
+        L.check(lib.hilda_flce_sum_loss(L.ptr(loss_rows), BT, None, 0, status_p, L.ptr(loss), st), "flce_sum_loss")
+    return loss, dh, dw
 
 
 class HildaFusedLinearJSDFunction(torch.autograd.Function):

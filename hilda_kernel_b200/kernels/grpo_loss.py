@@ -13,11 +13,13 @@ from .. import _lib as L
 from .._lib import device_guard
 
 
-def _mask_i32(mask):
+def _mask_f32(mask):
+    """The kernels take the mask as fp32: 0 skips the token, any other value is its weight in the
+    reductions (the reference tests ``mask == 0`` in its kernels and weights with ``mask.float()``,
+    grpo_loss.py:104, :264), so bool, integer and fractional float masks all behave as there."""
     if mask is None:
         return None
-    mask = mask.contiguous()
-    return mask if mask.dtype == torch.int32 else mask.to(torch.int32)
+    return mask.to(torch.float32).contiguous()
 
 
 @torch.no_grad()
@@ -31,7 +33,7 @@ def fused_selective_log_softmax(logits, input_ids, temperature=1.0, mask=None):
     if input_ids.dtype != torch.int64:
         input_ids = input_ids.long()
     if mask is not None:
-        mask = _mask_i32(mask[:, -Lc:] if Lc > 0 else mask[:, :0])
+        mask = _mask_f32(mask[:, -Lc:] if Lc > 0 else mask[:, :0])
     log_p = torch.empty(B, Lc, dtype=torch.float32, device=dev)
     with device_guard(dev):
         rc = L.lib().hilda_selective_log_softmax(L.ptr(logits), L.ptr(input_ids), L.ptr(mask), L.ptr(log_p), B, Lc, N,
@@ -57,8 +59,8 @@ def grpo_loss_forward(logits, completion_ids, advantages, old_logp=None, ref_log
     adv = advantages.to(torch.float32).contiguous()
     old = old_logp.to(torch.float32).contiguous() if old_logp is not None else None
     ref = ref_logp.to(torch.float32).contiguous() if ref_logp is not None else None
-    mask_i = _mask_i32(completion_mask)
-    mask = completion_mask.float() if completion_mask is not None else torch.ones(B, Lc, device=dev)
+    mask_i = _mask_f32(completion_mask)
+    mask = mask_i if completion_mask is not None else torch.ones(B, Lc, device=dev)
 
     loss = torch.empty(B, Lc, device=dev, dtype=torch.float32)
     lse = torch.empty_like(loss)
@@ -75,6 +77,7 @@ def grpo_loss_forward(logits, completion_ids, advantages, old_logp=None, ref_log
                                      float(beta),
                                      float(eps_low), float(eps_high), L.dt(logits), L.stream(dev))
     L.check(rc, "grpo_loss_fwd")
+    L.check_status(ws[:1].view(torch.int32)[0], "grpo_loss_fwd")
     kl_mean = scalars[1] if beta != 0.0 else None
     return scalars[0], kl_mean, scalars[2], lse, mask, dlogits
 

@@ -51,6 +51,60 @@ def _world(group):
     return dist.get_world_size(group), dist.get_rank(group)
 
 
+# ------------------------------------------------------------------ host-side failure detection
+def check_vocab_sharding(BT: int, H: int, V_local: int, vocab_start: int, group=None) -> int:
+    """Collective, host side, before anything is launched: every rank contributes (rows, hidden dim,
+    shard height, shard start) and every rank checks the same list, so all of them accept or all of
+    them raise ValueError. The shards must agree on rows and hidden dim and tile [0, V) without gap
+    or overlap in rank order. Returns V. (A mismatch would otherwise show up as a collective on
+    buffers of different sizes: a hang or a wrong loss.)"""
+    world, rank = _world(group)
+    mine = (int(BT), int(H), int(V_local), int(vocab_start))
+    if world == 1:
+        everyone = [mine]
+    else:
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine, group=group)
+    rows = {e[0] for e in everyone}
+    dims = {e[1] for e in everyone}
+    if len(rows) != 1 or len(dims) != 1:
+        raise ValueError(f"vocab-parallel ranks disagree on hidden's shape (rows, hidden dim): {[(e[0], e[1]) for e in everyone]}")
+    expect = 0
+    for r, (_, _, v, start) in enumerate(everyone):
+        if v <= 0 or start != expect:
+            raise ValueError(f"vocabulary shards do not tile [0, V): rank {r} holds [{start}, {start + v}) but should start "
+                             f"at {expect}; shards {[(e[3], e[3] + e[2]) for e in everyone]}")
+        expect = start + v
+    return expect
+
+
+class RankWatch:
+    """Liveness over the process group's key-value store, for the rule that a rank may leave only
+    between steps with nothing of it in flight: the leaving rank calls ``leave()``; every other rank
+    calls ``check()`` before it launches its next step and gets a RuntimeError naming the ranks that
+    left, instead of entering a collective that can never complete. Pure host logic: no kernel and
+    no collective is involved, so nothing has to time out on a GPU."""
+
+    def __init__(self, store=None, rank=None, world=None, prefix="hilda_b200/left/"):
+        if store is None:
+            store = dist.distributed_c10d._get_default_store()
+        self.store = store
+        self.rank = dist.get_rank() if rank is None else rank
+        self.world = dist.get_world_size() if world is None else world
+        self.prefix = prefix
+
+    def leave(self, reason: str = "left") -> None:
+        self.store.set(f"{self.prefix}{self.rank}", reason)
+
+    def departed(self) -> list:
+        return [r for r in range(self.world) if r != self.rank and self.store.check([f"{self.prefix}{r}"])]
+
+    def check(self) -> None:
+        gone = self.departed()
+        if gone:
+            raise RuntimeError(f"rank(s) {gone} left the job; not launching the next step")
+
+
 # ------------------------------------------------------------------ row-sharded helpers
 def allreduce_weight_grad(dW: torch.Tensor, group=None) -> torch.Tensor:
     """Sum the norm weight gradient over row shards (in fp32, then back to dW's dtype)."""
@@ -107,8 +161,12 @@ class VocabParallelFLCE:
     """Vocab-parallel fused linear + cross entropy. Every rank holds ``weight_shard`` = rows
     [vocab_start, vocab_start + V_local) of the lm_head and the full hidden / targets."""
 
-    def __init__(self, group=None, comm_dtype=torch.float32, overlap_sms=0):
+    def __init__(self, group=None, comm_dtype=torch.float32, overlap_sms=0, validate=True):
         self.group = group
+        # first call with a new (rows, hidden dim, shard height, shard start): one host-side collective
+        # that checks the ranks' shards against each other (check_vocab_sharding); later calls skip it
+        self.validate = validate
+        self._validated = set()
         self.comm_dtype = comm_dtype  # dtype of the d(hidden) all-reduce
         # > 0: reduce each chunk's d(hidden) rows on a second stream beside that chunk's d(W) GEMM,
         # which then leaves this many SMs to the collective (needs comm_dtype == the data dtype)
@@ -128,39 +186,26 @@ class VocabParallelFLCE:
 
     def __call__(self, hidden, weight_shard, targets, vocab_start, ignore_index=-100, reduction='mean',
                  compute_grad=True, chunk_rows=None, skip_ignored=None):
+        """Returns (loss, d_hidden, d_weight_shard). No host synchronisation: the count of non-ignored
+        rows, the compaction of the ignored ones and the status word all stay on the device."""
         from .kernels import fused_linear_cross_entropy as FL
         if skip_ignored is None:
             skip_ignored = FL.SKIP_IGNORED_ROWS
-        if skip_ignored:
-            # hidden and targets are replicated, so every rank drops the same ignored rows
-            keep = (targets != ignore_index).nonzero().squeeze(1)
-            BT = targets.shape[0]
-            if 0 < keep.numel() < BT:
-                hs = hidden.contiguous()
-                H = hs.shape[1]
-                h_c = torch.empty(keep.numel(), H, dtype=hs.dtype, device=hs.device)
-                FL._move_rows("hilda_gather_rows", hs, keep, h_c, H * hs.element_size())
-                loss, dh_c, dw = self(h_c, weight_shard, targets.contiguous()[keep], vocab_start, ignore_index,
-                                      reduction, compute_grad, chunk_rows, skip_ignored=False)
-                dh = None
-                if compute_grad:
-                    dh = torch.empty_like(hs)
-                    FL._move_rows("hilda_scatter_rows", dh_c, keep, dh, BT, H * hs.element_size())
-                if reduction == 'none':
-                    full = torch.zeros(BT, dtype=loss.dtype, device=loss.device)
-                    full[keep] = loss
-                    loss = full
-                return loss, dh, dw
         dev = L.require_cuda(hidden, weight_shard, targets)
         world, rank = _world(self.group)
         BT, H = hidden.shape
         V = weight_shard.shape[0]
         assert weight_shard.shape[1] == H and hidden.dtype == weight_shard.dtype
         assert hidden.dtype in (torch.bfloat16, torch.float16)
+        assert targets.shape[0] == BT
+        if self.validate and world > 1 and (BT, H, V, int(vocab_start)) not in self._validated:
+            check_vocab_sharding(BT, H, V, int(vocab_start), self.group)
+            self._validated.add((BT, H, V, int(vocab_start)))
         hidden = hidden.contiguous()
         weight_shard = weight_shard.contiguous()
         targets = targets.contiguous().long()
         dt = L.dt(hidden)
+        esz = hidden.element_size()
         lib = L.lib()
         with device_guard(dev):
             st = L.stream(dev)
@@ -176,7 +221,22 @@ class VocabParallelFLCE:
             loss_rows = torch.empty(BT, dtype=torch.float32, device=dev)
             head = torch.zeros(2, dtype=torch.int32, device=dev)  # [status, n_valid]
             status_p, n_valid_p = head.data_ptr(), head.data_ptr() + 4
-            L.check(lib.hilda_count_valid(L.ptr(targets), BT, int(ignore_index), n_valid_p, st), "count_valid")
+            dyn = None
+            h_use, t_use = hidden, targets
+            if skip_ignored:
+                # hidden and targets are replicated, so every rank drops the same ignored rows; the
+                # lists are built on the device and every later step follows the device-side count
+                idx = torch.empty(BT, dtype=torch.int64, device=dev)
+                inv = torch.empty(BT, dtype=torch.int32, device=dev)
+                t_use = torch.empty(BT, dtype=torch.int64, device=dev)
+                h_use = torch.empty_like(hidden)
+                L.check(lib.hilda_flce_compact(L.ptr(targets), BT, int(ignore_index), L.ptr(idx), L.ptr(inv),
+                                               L.ptr(t_use), n_valid_p, st), "flce_compact")
+                L.check(lib.hilda_gather_valid_rows(L.ptr(hidden), L.ptr(idx), n_valid_p, L.ptr(h_use), BT, H * esz, st),
+                        "gather_valid_rows")
+                dyn = n_valid_p
+            else:
+                L.check(lib.hilda_count_valid(L.ptr(targets), BT, int(ignore_index), n_valid_p, st), "count_valid")
             # partial sums of d(hidden) over the vocabulary shards: fp32 when they are reduced in fp32,
             # otherwise written by the GEMM directly in the 16-bit dtype they are reduced in
             reduce32 = compute_grad and world > 1 and self.comm_dtype == torch.float32
@@ -184,36 +244,41 @@ class VocabParallelFLCE:
             dh = torch.empty_like(hidden) if compute_grad else None
             dw = torch.empty_like(weight_shard) if compute_grad else None
             dw32 = torch.empty(V, H, dtype=torch.float32, device=dev) if (compute_grad and n_chunks > 1) else None
+            if compute_grad and skip_ignored and world > 1:
+                # rows of the compacted d(hidden) beyond the count are never written by the GEMM but
+                # do take part in the all-reduce: they must hold finite values
+                (dh32 if reduce32 else dh).zero_()
             reduced_rows = 0
             for c in range(n_chunks):
                 r0 = c * chunk_rows
                 rows = min(chunk_rows, BT - r0)
-                hc = hidden[r0:r0 + rows]
-                tc = targets[r0:r0 + rows]
+                hc = h_use[r0:r0 + rows]
+                tc = t_use[r0:r0 + rows]
                 L.check(lib.hilda_flce_logits(L.ptr(hc), L.ptr(weight_shard), L.ptr(scratch), L.ptr(stats), rows, H, V,
-                                              dt, status_p, st), "flce_logits")
+                                              dt, status_p, dyn, r0, st), "flce_logits")
                 rs = rowstat[:, :rows].contiguous() if rows != chunk_rows else rowstat
                 L.check(lib.hilda_flce_row_stats(L.ptr(stats), L.ptr(scratch), L.ptr(tc), L.ptr(rs), rows, V,
-                                                 int(vocab_start), dt, st), "flce_row_stats")
+                                                 int(vocab_start), dt, dyn, r0, st), "flce_row_stats")
+                n_shards = 1
                 if world > 1:
                     gathered = torch.empty(world * 3, rows, dtype=torch.float32, device=dev)
                     dist.all_gather_into_tensor(gathered, rs, group=self.group)
-                    rs = combine_rowstats(gathered.view(world, 3, rows)).contiguous()
-                L.check(lib.hilda_flce_finalize(L.ptr(rs), L.ptr(tc), int(ignore_index), L.ptr(lse),
-                                                loss_rows.data_ptr() + 4 * r0, rows, st), "flce_finalize")
+                    rs, n_shards = gathered, world  # merged inside the finalize kernel
+                L.check(lib.hilda_flce_finalize(L.ptr(rs), n_shards, L.ptr(tc), int(ignore_index), L.ptr(lse),
+                                                loss_rows.data_ptr() + 4 * r0, rows, dyn, r0, st), "flce_finalize")
                 if not compute_grad:
                     continue
                 L.check(lib.hilda_flce_dlogits(L.ptr(scratch), L.ptr(lse), L.ptr(tc), int(ignore_index),
                                                n_valid_p if reduction == 'mean' else None, rows, V, int(vocab_start),
-                                               dt, st), "flce_dlogits")
+                                               dt, dyn, r0, st), "flce_dlogits")
                 if reduce32:
                     L.check(lib.hilda_flce_grad_hidden(L.ptr(scratch), L.ptr(weight_shard), None,
-                                                       dh32.data_ptr() + 4 * r0 * H, rows, H, V, dt, status_p, st),
-                            "flce_grad_hidden")
+                                                       dh32.data_ptr() + 4 * r0 * H, rows, H, V, dt, status_p, dyn, r0,
+                                                       st), "flce_grad_hidden")
                 else:
                     L.check(lib.hilda_flce_grad_hidden(L.ptr(scratch), L.ptr(weight_shard),
-                                                       dh.data_ptr() + 2 * r0 * H, None, rows, H, V, dt, status_p, st),
-                            "flce_grad_hidden")
+                                                       dh.data_ptr() + 2 * r0 * H, None, rows, H, V, dt, status_p, dyn,
+                                                       r0, st), "flce_grad_hidden")
                 mode = 3 if n_chunks == 1 else (0 if c == 0 else (2 if c == n_chunks - 1 else 1))
                 overlap = world > 1 and self.overlap_sms > 0 and not reduce32 and self.comm_dtype == dh.dtype
                 if overlap:
@@ -226,7 +291,7 @@ class VocabParallelFLCE:
                     lib.hilda_gemm_set_sm_limit(self._sm_count(dev) - self.overlap_sms)
                 try:
                     L.check(lib.hilda_flce_grad_weight(L.ptr(scratch), L.ptr(hc), L.ptr(dw32), L.ptr(dw), mode, rows, H,
-                                                       V, dt, status_p, st), "flce_grad_weight")
+                                                       V, dt, status_p, dyn, r0, st), "flce_grad_weight")
                 finally:
                     if overlap:
                         lib.hilda_gemm_set_sm_limit(0)
@@ -244,14 +309,23 @@ class VocabParallelFLCE:
                     buf = dh.to(self.comm_dtype)
                     dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=self.group)
                     dh.copy_(buf)
+            if skip_ignored:
+                if compute_grad:
+                    dh_c, dh = dh, torch.empty_like(hidden)
+                    L.check(lib.hilda_scatter_valid_rows(L.ptr(dh_c), L.ptr(inv), L.ptr(dh), BT, H * esz, st),
+                            "scatter_valid_rows")
+                if reduction == 'none':
+                    lr_c, loss_rows = loss_rows, torch.empty_like(loss_rows)
+                    L.check(lib.hilda_scatter_valid_f32(L.ptr(lr_c), L.ptr(inv), L.ptr(loss_rows), BT, st),
+                            "scatter_valid_f32")
+            if reduction == 'none':
+                loss = loss_rows
+            else:
+                # one reduction kernel; NaN if a bounded wait inside a GEMM ran out on this rank
+                loss = torch.empty((), dtype=torch.float32, device=dev)
+                L.check(lib.hilda_flce_sum_loss(L.ptr(loss_rows), BT, n_valid_p, 1 if reduction == 'mean' else 0,
+                                                status_p, L.ptr(loss), st), "flce_sum_loss")
         self.last_status = head
-        n_valid = head[1]
-        if reduction == 'none':
-            loss = loss_rows
-        elif reduction == 'sum':
-            loss = loss_rows.sum()
-        else:
-            loss = loss_rows.sum() / n_valid.clamp_min(1).to(torch.float32)
         return loss, dh, dw
 
     def check_status(self):

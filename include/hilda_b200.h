@@ -124,22 +124,32 @@ int hilda_scale_rows(const void* in, void* out, const float* scale, int per_row,
  * none (per-row loss in loss_rows), 1 mean, 2 sum (fp32 scalar loss_out). dh [BT, H] and dw [V, H]
  * (both or neither) receive the gradients for a unit upstream gradient. Rows are processed in
  * chunks of chunk_rows (<= 0: library default, scratch <= 1.25 GiB); the chunk's logits live in the
- * workspace, the full [BT, V] logits never exist. The call only enqueues work; afterwards the
- * int at workspace[0] is non-zero if a bounded device-side wait ran out (HILDA_ERR_DEVICE). */
+ * workspace, the full [BT, V] logits never exist. flags: HILDA_FLCE_COMPACT = the rows whose target
+ * is ignore_index are compacted away ON THE DEVICE before the GEMMs (they contribute nothing to the
+ * loss or to either gradient; their dh rows come back as zeros); the reference runs its GEMMs over
+ * them and pays a host synchronisation for their count (:121), this call pays none. The call only
+ * enqueues work; afterwards the int at workspace[0] is non-zero if a bounded device-side wait ran
+ * out (HILDA_ERR_DEVICE), and a mean / sum loss is then NaN. */
+#define HILDA_FLCE_COMPACT 1
 int64_t hilda_flce_default_chunk_rows(int64_t BT, int64_t H, int64_t V);
-int64_t hilda_flce_workspace_bytes(int64_t BT, int64_t H, int64_t V, int64_t chunk_rows, int with_grad);
+int64_t hilda_flce_workspace_bytes(int64_t BT, int64_t H, int64_t V, int64_t chunk_rows, int with_grad, int flags);
 int hilda_fused_linear_cross_entropy_fwd(const void* hidden, const void* W, const int64_t* targets, float* loss_out,
                                          float* loss_rows, void* dh, void* dw, void* workspace, int64_t BT,
                                          int64_t H, int64_t V, int64_t ignore_index, int reduction,
-                                         int64_t chunk_rows, int dtype, void* stream);
+                                         int64_t chunk_rows, int dtype, int flags, void* stream);
 
 /* The same operator as separate steps, for the vocab-parallel form (W sharded by rows over
  * ranks; no counterpart in the reference, which is single-device): between row_stats and
- * finalize the caller combines the per-row (max, sum-exp, target logit) triples of all ranks.
+ * finalize the caller gathers the per-row (max, sum-exp, target logit) triples of all ranks.
  *   logits scratch: [hilda_flce_padded_rows(rows), hilda_flce_logits_pitch(V)] 16-bit
  *   stats:          [rows, hilda_flce_stat_tiles(V), 2] fp32
  *   rowstat:        [3, rows] fp32 = natural-log max, sum exp(x - max), target logit (0 if the
- *                   target is outside [vocab_start, vocab_start + V)) */
+ *                   target is outside [vocab_start, vocab_start + V))
+ * dyn_rows / dyn_off (dyn_rows nullable = off): a DEVICE int holding how many leading rows of the
+ * whole (compacted) batch are real, and the index of this call's first row in that batch. Rows at
+ * or beyond the count are skipped: GEMM tiles (logits, d hidden) and k-blocks (d W) beyond it do
+ * not run. Their targets must equal ignore_index and their hidden rows must be zero up to the next
+ * multiple of 256 (what hilda_flce_compact / hilda_gather_valid_rows produce). */
 int64_t hilda_flce_logits_pitch(int64_t V);
 int64_t hilda_flce_padded_rows(int64_t rows);
 int64_t hilda_flce_stat_tiles(int64_t V);
@@ -147,27 +157,51 @@ int64_t hilda_flce_stat_tiles(int64_t V);
 int hilda_count_valid(const int64_t* targets, int64_t n, int64_t ignore_index, int* out, void* stream);
 /* logits = hidden @ W^T rounded to dtype (fused_linear_cross_entropy.py:140) + online-LSE tile stats. */
 int hilda_flce_logits(const void* hidden, const void* W, void* logits, float* stats, int64_t rows, int64_t H,
-                      int64_t V, int dtype, int* status, void* stream);
+                      int64_t V, int dtype, int* status, const int* dyn_rows, int64_t dyn_off, void* stream);
 /* The same with the statistics taken of logits * inv_temperature (stored logits unscaled): the
  * log-softmax at a temperature of the fused linear + JSD loss (kernels/fused_linear_jsd.py:46-62). */
 int hilda_flce_logits_scaled(const void* hidden, const void* W, void* logits, float* stats, int64_t rows, int64_t H,
                              int64_t V, float inv_temperature, int dtype, int* status, void* stream);
 /* targets may be null: no target logit is fetched (rowstat[2] = 0). */
 int hilda_flce_row_stats(const float* stats, const void* logits, const int64_t* targets, float* rowstat,
-                         int64_t rows, int64_t V, int64_t vocab_start, int dtype, void* stream);
-int hilda_flce_finalize(const float* rowstat, const int64_t* targets, int64_t ignore_index, float* lse,
-                        float* loss_rows, int64_t rows, void* stream);
+                         int64_t rows, int64_t V, int64_t vocab_start, int dtype, const int* dyn_rows,
+                         int64_t dyn_off, void* stream);
+/* lse = max + log(sum-exp), loss = lse - target logit (0 on ignored rows). rowstat is [3, rows]
+ * (n_shards <= 1) or the gathered [n_shards, 3, rows] of all vocabulary shards, merged here. */
+int hilda_flce_finalize(const float* rowstat, int n_shards, const int64_t* targets, int64_t ignore_index,
+                        float* lse, float* loss_rows, int64_t rows, const int* dyn_rows, int64_t dyn_off,
+                        void* stream);
 /* In place: logits -> (softmax - onehot) * (n_valid ? 1/max(*n_valid,1) : 1); ignored rows -> 0
  * (the second pass of _ce_fwd_inplace_kernel, fused_linear_cross_entropy.py:66-77). */
 int hilda_flce_dlogits(void* logits, const float* lse, const int64_t* targets, int64_t ignore_index,
-                       const int* n_valid, int64_t rows, int64_t V, int64_t vocab_start, int dtype, void* stream);
+                       const int* n_valid, int64_t rows, int64_t V, int64_t vocab_start, int dtype,
+                       const int* dyn_rows, int64_t dyn_off, void* stream);
 /* dh = dlogits @ W (fused_linear_cross_entropy.py:158); exactly one of dh16 / dh32 non-null. */
 int hilda_flce_grad_hidden(const void* dlogits, const void* W, void* dh16, float* dh32, int64_t rows, int64_t H,
-                           int64_t V, int dtype, int* status, void* stream);
+                           int64_t V, int dtype, int* status, const int* dyn_rows, int64_t dyn_off, void* stream);
 /* dW (+)= dlogits^T @ hidden (fused_linear_cross_entropy.py:161). mode 0: dw32 = .; 1: dw32 += .;
  * 2: dw16 = dw32 + .; 3: dw16 = . */
 int hilda_flce_grad_weight(const void* dlogits, const void* hidden, float* dw32, void* dw16, int mode,
-                           int64_t rows, int64_t H, int64_t V, int dtype, int* status, void* stream);
+                           int64_t rows, int64_t H, int64_t V, int dtype, int* status, const int* dyn_rows,
+                           int64_t dyn_off, void* stream);
+/* *out = sum(rows) (/ max(*n_valid, 1) when divide != 0); NaN if status is given and *status != 0
+ * (the final reduction of fused_linear_cross_entropy.py:165-171, on the device). */
+int hilda_flce_sum_loss(const float* rows, int64_t n, const int* n_valid, int divide, const int* status, float* out,
+                        void* stream);
+
+/* Device-side compaction of the ignored tokens (no counterpart in the reference). hilda_flce_compact:
+ * idx int64 [n] = source row of compacted row j (-1 beyond the count), inv int32 [n] = compacted
+ * position of row i (-1 if ignored), t_c int64 [n] = targets in compacted order (ignore_index beyond
+ * the count), *n_valid = the count. hilda_gather_valid_rows: dst[j,:] = src[idx[j],:] for the leading
+ * *n_valid rows, zero rows up to the next multiple of 256, the rest untouched. hilda_scatter_valid_rows:
+ * dst[i,:] = inv[i] >= 0 ? src[inv[i],:] : 0 for all n rows. hilda_scatter_valid_f32: the same for one
+ * fp32 value per row. Rows of row_bytes (multiple of 16) bytes. */
+int hilda_flce_compact(const int64_t* targets, int64_t n, int64_t ignore_index, int64_t* idx, int* inv, int64_t* t_c,
+                       int* n_valid, void* stream);
+int hilda_gather_valid_rows(const void* src, const int64_t* idx, const int* n_valid, void* dst, int64_t n,
+                            int64_t row_bytes, void* stream);
+int hilda_scatter_valid_rows(const void* src, const int* inv, void* dst, int64_t n, int64_t row_bytes, void* stream);
+int hilda_scatter_valid_f32(const float* in, const int* inv, float* out, int64_t n, void* stream);
 
 /* Measurement hook (no counterpart in the reference): while enabled, every GEMM launch of the
  * FLCE entry points is bracketed by CUDA events on its stream. collect waits for them and returns
@@ -176,14 +210,16 @@ int hilda_flce_grad_weight(const void* dlogits, const void* hidden, float* dw32,
 void hilda_flce_profile(int enable);
 int hilda_flce_profile_collect(float* ms_per_kind, int* launches_per_kind);
 
-/* Row compaction for skipping ignored tokens (no counterpart in the reference, which runs its
- * GEMMs over ignored rows too): dst[i,:] = src[idx[i],:] and dst[idx[i],:] = src[i,:] over rows of
- * row_bytes (multiple of 16) bytes; the scatter zero-fills the n_dst_rows rows of dst first. */
+/* Row moves with an index list whose length the host knows (no counterpart in the reference):
+ * dst[i,:] = src[idx[i],:] and dst[idx[i],:] = src[i,:] over rows of row_bytes (multiple of 16)
+ * bytes; the scatter zero-fills the n_dst_rows rows of dst first. */
 int hilda_gather_rows(const void* src, const int64_t* idx, void* dst, int64_t n_idx, int64_t row_bytes, void* stream);
 int hilda_scatter_rows(const void* src, const int64_t* idx, void* dst, int64_t n_idx, int64_t n_dst_rows,
                        int64_t row_bytes, void* stream);
 
-/* GEMM variant used by the FLCE entry points (no counterpart in the reference), per use: bit 0 =
+/* The setters from here to hilda_gemm_set_probe act on the CALLING HOST THREAD's later launches only
+ * (thread-local state), so threads that drive different GPUs do not disturb each other.
+ * GEMM variant used by the FLCE entry points (no counterpart in the reference), per use: bit 0 =
  * logits GEMM, bit 1 = d(hidden) GEMM, bit 2 = d(W) GEMM run on CTA pairs (tcgen05 cta_group::2,
  * 256 x 256 tiles over two SMs); a clear bit = one CTA per 128 x 256 tile. hilda_debug_gemm uses
  * pairs when any bit is set. Initial value: environment HILDA_GEMM_PAIR, else the built-in default. */
@@ -192,13 +228,18 @@ int hilda_gemm_get_pair(void);
 /* The FLCE GEMMs launch on at most `sms` SMs (0 = all) until set back; used to leave a few SMs to a
  * collective that runs on another stream beside a GEMM. No counterpart in the reference. */
 void hilda_gemm_set_sm_limit(int sms);
+/* Attempts every bounded mbarrier wait of the GEMM kernels makes before it gives up, writes a code
+ * to the status word and lets the CTA return (0 = the default, 2^22). No counterpart in the reference. */
+void hilda_gemm_set_wait_cap(unsigned attempts);
 /* Tile walk order hilda_debug_gemm uses (1 = M first, 0 = N first); no counterpart in the reference. */
 void hilda_debug_gemm_set_order(int m_fast);
 /* Cycle counters of the GEMM kernels' role loops, written by every launch while set: device
  * buffer of [SM count][8] int64 {producer wait-for-slot, producer total, issuer wait-for-data,
  * issuer wait-for-accumulator, issuer total, epilogue wait-for-accumulator, epilogue busy, 0};
- * NULL switches it off (the default). dry != 0 is for measurement only (results are garbage): the
- * producer marks its slots full without loading, taking the memory system out of the loop. */
+ * NULL switches it off (the default). dry = 1 is for measurement only (results are garbage): the
+ * producer marks its slots full without loading, taking the memory system out of the loop. dry = 2
+ * exercises the failure path: the producer neither loads nor signals, every bounded wait runs out,
+ * the status word is set and the kernel returns with nothing in flight. */
 void hilda_gemm_set_probe(void* buf, int dry);
 
 /* Validation hook: plain C = A x B through the tcgen05 kernel with either operand K-major
@@ -282,19 +323,20 @@ int hilda_paged_attention_set_path(int path);
 /* ---- GRPO --------------------------------------------------------------------------------- */
 int64_t hilda_grpo_workspace_bytes(int64_t B);
 /* Replaces grpo_loss_forward + grpo_loss_backward (kernels/grpo_loss.py:241-297, :300-330) in one
- * pass. logits [B, L+1, V]; ids [B, L] int64; mask [B, L] int32 or null; advantages [B] fp32;
+ * pass. logits [B, L+1, V]; ids [B, L] int64; mask [B, L] fp32 or null (0 = token skipped; otherwise its weight in the
+ * reductions, the reference's completion_mask.float(), grpo_loss.py:264); advantages [B] fp32;
  * old_logp/ref_logp [B, L] fp32 or null. Per-token fp32 outputs loss/kl/clipped/lse [B, L];
  * scalars_out[4] = {loss, kl_mean, clip_ratio, sum(mask)}; B_total > 0 normalises loss and gradient by
  * B_total sequences instead of B (sequences sharded over ranks). grad (nullable): d loss / d logits for a unit
  * upstream gradient, [B, L+1, V] in dtype, last position and masked tokens zero. */
 int hilda_grpo_loss_fwd(const void* logits, const int64_t* ids, const float* advantages, const float* old_logp,
-                        const float* ref_logp, const int32_t* mask, void* grad, float* loss, float* kl,
+                        const float* ref_logp, const float* mask, void* grad, float* loss, float* kl,
                         float* clipped, float* lse, float* scalars_out, void* workspace, int64_t B, int64_t L,
                         int64_t V, int64_t B_total, float temperature, float beta, float eps_low, float eps_high,
                         int dtype, void* stream);
 
 /* Replaces fused_selective_log_softmax (kernels/grpo_loss.py:65-80). */
-int hilda_selective_log_softmax(const void* logits, const int64_t* ids, const int32_t* mask, float* logp,
+int hilda_selective_log_softmax(const void* logits, const int64_t* ids, const float* mask, float* logp,
                                 int64_t B, int64_t L, int64_t V, float temperature, int dtype, void* stream);
 
 /* Tuning hook for the row engine behind CrossEntropy/GRPO: force (vectors per thread, CTAs per

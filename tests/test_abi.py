@@ -52,9 +52,12 @@ def test_size_queries_need_no_gpu(libpath):
         lib.hilda_gemm_set_pair(default)
     assert lib.hilda_flce_default_chunk_rows(100, 64, 1000) == 100
     assert lib.hilda_flce_default_chunk_rows(4096, 4096, 128256) == 4096
-    one = lib.hilda_flce_workspace_bytes(4096, 4096, 128256, 4096, 1)
-    four = lib.hilda_flce_workspace_bytes(16384, 4096, 128256, 4096, 1)
+    one = lib.hilda_flce_workspace_bytes(4096, 4096, 128256, 4096, 1, 0)
+    four = lib.hilda_flce_workspace_bytes(16384, 4096, 128256, 4096, 1, 0)
     assert four - one >= 128256 * 4096 * 4  # the fp32 dW accumulator appears only with > 1 chunk
+    # compaction on the device adds the index lists and the compacted hidden / d(hidden) copies
+    compact = lib.hilda_flce_workspace_bytes(16384, 4096, 128256, 4096, 1, 1)
+    assert compact - four >= 2 * 16384 * 4096 * 2 + 16384 * 20
     assert lib.hilda_cross_entropy_workspace_bytes(8192) >= 16
     assert lib.hilda_grpo_workspace_bytes(16) >= 16 + 64
 
@@ -142,3 +145,16 @@ def test_top_level_kernels_package_like_the_reference_benches():
     with tempfile.TemporaryDirectory() as tmp:
         r = subprocess.run([sys.executable, "-c", code], cwd=tmp, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "dropin ok" in r.stdout, r.stderr[-2000:]
+
+
+def test_debug_flag_compiles(tmp_path):
+    """The -DHILDA_DEBUG variant (every launch followed by a synchronise-and-check) compiles for
+    sm_100a; two small sources stand for the whole library here, the full debug build takes minutes."""
+    import subprocess
+    from hilda_kernel_b200 import _build
+    for name in ("swiglu.cu", "rope.cu"):
+        obj = str(tmp_path / (name + ".o"))
+        cmd = _build.compile_one(os.path.join(_build.CSRC, name), obj, debug=True)
+        assert "-DHILDA_DEBUG" in cmd
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0 and os.path.getsize(obj) > 0, r.stderr[-2000:]

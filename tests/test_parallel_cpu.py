@@ -116,3 +116,101 @@ def test_vocab_parallel_exchange_gloo_world2():
         assert p.exitcode == 0
     results = dict(q.get(timeout=5) for _ in range(2))
     assert results == {0: True, 1: True}
+
+
+# ------------------------------------------------------------------ failure detection on the host
+def _run_ranks(target, world, *args, timeout=120):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=target, args=(r, world, port, q, *args)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=timeout)
+        assert p.exitcode is not None, "a rank hung"
+    out = {}
+    while not q.empty():
+        r, v = q.get(timeout=5)
+        out[r] = v
+    return out
+
+
+def _shard_check_worker(rank, world, port, q, case):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from hilda_kernel_b200.parallel import check_vocab_sharding
+        V = 1000
+        v0, v1 = shard_bounds(V, world, rank, 8)
+        BT, H = 64, 32
+        if case == "overlap" and rank == 1:
+            v0 -= 8
+        if case == "gap" and rank == 1:
+            v0 += 8
+        if case == "rows" and rank == 1:
+            BT = 65
+        try:
+            total = check_vocab_sharding(BT, H, v1 - v0, v0)
+            q.put((rank, ("ok", total)))
+        except ValueError as e:
+            q.put((rank, ("rejected", str(e)[:60])))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("case", ["good", "overlap", "gap", "rows"])
+def test_mismatched_shards_are_rejected_on_every_rank(case):
+    res = _run_ranks(_shard_check_worker, 2, case)
+    assert set(res) == {0, 1}
+    if case == "good":
+        assert res[0] == res[1] == ("ok", 1000)
+    else:
+        assert res[0][0] == res[1][0] == "rejected", res  # both ranks refuse, so neither enters a collective alone
+
+
+def _leaving_worker(rank, world, port, q):
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    from hilda_kernel_b200.parallel import RankWatch
+    watch = RankWatch()
+    x = torch.ones(3, 4)
+    out = torch.empty(world * 3, 4)
+    dist.all_gather_into_tensor(out, x)   # step 0: everyone is there
+    watch.check()
+    if rank == 1:
+        watch.leave("done early")         # between steps, nothing in flight
+        q.put((rank, "left"))
+        q.close()
+        q.join_thread()
+        time.sleep(1.0)
+        os._exit(0)
+    # rank 0: learns of it on the host before its next launch ...
+    t0 = time.time()
+    while not watch.departed() and time.time() - t0 < 20:
+        time.sleep(0.05)
+    try:
+        watch.check()
+        q.put((rank, "not noticed"))
+        return
+    except RuntimeError as e:
+        noticed = "rank(s) [1]" in str(e)
+    # ... and if it entered the exchange all the same, the short process-group timeout ends it with an error
+    t1 = time.time()
+    try:
+        dist.all_gather_into_tensor(out, x)
+        ended = "completed?"
+    except Exception:
+        ended = "error"
+    q.put((rank, (noticed, ended, time.time() - t1 < 60)))
+    q.close()
+    q.join_thread()   # the result is on its way before the process ends without further clean-up
+    os._exit(0)
+
+
+def test_a_rank_that_leaves_between_steps_is_noticed_and_the_exchange_errors_out():
+    res = _run_ranks(_leaving_worker, 2, timeout=180)
+    assert res.get(1) == "left"
+    assert res.get(0) == (True, "error", True), res

@@ -28,6 +28,11 @@ import time
 import torch
 import torch.nn.functional as F
 
+try:  # Liger 0.8 looks at torch.distributed.tensor.DTensor without importing the sub-module itself
+    import torch.distributed.tensor  # noqa: F401
+except Exception:
+    pass
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 REF_DIR = os.path.join(ROOT, "baseline", "_ref")
 DEV = "cuda"

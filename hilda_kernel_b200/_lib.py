@@ -38,6 +38,7 @@ SIGNATURES = {
     "hilda_fused_add_rms_norm_fwd": (_i32, [_p, _p, _p, _p, _p, _p, _i64, _i64, _f32, _i32, _i32, _p]),
     "hilda_norm_bwd_workspace_bytes": (_i64, [_i64, _i64, _i32]),
     "hilda_norm_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i32, _i32, _p]),
+    "hilda_norm_bwd_set_path": (_i32, [_i32]),
     "hilda_norm_bwd_noalloc_max_bytes": (_i64, []),
     "hilda_norm_bwd_noalloc": (_i32, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i32, _i32, _p]),
     "hilda_rope": (_i32, [_p, _p, _p, _i32, _p, _p, _p, _i32, _p, _p, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _p]),

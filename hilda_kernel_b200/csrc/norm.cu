@@ -9,6 +9,7 @@
 // tensor is read once and written once. dW is accumulated per CTA in registers over the rows it
 // owns, written as one fp32 partial row per CTA, and reduced by a second small kernel (fixed
 // order, no atomics, bit-reproducible).
+#include <cstdlib>
 #include "common.cuh"
 
 namespace hilda {
@@ -217,6 +218,163 @@ norm_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __r
   }
 }
 
+// ---- backward with the row loads decoupled from the arithmetic --------------------------------
+// norm_bwd_kernel above keeps ONE row per CTA in flight and goes load -> block reduction -> store, so
+// every row exposes a DRAM round trip (2 CTAs of 122 registers per SM for fp32: about 64 KB in
+// flight per SM, and only during the load phase). Here a CTA owns a ring of `stages` shared-memory
+// slots; one thread fills a slot with the row's dY, X (and dS) by bulk asynchronous copies
+// (cp.async.bulk, completion counted on an mbarrier) and refills it as soon as the CTA has taken the
+// row into registers, so `stages` rows per CTA are in flight the whole time while the CTA reduces
+// and stores the current one. Same arithmetic, same order, same results as norm_bwd_kernel.
+__device__ __forceinline__ uint32_t nb_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void nb_bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ bool nb_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+constexpr uint32_t NB_WAIT_CAP = 1u << 24;  // try_wait attempts (each suspends for a while) before giving up
+constexpr int NB_MAX_STAGES = 6;
+
+template <typename T, int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS, (sizeof(T) == 2 && VPT <= 2) ? (1024 / THREADS) : 1)
+norm_bwd_ring_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __restrict__ X,
+                     const void* __restrict__ W, int w_dt, const float* __restrict__ RSTD,
+                     T* __restrict__ dX, float* __restrict__ partial, int64_t n_rows, int n_cols, int stages) {
+  constexpr int VEC = VT<T>::N;
+  extern __shared__ __align__(128) uint8_t ring[];
+  __shared__ __align__(8) uint64_t full_bar[NB_MAX_STAGES];
+  __shared__ float red[33];
+  __shared__ int gave_up;
+  const int n_vec = n_cols / VEC;
+  const int tid = threadIdx.x;
+  const float inv_n = 1.0f / (float)n_cols;
+  const uint32_t row_bytes = (uint32_t)n_cols * (uint32_t)sizeof(T);
+  const int n_tensors = 1 + (dY ? 1 : 0) + (dS ? 1 : 0);
+  const uint32_t stage_bytes = row_bytes * n_tensors;
+  // slot layout: X, then dY (if any), then dS (if any)
+  const uint32_t off_dy = row_bytes, off_ds = row_bytes * (dY ? 2u : 1u);
+  const uint32_t ring0 = nb_smem_u32(ring), bar0 = nb_smem_u32(full_bar);
+  const int64_t n_mine = (n_rows > (int64_t)blockIdx.x) ? (n_rows - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+
+  auto issue = [&](int64_t it) {  // thread 0 only: fill slot it % stages with this CTA's it-th row
+    const int s = (int)(it % stages);
+    const int64_t row = (int64_t)blockIdx.x + it * gridDim.x;
+    const uint32_t dst = ring0 + (uint32_t)s * stage_bytes, bar = bar0 + 8u * s;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(stage_bytes) : "memory");
+    nb_bulk_load(dst, X + row * n_cols, row_bytes, bar);
+    if (dY) nb_bulk_load(dst + off_dy, dY + row * n_cols, row_bytes, bar);
+    if (dS) nb_bulk_load(dst + off_ds, dS + row * n_cols, row_bytes, bar);
+  };
+
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0 + 8u * s) : "memory");
+    gave_up = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    for (int64_t it = 0; it < n_mine && it < stages; ++it) issue(it);
+  }
+  __syncthreads();
+
+  float dw[VPT][VEC];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i)
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) dw[i][j] = 0.f;
+
+  int64_t it = 0;
+  for (; it < n_mine; ++it) {
+    const int s = (int)(it % stages);
+    const uint32_t parity = (uint32_t)((it / stages) & 1);
+    const int64_t row = (int64_t)blockIdx.x + it * gridDim.x;
+    const float rstd = RSTD[row];
+    bool ok = false;
+    for (uint32_t t = 0; t < NB_WAIT_CAP; ++t)
+      if (nb_try_wait(bar0 + 8u * s, parity)) { ok = true; break; }
+    if (!ok) gave_up = 1;  // reported below; every thread sees the same barrier, so all or none get here
+    const uint8_t* slot = ring + (size_t)s * stage_bytes;
+    uint4 dyv[VPT], xv[VPT], dsv[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = tid + i * THREADS;
+      const bool in = v < n_vec;
+      xv[i] = in ? *reinterpret_cast<const uint4*>(slot + (size_t)v * 16) : make_uint4(0, 0, 0, 0);
+      dyv[i] = (in && dY) ? *reinterpret_cast<const uint4*>(slot + off_dy + (size_t)v * 16) : make_uint4(0, 0, 0, 0);
+      dsv[i] = (in && dS) ? *reinterpret_cast<const uint4*>(slot + off_ds + (size_t)v * 16) : make_uint4(0, 0, 0, 0);
+    }
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = tid + i * THREADS;
+      float dy[VEC], x[VEC], w[VEC];
+      VT<T>::unpack(dyv[i], dy);
+      VT<T>::unpack(xv[i], x);
+      if (v < n_vec) {
+        load_w_vec<VEC>(W, w_dt, v * VEC, w);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) acc = fmaf(dy[j] * w[j], x[j], acc);
+      }
+    }
+    // the block sum's barriers also mean: every thread has taken its part of the slot into registers
+    acc = block_sum<THREADS>(acc, red);
+    if (gave_up) break;
+    if (tid == 0 && it + stages < n_mine) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the reads above before the refill below
+      issue(it + stages);
+    }
+    const float coef = rstd * rstd * rstd * (acc * inv_n);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = tid + i * THREADS;
+      float dy[VEC], x[VEC], dx[VEC], w[VEC];
+      VT<T>::unpack(dyv[i], dy);
+      VT<T>::unpack(xv[i], x);
+      if (v < n_vec) {
+        load_w_vec<VEC>(W, w_dt, v * VEC, w);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+          dx[j] = rstd * (dy[j] * w[j]) - coef * x[j];
+          dw[i][j] = fmaf(dy[j], x[j] * rstd, dw[i][j]);
+        }
+        if (dS != nullptr) {
+          float ds[VEC];
+          VT<T>::unpack(dsv[i], ds);
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) dx[j] += ds[j];
+        }
+        st16(dX + row * n_cols + (int64_t)v * VEC, VT<T>::pack(dx));
+      }
+    }
+  }
+  if (gave_up) {
+    // A wait ran out (it never should: the copies are this CTA's own). Say so loudly, NaN in this CTA's
+    // partial sums and therefore in dW, and before leaving wait, again bounded, for the copies still
+    // in flight into this CTA's shared memory.
+    for (int64_t j = it; j < n_mine && j < it + stages; ++j)
+      for (uint32_t t = 0; t < NB_WAIT_CAP; ++t)
+        if (nb_try_wait(bar0 + 8u * (int)(j % stages), (uint32_t)((j / stages) & 1))) break;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) dw[i][j] = __int_as_float(0x7fc00000);
+  }
+  float* pr = partial + (int64_t)blockIdx.x * n_cols;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * THREADS;
+    if (v < n_vec) {
+#pragma unroll
+      for (int j = 0; j < VEC; j += 4)
+        st16(pr + (int64_t)v * VEC + j, VT<float>::pack(&dw[i][j]));
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 norm_bwd_generic_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __restrict__ X,
@@ -339,21 +497,61 @@ static int norm_bwd_ctas(int64_t n_rows, int64_t n_cols, bool al) {
   return (int)ctas;
 }
 
+// 1 (default): the backward stages its rows through a shared-memory ring (norm_bwd_ring_kernel) when
+// at least two slots fit; 0: always the register-only kernel. Per host thread. HILDA_NORM_RING presets it.
+static int norm_ring_default() {
+  static const int v = []() { const char* e = getenv("HILDA_NORM_RING"); return e ? (atoi(e) != 0) : 1; }();
+  return v;
+}
+static thread_local int g_norm_ring = norm_ring_default();
+
 template <typename T>
 static int norm_bwd_t(const void* dy, const void* ds, const void* x, const void* w, int w_dt, const float* rstd,
-                      void* dx, void* dw, float* workspace, int64_t n_rows, int64_t n_cols, cudaStream_t st) {
+                      void* dx, void* dw, float* workspace, int64_t n_rows, int64_t n_cols, cudaStream_t st,
+                      int64_t max_ctas = 0) {
   const bool al = aligned16(x) && aligned16(dx) && aligned16(w) && aligned16(workspace) &&
                   (!dy || aligned16(dy)) && (!ds || aligned16(ds));
   const int pref = (sizeof(T) == 4) ? 4 : 2;
   NormPlan plan = plan_norm(n_cols, VT<T>::N, pref, al);
   // The workspace is sized for the aligned plan; a misaligned call uses no more CTAs than that.
   int grid = norm_bwd_ctas<T>(n_rows, n_cols, true);
+  if (max_ctas > 0 && grid > max_ctas) grid = (int)max_ctas;  // the rows are walked with a grid stride: any grid is correct
   if (plan.generic) {
     int g2 = norm_bwd_ctas<T>(n_rows, n_cols, false);
     if (g2 < grid) grid = g2;
     norm_bwd_generic_kernel<T><<<grid, 256, 0, st>>>((const T*)dy, (const T*)ds, (const T*)x, w, w_dt, rstd,
                                                        (T*)dx, workspace, n_rows, n_cols);
   } else {
+    // ring of row slots in shared memory: as many as fit beside the other CTAs of the SM, at most NB_MAX_STAGES
+    const int per_sm = (grid + sm_count() - 1) / sm_count();
+    const int64_t stage_bytes = n_cols * (int64_t)sizeof(T) * (1 + (dy ? 1 : 0) + (ds ? 1 : 0));
+    int64_t stages = ((int64_t)220 * 1024 / per_sm - 1024) / stage_bytes;
+    if (stages > NB_MAX_STAGES) stages = NB_MAX_STAGES;
+    if (g_norm_ring && stages >= 2) {
+      const int smem = (int)(stages * stage_bytes);
+      cudaError_t e = cudaSuccess;
+      int occ = 0;
+#define RING_PREP(TT, TH, VP)                                                                                  \
+  do {                                                                                                         \
+    e = cudaFuncSetAttribute(norm_bwd_ring_kernel<TT, TH, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, norm_bwd_ring_kernel<TT, TH, VP>, TH, smem); \
+  } while (0)
+      NORM_DISPATCH_TV(T, RING_PREP)
+#undef RING_PREP
+      if (e != cudaSuccess) return HILDA_ERR_CUDA;
+      if (occ >= 1) {
+        if (occ < per_sm && (int64_t)occ * sm_count() < grid) grid = occ * sm_count();
+#define RING_CALL(TT, TH, VP)                                                                                  \
+  norm_bwd_ring_kernel<TT, TH, VP><<<grid, TH, smem, st>>>((const TT*)dy, (const TT*)ds, (const TT*)x, w, w_dt, rstd, \
+                                                           (TT*)dx, workspace, n_rows, (int)n_cols, (int)stages)
+        NORM_DISPATCH_TV(T, RING_CALL)
+#undef RING_CALL
+        HILDA_LAUNCH_CHECK();
+        dw_reduce_kernel<<<(unsigned)((n_cols + 31) / 32), 1024, 0, st>>>(workspace, grid, n_cols, dw, w_dt);
+        HILDA_LAUNCH_CHECK();
+        return HILDA_OK;
+      }
+    }
 #define BWD_CALL(TT, TH, VP)                                                                               \
   norm_bwd_kernel<TT, TH, VP><<<grid, TH, 0, st>>>((const TT*)dy, (const TT*)ds, (const TT*)x, w, w_dt, rstd, \
                                                     (TT*)dx, workspace, n_rows, (int)n_cols)
@@ -435,11 +633,9 @@ int64_t hilda_norm_bwd_workspace_bytes(int64_t n_rows, int64_t n_cols, int dtype
   return (int64_t)ctas * n_cols * 4;
 }
 
-// dy and ds may each be null (treated as zero); x is the saved input (RMSNorm) or saved sum S
-// (FusedAddRMSNorm).
-int hilda_norm_bwd(const void* dy, const void* ds, const void* x, const void* w, const float* rstd, void* dx,
-                   void* dw, float* workspace, int64_t n_rows, int64_t n_cols, int dtype, int w_dtype,
-                   void* stream) {
+static int norm_bwd_any(const void* dy, const void* ds, const void* x, const void* w, const float* rstd, void* dx,
+                        void* dw, float* workspace, int64_t n_rows, int64_t n_cols, int dtype, int w_dtype,
+                        void* stream, int64_t max_ctas) {
   if (!w || !dw) return HILDA_ERR_NULL;
   if (n_rows > 0 && (!x || !rstd || !dx || !workspace)) return HILDA_ERR_NULL;
   if (n_rows < 0 || n_cols <= 0 || n_cols > 0x7fffffff) return HILDA_ERR_SIZE;
@@ -450,24 +646,45 @@ int hilda_norm_bwd(const void* dy, const void* ds, const void* x, const void* w,
     return HILDA_OK;
   }
   switch (dtype) {
-    case HILDA_F32: return norm_bwd_t<float>(dy, ds, x, w, w_dtype, rstd, dx, dw, workspace, n_rows, n_cols, st);
-    case HILDA_BF16: return norm_bwd_t<__nv_bfloat16>(dy, ds, x, w, w_dtype, rstd, dx, dw, workspace, n_rows, n_cols, st);
-    case HILDA_F16: return norm_bwd_t<__half>(dy, ds, x, w, w_dtype, rstd, dx, dw, workspace, n_rows, n_cols, st);
+    case HILDA_F32: return norm_bwd_t<float>(dy, ds, x, w, w_dtype, rstd, dx, dw, workspace, n_rows, n_cols, st, max_ctas);
+    case HILDA_BF16: return norm_bwd_t<__nv_bfloat16>(dy, ds, x, w, w_dtype, rstd, dx, dw, workspace, n_rows, n_cols, st, max_ctas);
+    case HILDA_F16: return norm_bwd_t<__half>(dy, ds, x, w, w_dtype, rstd, dx, dw, workspace, n_rows, n_cols, st, max_ctas);
   }
   return HILDA_ERR_DTYPE;
+}
+
+// dy and ds may each be null (treated as zero); x is the saved input (RMSNorm) or saved sum S
+// (FusedAddRMSNorm).
+int hilda_norm_bwd(const void* dy, const void* ds, const void* x, const void* w, const float* rstd, void* dx,
+                   void* dw, float* workspace, int64_t n_rows, int64_t n_cols, int dtype, int w_dtype,
+                   void* stream) {
+  return norm_bwd_any(dy, ds, x, w, rstd, dx, dw, workspace, n_rows, n_cols, dtype, w_dtype, stream, 0);
+}
+
+// Kernel behind hilda_norm_bwd for vectorisable shapes: 1 (default) = rows staged through a
+// shared-memory ring by bulk asynchronous copies, 0 = register-only kernel; anything else only
+// queries. Returns the previous choice. Per host thread.
+int hilda_norm_bwd_set_path(int path) {
+  const int prev = g_norm_ring;
+  if (path == 0 || path == 1) g_norm_ring = path;
+  return prev;
 }
 
 int64_t hilda_norm_bwd_noalloc_max_bytes(void) { return NOALLOC_SCRATCH_FLOATS * 4; }
 
 // hilda_norm_bwd for hosts that cannot hand over a workspace: same arguments minus `workspace`, same
-// kernels, same results. The per-CTA dW partial sums go to a 16 MiB array that lives inside the
-// library (one copy on every GPU that loads it). Meant for callers that have no allocator to ask:
-// a C/FFI host without torch's caching allocator, or a server that gave all device memory to its
-// own pool at start-up and must not call cudaMalloc afterwards.
-//  * Sizes whose partial sums need more than hilda_norm_bwd_noalloc_max_bytes() are refused with
-//    HILDA_ERR_SIZE (use hilda_norm_bwd with your own workspace for those).
+// kernels. The per-CTA dW partial sums go to a 16 MiB array that lives inside the library (one copy
+// on every GPU that loads it). Meant for callers that have no allocator to ask: a C/FFI host
+// without torch's caching allocator, or a server that gave all device memory to its own pool at
+// start-up and must not call cudaMalloc afterwards.
+//  * The array holds hilda_norm_bwd_noalloc_max_bytes() / (4 * n_cols) partial rows. When the default
+//    launch would use more CTAs than that, fewer CTAs are launched (the kernel walks the rows with a
+//    grid stride, so any grid is correct): dX is then bit-identical to hilda_norm_bwd's and dW equal
+//    within the rounding of a different summation grouping. Only a row longer than the whole array
+//    (n_cols > 4 Mi) is refused with HILDA_ERR_SIZE.
 //  * The first call on each device looks up the array's device address (cudaGetSymbolAddress);
-//    make that first call during set-up, before any stream capture begins.
+//    make that first call during set-up, before any stream capture begins. (The look-up fills a
+//    per-device table without a lock; two threads racing on it store the same value.)
 //  * Nothing in the array has to start at zero (each CTA overwrites its whole partial row before
 //    the reduce pass reads it), so the contents left by an earlier call are harmless. But every
 //    call uses the SAME array: two calls that can overlap on the GPU (different streams, or the
@@ -475,13 +692,13 @@ int64_t hilda_norm_bwd_noalloc_max_bytes(void) { return NOALLOC_SCRATCH_FLOATS *
 //  * Calls no cudaMalloc / cudaFree and no allocating library routine.
 int hilda_norm_bwd_noalloc(const void* dy, const void* ds, const void* x, const void* w, const float* rstd, void* dx,
                            void* dw, int64_t n_rows, int64_t n_cols, int dtype, int w_dtype, void* stream) {
-  const int64_t need = hilda_norm_bwd_workspace_bytes(n_rows, n_cols, dtype);
-  if (need < 0) return (int)need;
-  if (need > NOALLOC_SCRATCH_FLOATS * 4) return HILDA_ERR_SIZE;
+  if (n_cols <= 0) return HILDA_ERR_SIZE;
+  const int64_t fit = NOALLOC_SCRATCH_FLOATS / n_cols;
+  if (fit < 1) return HILDA_ERR_SIZE;
   int rc = HILDA_OK;
   float* scratch = noalloc_scratch_ptr(&rc);
   if (rc != HILDA_OK) return rc;
-  return hilda_norm_bwd(dy, ds, x, w, rstd, dx, dw, scratch, n_rows, n_cols, dtype, w_dtype, stream);
+  return norm_bwd_any(dy, ds, x, w, rstd, dx, dw, scratch, n_rows, n_cols, dtype, w_dtype, stream, fit);
 }
 
 }  // extern "C"

@@ -12,6 +12,7 @@
 // first three dims and a contiguous last dim, so both (B,H,S,D) and transposed views of (B,S,H,D)
 // memory work without a copy. One thread handles one 16-byte vector of x1 and the matching vector
 // of x2; q and k items are folded into one flat index space so a single launch covers both.
+#include <cstdlib>
 #include "common.cuh"
 
 namespace hilda {
@@ -163,6 +164,70 @@ __global__ void __launch_bounds__(512) rope_kernel(const RopeArgs a, int inner_i
   }
 }
 
+// Fast path for the common training layout: 16-bit q/k whose tables share their dtype (packed
+// arithmetic), positions slower than heads in memory ((B,S,H,D) order), head_dim/2 a multiple of 8.
+// A CTA owns TOK consecutive tokens; thread i owns the same (head, vector) item of each of them, so
+// its index arithmetic is done once and all TOK tokens' loads (two 16-byte vectors of q or k and the
+// token's cos / sin vectors, which hit L1 after the first head) are in flight together before the
+// first result is stored. TOK x 2 x 16 bytes per thread in flight is what hides the DRAM latency that
+// the one-token-per-CTA form above exposes once per CTA.
+__device__ __forceinline__ uint4 ld16_once(const void* p) {  // read once, do not keep in L1; not .nc: may be in place
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+template <typename T, int TOK>
+__global__ void __launch_bounds__(512) rope_tokens_kernel(const RopeArgs a, int items, int64_t n_tokens) {
+  using P2 = typename Pk<T>::P2;
+  const int i = threadIdx.x;
+  if (i >= items) return;
+  const unsigned vph = a.half / 8;
+  const unsigned mid = (unsigned)i / vph;
+  const int v = (int)((unsigned)i - mid * vph);
+  const int ti = ((int)mid >= a.t[0].n_heads) ? 1 : 0;
+  const RopeTensor& t = a.t[ti];
+  const int hh = ti ? (int)mid - a.t[0].n_heads : (int)mid;
+  const T* in = reinterpret_cast<const T*>(t.in) + hh * t.stride_h + (int64_t)v * 8;
+  T* out = reinterpret_cast<T*>(t.out) + hh * t.ostride_h + (int64_t)v * 8;
+  const T* cosp = reinterpret_cast<const T*>(a.cos) + (int64_t)v * 8;
+  const T* sinp = reinterpret_cast<const T*>(a.sin) + (int64_t)v * 8;
+  const bool neg = a.sin_sign < 0.f;
+  const int64_t tok0 = (int64_t)blockIdx.x * TOK;
+  uint4 X1[TOK], X2[TOK], C[TOK], S[TOK];
+  int64_t oo[TOK];
+#pragma unroll
+  for (int k = 0; k < TOK; ++k) {
+    const int64_t tok = tok0 + k;
+    if (tok < n_tokens) {
+      const int64_t b = tok / a.seq, s_ = tok - b * a.seq;
+      const T* p = in + b * t.stride_b + s_ * t.stride_s;
+      oo[k] = b * t.ostride_b + s_ * t.ostride_s;
+      X1[k] = ld16_once(p);
+      X2[k] = ld16_once(p + a.half);
+      const int64_t coff = b * a.cos_stride_b + s_ * a.cos_stride_s;
+      C[k] = ld16(cosp + coff);
+      S[k] = ld16(sinp + coff);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < TOK; ++k) {
+    if (tok0 + k < n_tokens) {
+      uint4 Y1, Y2;
+      rope_packed<P2>(X1[k], X2[k], C[k], S[k], neg, Y1, Y2);
+      st16(out + oo[k], Y1);
+      st16(out + oo[k] + a.half, Y2);
+    }
+  }
+}
+
+// tokens per CTA of the fast path: 0 = the general kernel; HILDA_ROPE_TOK presets it
+static int rope_tok_default() {
+  static const int v = []() { const char* e = getenv("HILDA_ROPE_TOK"); return e ? atoi(e) : 4; }();
+  return v;
+}
+
 template <typename T>
 static int rope_launch(const RopeArgs& a, bool vec_ok, cudaStream_t st) {
   const int h_total = a.t[0].n_heads + a.t[1].n_heads;
@@ -172,6 +237,20 @@ static int rope_launch(const RopeArgs& a, bool vec_ok, cudaStream_t st) {
   const int64_t inner = (int64_t)(a.s_inner ? a.seq : h_total) * vph;
   if (outer == 0 || inner == 0) return HILDA_OK;
   if (outer > 0x7fffffffLL || inner > 0x7fffffffLL) return HILDA_ERR_SIZE;
+  if constexpr (sizeof(T) == 2) {
+    const int tok = rope_tok_default();
+    if (vec_ok && tok > 0 && !a.s_inner && a.cs_dtype == Pk<T>::DT && inner <= 512) {
+      const int threads = (int)((inner + 31) / 32 * 32);
+      const int64_t n_tokens = outer;
+      const int per = tok >= 4 ? 4 : (tok >= 2 ? 2 : 1);
+      const int64_t ctas = (n_tokens + per - 1) / per;
+      if (per == 4) rope_tokens_kernel<T, 4><<<(unsigned)ctas, threads, 0, st>>>(a, (int)inner, n_tokens);
+      else if (per == 2) rope_tokens_kernel<T, 2><<<(unsigned)ctas, threads, 0, st>>>(a, (int)inner, n_tokens);
+      else rope_tokens_kernel<T, 1><<<(unsigned)ctas, threads, 0, st>>>(a, (int)inner, n_tokens);
+      HILDA_LAUNCH_CHECK();
+      return HILDA_OK;
+    }
+  }
   int threads, chunk;
   if (inner <= 512) { threads = (int)((inner + 31) / 32 * 32); chunk = threads; }
   else { threads = 256; chunk = 1024; }

@@ -59,13 +59,22 @@ int hilda_norm_bwd(const void* dy, const void* ds, const void* x, const void* w,
                    void* dw, float* workspace, int64_t n_rows, int64_t n_cols, int dtype, int w_dtype,
                    void* stream);
 
+/* Kernel behind hilda_norm_bwd for vectorisable shapes (no counterpart in the reference): 1
+ * (default) = every CTA stages its rows through a ring of shared-memory slots filled by bulk
+ * asynchronous copies, so several rows per CTA are in flight while one is reduced; 0 = the
+ * register-only kernel (one row in flight per CTA). Same results. Other values only query.
+ * Returns the previous choice; per host thread. Environment: HILDA_NORM_RING. */
+int hilda_norm_bwd_set_path(int path);
+
 /* No counterpart in the reference. hilda_norm_bwd without the workspace argument, for hosts that
  * cannot supply one (a C/FFI caller with no allocator to borrow from, or a server whose memory was
  * all handed to its own pool at start-up and which must not call cudaMalloc afterwards). The dW
- * partial sums use a 16 MiB array inside the library, one copy per GPU that loads it. Sizes whose
- * partial sums exceed hilda_norm_bwd_noalloc_max_bytes() return HILDA_ERR_SIZE. The first call on
- * a device resolves the array's address: make it before any stream capture. All calls share the
- * array, so calls that may overlap on the GPU race; keep them ordered. Allocates nothing. */
+ * partial sums use a 16 MiB array inside the library, one copy per GPU that loads it; when the
+ * default launch would need more partial rows than fit, fewer CTAs run (dX unchanged bit for bit, dW
+ * equal within the rounding of another summation grouping); only n_cols * 4 bytes >
+ * hilda_norm_bwd_noalloc_max_bytes() returns HILDA_ERR_SIZE. The first call on a device resolves
+ * the array's address: make it before any stream capture. All calls share the array, so calls that
+ * may overlap on the GPU race; keep them ordered. Allocates nothing. */
 int64_t hilda_norm_bwd_noalloc_max_bytes(void);
 int hilda_norm_bwd_noalloc(const void* dy, const void* ds, const void* x, const void* w, const float* rstd,
                            void* dx, void* dw, int64_t n_rows, int64_t n_cols, int dtype, int w_dtype,

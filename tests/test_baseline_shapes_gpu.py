@@ -86,7 +86,13 @@ def test_rope_llama_block_shape(cs_dtype):
     assert qd.stride() == q.stride()
     qo, ko = hk.hilda_rope(qd, kd, cos.to(DEV), sin.to(DEV))
     torch.autograd.backward([qo, ko], [dq, dk])
-    qr, kr = q.cpu().requires_grad_(True), k.cpu().requires_grad_(True)
+    # With bf16 tables the oracle runs in bf16 and the kernel has the same rounding points (bit-exact
+    # forward). With fp32 tables the kernel computes in fp32 and rounds once, while autograd through the
+    # oracle on bf16 leaves would round each of the two gradient terms to bf16 before adding them (an
+    # error of an ulp of the TERMS on a sum that may cancel): there the oracle is evaluated on the
+    # same values held in fp32.
+    up = (lambda t: t.cpu()) if cs_dtype == torch.bfloat16 else (lambda t: t.cpu().float())
+    qr, kr = up(q).requires_grad_(True), up(k).requires_grad_(True)
     q_ref, k_ref = R.rope(qr, kr, cos, sin)
     torch.autograd.backward([q_ref, k_ref], [dq.cpu().to(q_ref.dtype), dk.cpu().to(k_ref.dtype)])
     if cs_dtype == torch.bfloat16:

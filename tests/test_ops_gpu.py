@@ -129,6 +129,41 @@ def test_rms_norm_dw_deterministic():
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
 
 
+def test_norm_backward_ring_and_register_kernels_agree():
+    """The backward that stages rows through a shared-memory ring (the default) and the register-only
+    kernel do the same arithmetic in the same order: bit-identical dX and dW, with and without dS and
+    dY, for row counts below, at and above the grid size."""
+    import hilda_kernel_b200._lib as L
+    lib = L.lib()
+    assert lib.hilda_norm_bwd_set_path(-1) == 1
+    g = gen(17)
+    for n_rows, n_cols, dtype in [(5, 4096, torch.float32), (4096, 4096, torch.float32), (1000, 4096, torch.bfloat16),
+                                  (9000, 2048, torch.bfloat16), (300, 8192, torch.float16), (777, 1024, torch.float32)]:
+        x = torch.randn(n_rows, n_cols, generator=g).to(dtype).to(DEV)
+        dy = torch.randn(n_rows, n_cols, generator=g).to(dtype).to(DEV)
+        ds = torch.randn(n_rows, n_cols, generator=g).to(dtype).to(DEV)
+        w = (1 + 0.1 * torch.randn(n_cols, generator=g)).to(dtype).to(DEV)
+        rstd = torch.rsqrt(x.float().pow(2).mean(-1) + 1e-6)
+        ws = torch.empty(lib.hilda_norm_bwd_workspace_bytes(n_rows, n_cols, L.dt(x)) // 4, dtype=torch.float32, device=DEV)
+        for use_dy, use_ds in ((True, False), (True, True), (False, True)):
+            res = []
+            for path in (1, 0):
+                lib.hilda_norm_bwd_set_path(path)
+                try:
+                    dx, dw = torch.empty_like(x), torch.empty_like(w)
+                    rc = lib.hilda_norm_bwd(dy.data_ptr() if use_dy else None, ds.data_ptr() if use_ds else None,
+                                            x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dw.data_ptr(),
+                                            ws.data_ptr(), n_rows, n_cols, L.dt(x), L.dt(w), L.stream(x.device))
+                    assert rc == 0
+                    torch.cuda.synchronize()
+                    res.append((dx, dw))
+                finally:
+                    lib.hilda_norm_bwd_set_path(1)
+            assert torch.equal(res[0][0], res[1][0]), (n_rows, n_cols, dtype, use_dy, use_ds)
+            assert torch.equal(res[0][1], res[1][1]), (n_rows, n_cols, dtype, use_dy, use_ds)
+            assert bool(torch.isfinite(res[0][1].float()).all())
+
+
 # ------------------------------------------------------------------ FusedAddRMSNorm
 @pytest.mark.parametrize("shape", [(2, 64, 4096), (3, 7, 5120), (1, 9, 8192), (5, 100), (300, 1024)])
 @pytest.mark.parametrize("dtype", DTYPES)

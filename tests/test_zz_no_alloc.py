@@ -4,8 +4,10 @@ It exists for hosts that have no workspace to pass: a plain C/FFI caller without
 a server that gave the whole device to its own memory pool and may not call cudaMalloc any more.
 The test calls it through the C ABI twice in a row (the second time on different data and a
 different shape, so anything left in the shared scratch array by the first call would show) and
-requires bit-identical results to hilda_norm_bwd with a caller-supplied workspace. This file is
-named so that pytest collects it last."""
+requires bit-identical results to hilda_norm_bwd with a caller-supplied workspace (dW within the
+tolerance of the other tests where the built-in array forces a smaller grid), and checks that a
+call changes neither the driver's free memory nor torch's allocation count. This file is named so
+that pytest collects it last."""
 import pytest
 import torch
 
@@ -13,7 +15,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def _run_pair(L, n_rows, n_cols, dtype, seed, with_ds):
+def _run_pair(L, n_rows, n_cols, dtype, seed, with_ds, same_grid=True):
     lib = L.lib()
     g = torch.Generator().manual_seed(seed)
     x = torch.randn(n_rows, n_cols, generator=g).to(dtype).to(DEV)
@@ -35,8 +37,19 @@ def _run_pair(L, n_rows, n_cols, dtype, seed, with_ds):
     assert lib.hilda_norm_bwd_noalloc(dy.data_ptr(), L.ptr(ds), x.data_ptr(), w.data_ptr(), rstd.data_ptr(),
                                       dx_b.data_ptr(), dw_b.data_ptr(), n_rows, n_cols, L.dt(x), L.dt(w), st) == 0
     torch.cuda.synchronize()
+    # the entry point's one promise: it takes no device memory, neither from the driver nor from torch
+    free0, alloc0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+    assert lib.hilda_norm_bwd_noalloc(dy.data_ptr(), L.ptr(ds), x.data_ptr(), w.data_ptr(), rstd.data_ptr(),
+                                      dx_b.data_ptr(), dw_b.data_ptr(), n_rows, n_cols, L.dt(x), L.dt(w), st) == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0 and torch.cuda.memory_allocated() == alloc0
     assert torch.equal(dx_a, dx_b), "dx differs"
-    assert torch.equal(dw_a, dw_b), "dw differs"
+    if same_grid:
+        assert torch.equal(dw_a, dw_b), "dw differs"
+    else:
+        # fewer CTAs than the workspace version: the partial sums are grouped differently
+        tol = dict(rtol=1e-5, atol=1e-4) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1e-2 * n_rows ** 0.5)
+        torch.testing.assert_close(dw_b.float(), dw_a.float(), **tol)
     assert bool(torch.isfinite(dw_b.float()).all())
 
 
@@ -47,13 +60,23 @@ def test_norm_bwd_noalloc_matches_workspace_version_twice():
     _run_pair(L, 3000, 4096, torch.bfloat16, seed=23, with_ds=True)
 
 
-def test_norm_bwd_noalloc_rejects_oversize():
+def test_norm_bwd_noalloc_uses_a_smaller_grid_when_the_default_one_does_not_fit():
+    """Hidden size 8192 in bf16: the default plan wants more partial rows than the 16 MiB array holds,
+    so fewer CTAs run. dX must not change at all, dW only by the summation grouping."""
+    import hilda_kernel_b200._lib as L
+    lib = L.lib()
+    n_rows, n_cols = 6000, 8192
+    grouped = lib.hilda_norm_bwd_workspace_bytes(n_rows, n_cols, 1) > lib.hilda_norm_bwd_noalloc_max_bytes()
+    _run_pair(L, n_rows, n_cols, torch.bfloat16, seed=31, with_ds=True, same_grid=not grouped)
+    _run_pair(L, 5000, 16384, torch.float32, seed=32, with_ds=False, same_grid=False)
+
+
+def test_norm_bwd_noalloc_rejects_only_a_row_longer_than_the_array():
     import hilda_kernel_b200._lib as L
     lib = L.lib()
     cap = lib.hilda_norm_bwd_noalloc_max_bytes()
     assert cap == 16 * 1024 * 1024
-    n_rows, n_cols = 100000, 32768   # partial sums need far more than the built-in array holds
-    assert lib.hilda_norm_bwd_workspace_bytes(n_rows, n_cols, 0) > cap
+    n_rows, n_cols = 4, cap // 4 + 8   # one partial row alone exceeds the built-in array
     one = torch.zeros(8, device=DEV)
     rc = lib.hilda_norm_bwd_noalloc(one.data_ptr(), None, one.data_ptr(), one.data_ptr(), one.data_ptr(), one.data_ptr(),
                                     one.data_ptr(), n_rows, n_cols, 0, 0, L.stream(one.device))

@@ -86,6 +86,7 @@ SIGNATURES = {
     "hilda_fused_linear_cross_entropy_fwd": (_i32, [_p] * 8 + [_i64, _i64, _i64, _i64, _i32, _i64, _i32, _i32, _p]),
     "hilda_flce_profile": (None, [_i32]),
     "hilda_flce_profile_collect": (_i32, [_p, _p]),
+    "hilda_flce_profile_entry": (_i32, [_i32, _p, _p]),
     "hilda_gather_rows": (_i32, [_p, _p, _p, _i64, _i64, _p]),
     "hilda_scatter_rows": (_i32, [_p, _p, _p, _i64, _i64, _i64, _p]),
     "hilda_gemm_set_pair": (None, [_i32]),

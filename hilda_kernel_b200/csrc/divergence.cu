@@ -38,10 +38,10 @@ template <typename T> __device__ __forceinline__ float kl_log(float x) { return 
 template <typename T>
 __global__ void __launch_bounds__(DV_THREADS)
 kl_div_fwd_kernel(const T* __restrict__ y_pred, const T* __restrict__ y_true, float* __restrict__ loss_rows,
-                  int64_t n_rows, int64_t n_cols, float eps, int log_target) {
+                  int64_t n_rows, int64_t n_cols, float eps, int log_target, int aligned) {
   constexpr int VEC = VT<T>::N;
   __shared__ float red[33];
-  const bool vec_ok = (n_cols % VEC) == 0;
+  const bool vec_ok = aligned && (n_cols % VEC) == 0;  // misaligned views take the element-wise path
   for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
     const T* yp = y_pred + row * n_cols;
     const T* yt = y_true + row * n_cols;
@@ -72,10 +72,10 @@ kl_div_fwd_kernel(const T* __restrict__ y_pred, const T* __restrict__ y_true, fl
 template <typename T>
 __global__ void __launch_bounds__(256)
 kl_div_bwd_kernel(const T* __restrict__ y_true, T* __restrict__ dy, const float* __restrict__ grad_out, float factor,
-                  int64_t n, int log_target) {
+                  int64_t n, int log_target, int aligned) {
   constexpr int VEC = VT<T>::N;
   const float scale = grad_out ? factor * grad_out[0] : factor;
-  const int64_t n_vec = n / VEC;
+  const int64_t n_vec = aligned ? n / VEC : 0;  // misaligned views: everything goes through the element-wise tail
   const int64_t stride = (int64_t)gridDim.x * 256;
   for (int64_t v = (int64_t)blockIdx.x * 256 + threadIdx.x; v < n_vec; v += stride) {
     float t[VEC];
@@ -143,12 +143,12 @@ template <typename T>
 __global__ void __launch_bounds__(DV_THREADS)
 jsd_rows_kernel(const T* __restrict__ X, const T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ loss_rows,
                 const int64_t* __restrict__ labels, int64_t ignore_index, const int* __restrict__ n_valid,
-                int64_t n_rows, int64_t V, float beta) {
+                int64_t n_rows, int64_t V, float beta, int aligned) {
   constexpr int VEC = VT<T>::N;
   __shared__ float red[33];
   const int mode = jsd_mode(beta);
   const float inv_n = 1.0f / (n_valid ? fmaxf((float)(*n_valid), 1.0f) : (float)n_rows);
-  const bool vec_ok = (V % VEC) == 0;
+  const bool vec_ok = aligned && (V % VEC) == 0;
   for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
     const T* x = X + row * V;
     const T* y = Y + row * V;
@@ -288,20 +288,20 @@ int hilda_kl_div_fwd(const void* y_pred, const void* y_true, float* loss_rows, f
     return HILDA_OK;
   }
   if (!y_pred || !y_true || !loss_rows || (reduction != 0 && !loss_out)) return HILDA_ERR_NULL;
-  if (!aligned16(y_pred) || !aligned16(y_true)) return HILDA_ERR_ALIGN;
+  const int al = aligned16(y_pred) && aligned16(y_true);
   const int grid = dv_grid(n_rows);
   switch (dtype) {
     case HILDA_F32:
       kl_div_fwd_kernel<float><<<grid, DV_THREADS, 0, st>>>((const float*)y_pred, (const float*)y_true, loss_rows, n_rows,
-                                                           n_cols, eps, log_target);
+                                                           n_cols, eps, log_target, al);
       break;
     case HILDA_BF16:
       kl_div_fwd_kernel<__nv_bfloat16><<<grid, DV_THREADS, 0, st>>>((const __nv_bfloat16*)y_pred, (const __nv_bfloat16*)y_true,
-                                                                   loss_rows, n_rows, n_cols, eps, log_target);
+                                                                   loss_rows, n_rows, n_cols, eps, log_target, al);
       break;
     case HILDA_F16:
       kl_div_fwd_kernel<__half><<<grid, DV_THREADS, 0, st>>>((const __half*)y_pred, (const __half*)y_true, loss_rows, n_rows,
-                                                            n_cols, eps, log_target);
+                                                            n_cols, eps, log_target, al);
       break;
     default: return HILDA_ERR_DTYPE;
   }
@@ -322,7 +322,7 @@ int hilda_kl_div_bwd(const void* y_true, void* dy_pred, const float* grad_out, i
   if (n_rows < 0 || n_cols <= 0) return HILDA_ERR_SIZE;
   if (n_rows == 0) return HILDA_OK;
   if (!y_true || !dy_pred || (reduction != 0 && !grad_out)) return HILDA_ERR_NULL;
-  if (!aligned16(y_true) || !aligned16(dy_pred)) return HILDA_ERR_ALIGN;
+  const int al = aligned16(y_true) && aligned16(dy_pred);
   cudaStream_t st = (cudaStream_t)stream;
   const float factor = reduction == 2 ? 1.0f / ((float)n_rows * (float)n_cols) : (reduction == 3 ? 1.0f / (float)n_rows : 1.0f);
   const float* g = reduction == 0 ? nullptr : grad_out;
@@ -335,14 +335,14 @@ int hilda_kl_div_bwd(const void* y_true, void* dy_pred, const float* grad_out, i
   if (blocks < 1) blocks = 1;
   switch (dtype) {
     case HILDA_F32:
-      kl_div_bwd_kernel<float><<<(unsigned)blocks, 256, 0, st>>>((const float*)y_true, (float*)dy_pred, g, factor, n, log_target);
+      kl_div_bwd_kernel<float><<<(unsigned)blocks, 256, 0, st>>>((const float*)y_true, (float*)dy_pred, g, factor, n, log_target, al);
       break;
     case HILDA_BF16:
       kl_div_bwd_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>((const __nv_bfloat16*)y_true, (__nv_bfloat16*)dy_pred, g,
-                                                                       factor, n, log_target);
+                                                                       factor, n, log_target, al);
       break;
     default:
-      kl_div_bwd_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>((const __half*)y_true, (__half*)dy_pred, g, factor, n, log_target);
+      kl_div_bwd_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>((const __half*)y_true, (__half*)dy_pred, g, factor, n, log_target, al);
       break;
   }
   HILDA_LAUNCH_CHECK();
@@ -360,7 +360,7 @@ int hilda_jsd_fwd(const void* X, const void* Y, void* dX, float* loss_rows, floa
     return HILDA_OK;
   }
   if (!X || !Y || !dX || !loss_rows || !loss_out || (labels && !workspace)) return HILDA_ERR_NULL;
-  if (!aligned16(X) || !aligned16(Y) || !aligned16(dX)) return HILDA_ERR_ALIGN;
+  const int al = aligned16(X) && aligned16(Y) && aligned16(dX);
   int* n_valid = nullptr;
   if (labels) {
     n_valid = reinterpret_cast<int*>(workspace);
@@ -371,16 +371,16 @@ int hilda_jsd_fwd(const void* X, const void* Y, void* dX, float* loss_rows, floa
   switch (dtype) {
     case HILDA_F32:
       jsd_rows_kernel<float><<<grid, DV_THREADS, 0, st>>>((const float*)X, (const float*)Y, (float*)dX, loss_rows, labels,
-                                                         ignore_index, n_valid, n_rows, V, beta);
+                                                         ignore_index, n_valid, n_rows, V, beta, al);
       break;
     case HILDA_BF16:
       jsd_rows_kernel<__nv_bfloat16><<<grid, DV_THREADS, 0, st>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)Y,
                                                                  (__nv_bfloat16*)dX, loss_rows, labels, ignore_index, n_valid,
-                                                                 n_rows, V, beta);
+                                                                 n_rows, V, beta, al);
       break;
     case HILDA_F16:
       jsd_rows_kernel<__half><<<grid, DV_THREADS, 0, st>>>((const __half*)X, (const __half*)Y, (__half*)dX, loss_rows, labels,
-                                                          ignore_index, n_valid, n_rows, V, beta);
+                                                          ignore_index, n_valid, n_rows, V, beta, al);
       break;
     default: return HILDA_ERR_DTYPE;
   }

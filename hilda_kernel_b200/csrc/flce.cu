@@ -728,6 +728,17 @@ int hilda_flce_profile_collect(float* ms_per_kind, int* launches_per_kind) {
   return HILDA_OK;
 }
 
+// The i-th recorded launch since profiling was switched on: its kind and device time in ms
+// (HILDA_ERR_ARG once i is past the last one). Call after hilda_flce_profile_collect.
+int hilda_flce_profile_entry(int i, int* kind, float* ms) {
+  if (!kind || !ms) return HILDA_ERR_NULL;
+  if (i < 0 || i >= g_prof_n) return HILDA_ERR_ARG;
+  if (cudaEventSynchronize(g_prof_ev[i][1]) != cudaSuccess) return HILDA_ERR_CUDA;
+  if (cudaEventElapsedTime(ms, g_prof_ev[i][0], g_prof_ev[i][1]) != cudaSuccess) return HILDA_ERR_CUDA;
+  *kind = g_prof_kind[i];
+  return HILDA_OK;
+}
+
 // Row moves with a host-known index list: gather dst[i] = src[idx[i]] and scatter dst[idx[i]] = src[i]
 // over rows of row_bytes (a multiple of 16) bytes; idx is int64 on the device. The scatter first
 // clears dst (n_dst_rows rows), so rows not named by idx come out as zeros.

@@ -142,7 +142,7 @@ template <typename T, int THREADS, int VPT>
 __global__ void __launch_bounds__(THREADS, (sizeof(T) == 2 && VPT <= 2) ? (1024 / THREADS) : 1)
 norm_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __restrict__ X,
                 const void* __restrict__ W, int w_dt, const float* __restrict__ RSTD,
-                T* __restrict__ dX, float* __restrict__ partial, int64_t n_rows, int n_cols) {
+                T* __restrict__ dX, float* __restrict__ partial, int64_t n_rows, int n_cols, int prefetch_rows) {
   constexpr int VEC = VT<T>::N;
   const int n_vec = n_cols / VEC;
   __shared__ float red[33];
@@ -156,7 +156,18 @@ norm_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __r
 #pragma unroll
     for (int j = 0; j < VEC; ++j) dw[i][j] = 0.f;
 
+  const uint32_t row_bytes = (uint32_t)n_cols * (uint32_t)sizeof(T);
   for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
+    // Optional: one thread asks the L2 for the rows this CTA reaches `prefetch_rows` iterations from now
+    // (bulk prefetch, one instruction per tensor row), so that their loads find them on chip.
+    if (prefetch_rows > 0 && threadIdx.x == 0) {
+      const int64_t ahead = row + (int64_t)prefetch_rows * gridDim.x;
+      if (ahead < n_rows) {
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(X + ahead * n_cols), "r"(row_bytes) : "memory");
+        if (dY) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(dY + ahead * n_cols), "r"(row_bytes) : "memory");
+        if (dS) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(dS + ahead * n_cols), "r"(row_bytes) : "memory");
+      }
+    }
     // all of the row's loads (dS too) are issued before the reduction: one DRAM round trip per row
     uint4 dyv[VPT], xv[VPT], dsv[VPT];
 #pragma unroll
@@ -246,7 +257,11 @@ norm_bwd_ring_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T
                      const void* __restrict__ W, int w_dt, const float* __restrict__ RSTD,
                      T* __restrict__ dX, float* __restrict__ partial, int64_t n_rows, int n_cols, int stages) {
   constexpr int VEC = VT<T>::N;
-  extern __shared__ __align__(128) uint8_t ring[];
+  // dynamic shared memory: W as fp32 [n_cols] (the ring takes most of the SM's L1 away, so W would
+  // otherwise come from L2 twice per row), then the ring slots
+  extern __shared__ __align__(128) uint8_t ring_raw[];
+  float* w_s = reinterpret_cast<float*>(ring_raw);
+  uint8_t* ring = ring_raw + (size_t)n_cols * 4;
   __shared__ __align__(8) uint64_t full_bar[NB_MAX_STAGES];
   __shared__ float red[33];
   __shared__ int gave_up;
@@ -278,6 +293,16 @@ norm_bwd_ring_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     for (int64_t it = 0; it < n_mine && it < stages; ++it) issue(it);
+  }
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * THREADS;
+    if (v < n_vec) {
+      float w[VEC];
+      load_w_vec<VEC>(W, w_dt, v * VEC, w);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) w_s[v * VEC + j] = w[j];
+    }
   }
   __syncthreads();
 
@@ -315,7 +340,11 @@ norm_bwd_ring_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T
       VT<T>::unpack(dyv[i], dy);
       VT<T>::unpack(xv[i], x);
       if (v < n_vec) {
-        load_w_vec<VEC>(W, w_dt, v * VEC, w);
+#pragma unroll
+        for (int j = 0; j < VEC; j += 4) {
+          const float4 t4 = *reinterpret_cast<const float4*>(w_s + v * VEC + j);
+          w[j] = t4.x; w[j + 1] = t4.y; w[j + 2] = t4.z; w[j + 3] = t4.w;
+        }
 #pragma unroll
         for (int j = 0; j < VEC; ++j) acc = fmaf(dy[j] * w[j], x[j], acc);
       }
@@ -335,7 +364,11 @@ norm_bwd_ring_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T
       VT<T>::unpack(dyv[i], dy);
       VT<T>::unpack(xv[i], x);
       if (v < n_vec) {
-        load_w_vec<VEC>(W, w_dt, v * VEC, w);
+#pragma unroll
+        for (int j = 0; j < VEC; j += 4) {
+          const float4 t4 = *reinterpret_cast<const float4*>(w_s + v * VEC + j);
+          w[j] = t4.x; w[j + 1] = t4.y; w[j + 2] = t4.z; w[j + 3] = t4.w;
+        }
 #pragma unroll
         for (int j = 0; j < VEC; ++j) {
           dx[j] = rstd * (dy[j] * w[j]) - coef * x[j];
@@ -497,10 +530,16 @@ static int norm_bwd_ctas(int64_t n_rows, int64_t n_cols, bool al) {
   return (int)ctas;
 }
 
-// 1 (default): the backward stages its rows through a shared-memory ring (norm_bwd_ring_kernel) when
-// at least two slots fit; 0: always the register-only kernel. Per host thread. HILDA_NORM_RING presets it.
+// Kernel choice of the backward for vectorisable shapes (per host thread; HILDA_NORM_RING presets it):
+//   1 (default) automatic: the shared-memory ring (norm_bwd_ring_kernel) when three or more row slots
+//     fit beside the SM's other CTAs, else the register kernel with an L2 bulk prefetch one row ahead.
+//     Measured on B200: fp32 [4096,4096] (3 slots, 2 CTAs per SM) ring 37.6 us, register kernel 42.0,
+//     with prefetch 38.8; bf16 [16384,4096] with dS (2 slots, 4 CTAs per SM) ring 101.7 us, register
+//     kernel 100.5, with prefetch one row ahead 93.5, two rows ahead 96.7.
+//   0 register kernel, no prefetch; 2 / 3 register kernel with prefetch 1 / 2 rows ahead; 4 ring whenever
+//     two slots fit.
 static int norm_ring_default() {
-  static const int v = []() { const char* e = getenv("HILDA_NORM_RING"); return e ? (atoi(e) != 0) : 1; }();
+  static const int v = []() { const char* e = getenv("HILDA_NORM_RING"); return e ? atoi(e) : 1; }();
   return v;
 }
 static thread_local int g_norm_ring = norm_ring_default();
@@ -525,10 +564,10 @@ static int norm_bwd_t(const void* dy, const void* ds, const void* x, const void*
     // ring of row slots in shared memory: as many as fit beside the other CTAs of the SM, at most NB_MAX_STAGES
     const int per_sm = (grid + sm_count() - 1) / sm_count();
     const int64_t stage_bytes = n_cols * (int64_t)sizeof(T) * (1 + (dy ? 1 : 0) + (ds ? 1 : 0));
-    int64_t stages = ((int64_t)220 * 1024 / per_sm - 1024) / stage_bytes;
+    int64_t stages = ((int64_t)220 * 1024 / per_sm - 1024 - n_cols * 4) / stage_bytes;
     if (stages > NB_MAX_STAGES) stages = NB_MAX_STAGES;
-    if (g_norm_ring && stages >= 2) {
-      const int smem = (int)(stages * stage_bytes);
+    if ((g_norm_ring == 1 && stages >= 3) || (g_norm_ring == 4 && stages >= 2)) {
+      const int smem = (int)(stages * stage_bytes + n_cols * 4);
       cudaError_t e = cudaSuccess;
       int occ = 0;
 #define RING_PREP(TT, TH, VP)                                                                                  \
@@ -554,7 +593,8 @@ static int norm_bwd_t(const void* dy, const void* ds, const void* x, const void*
     }
 #define BWD_CALL(TT, TH, VP)                                                                               \
   norm_bwd_kernel<TT, TH, VP><<<grid, TH, 0, st>>>((const TT*)dy, (const TT*)ds, (const TT*)x, w, w_dt, rstd, \
-                                                    (TT*)dx, workspace, n_rows, (int)n_cols)
+                                                    (TT*)dx, workspace, n_rows, (int)n_cols, \
+                                                    (g_norm_ring == 1 || g_norm_ring == 4) ? 1 : (g_norm_ring >= 2 ? g_norm_ring - 1 : 0))
     NORM_DISPATCH_TV(T, BWD_CALL)
 #undef BWD_CALL
   }
@@ -666,7 +706,7 @@ int hilda_norm_bwd(const void* dy, const void* ds, const void* x, const void* w,
 // queries. Returns the previous choice. Per host thread.
 int hilda_norm_bwd_set_path(int path) {
   const int prev = g_norm_ring;
-  if (path == 0 || path == 1) g_norm_ring = path;
+  if (path >= 0 && path <= 4) g_norm_ring = path;
   return prev;
 }
 

@@ -12,6 +12,7 @@
 // the per-row scalars (loss, kl, ...) and the gradient coefficients follow from (lse, x_target):
 //     grad[j] = alpha * softmax(x/T)[j] + (j == target ? beta : 0).
 #pragma once
+#include <cstdlib>
 #include "common.cuh"
 
 namespace hilda {
@@ -152,7 +153,8 @@ constexpr int row_min_blocks(int threads, int nv) {
 
 template <typename T, int ROW_THREADS, int NV, int CLUSTER, class Op>
 __global__ void __launch_bounds__(ROW_THREADS, row_min_blocks(ROW_THREADS, NV))
-row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V, Op op, int* __restrict__ status) {
+row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V, Op op, int* __restrict__ status,
+                   int prefetch_rows) {
   constexpr int VEC = VT<T>::N;
   __shared__ float red[33];
   __shared__ float xchg[2 * CLUSTER];
@@ -163,6 +165,19 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
   const int slice = (n_vec + CLUSTER - 1) / CLUSTER;
   const int v0 = (int)rank * slice;
   const int v1 = min(n_vec, v0 + slice);
+  // CTAs start in row order, so the row `prefetch_rows` further on is one a CTA will begin shortly:
+  // ask the L2 for this CTA's slice of it now (one bulk prefetch instruction). DRAM then streams
+  // the upcoming rows while the resident CTAs are in their reduce / exchange / store phases, and
+  // the loads of a starting CTA find their row on chip.
+  if (prefetch_rows > 0 && tid == 0 && v1 > v0) {
+    const int64_t ahead = row + prefetch_rows;
+    int64_t tgt_ahead;
+    if (ahead < (int64_t)(gridDim.x / CLUSTER) && op.begin(ahead, tgt_ahead)) {
+      const T* p = logits + op.row_offset(ahead, V) + (int64_t)v0 * VEC;
+      const uint32_t bytes = (uint32_t)(v1 - v0) * 16u;
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+    }
+  }
   const int64_t roff = op.row_offset(row, V);
   const T* xr = logits + roff;
   T* gr = grad ? grad + roff : nullptr;
@@ -335,6 +350,11 @@ static inline RowPlan plan_row(int64_t V, int vec, bool aligned, int force_nv, i
 
 template <typename T, int THREADS, int NV, int CLUSTER, class Op>
 static int launch_row_cfg(const T* logits, T* grad, int64_t n_rows, int64_t V, const Op& op, int* status, cudaStream_t st) {
+  // rows ahead of a starting CTA whose slice it asks the L2 for: a little more than the rows resident
+  // at once (SMs x CTAs per SM / CTAs per row); HILDA_ROW_PREFETCH overrides (0 = off)
+  static const int env_pf = []() { const char* e = getenv("HILDA_ROW_PREFETCH"); return e ? atoi(e) : -1; }();
+  int prefetch_rows = env_pf >= 0 ? env_pf : (sm_count() * row_min_blocks(THREADS, NV) / CLUSTER) * 5 / 4 + 4;
+  if (!grad) prefetch_rows = env_pf >= 0 ? env_pf : prefetch_rows;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(n_rows * CLUSTER), 1, 1);
   cfg.blockDim = dim3(THREADS, 1, 1);
@@ -347,7 +367,7 @@ static int launch_row_cfg(const T* logits, T* grad, int64_t n_rows, int64_t V, c
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, row_softmax_kernel<T, THREADS, NV, CLUSTER, Op>, logits, grad, V, op, status);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, row_softmax_kernel<T, THREADS, NV, CLUSTER, Op>, logits, grad, V, op, status, prefetch_rows);
   return e == cudaSuccess ? HILDA_OK : HILDA_ERR_CUDA;
 }
 

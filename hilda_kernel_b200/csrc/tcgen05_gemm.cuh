@@ -219,6 +219,63 @@ __device__ __forceinline__ float ex2_fast(float x) {
 template <int EPI>
 __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t taddr0, int64_t row, int col0, int nt,
                                                    bool zero_acc = false) {
+  if constexpr (EPI == EPI_ACCUM32 || EPI == EPI_ACCUM_FINAL16) {
+    // C (+)= acc: the fp32 values of column chunk c + 1 are requested before chunk c is added and
+    // stored, so that a tile's 8 round trips to memory overlap instead of following one another (the
+    // tile has to be through here before the next one's main loop ends).
+    const bool in_m = row < p.M;
+    float* crow = p.C32 + row * p.ldc32 + col0;
+    float4 nxt[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      nxt[j] = (in_m && col0 + 4 * j + 4 <= p.N) ? *reinterpret_cast<const float4*>(crow + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t r[32];
+      float4 cur[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
+      tmem_ld32(taddr0 + c * 32, r);
+      const int cbase = col0 + c * 32;
+      if (c + 1 < BN / 32) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          nxt[j] = (in_m && cbase + 32 + 4 * j + 4 <= p.N) ? *reinterpret_cast<const float4*>(crow + (c + 1) * 32 + 4 * j)
+                                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      tmem_ld_wait();
+      if (zero_acc) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = 0u;
+      }
+      if (in_m) {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          v[4 * j] = cur[j].x + __uint_as_float(r[4 * j]);
+          v[4 * j + 1] = cur[j].y + __uint_as_float(r[4 * j + 1]);
+          v[4 * j + 2] = cur[j].z + __uint_as_float(r[4 * j + 2]);
+          v[4 * j + 3] = cur[j].w + __uint_as_float(r[4 * j + 3]);
+        }
+        if constexpr (EPI == EPI_ACCUM32) {
+          float* c32 = crow + c * 32;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (cbase + 4 * j + 4 <= p.N)
+              *reinterpret_cast<float4*>(c32 + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        } else {
+          uint16_t* dst = reinterpret_cast<uint16_t*>(p.C16) + row * p.ldc16 + cbase;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (cbase + 8 * j + 8 <= p.N)
+              *reinterpret_cast<uint4*>(dst + 8 * j) =
+                  make_uint4(pack16(v[8 * j], v[8 * j + 1], p.is_bf16), pack16(v[8 * j + 2], v[8 * j + 3], p.is_bf16),
+                             pack16(v[8 * j + 4], v[8 * j + 5], p.is_bf16), pack16(v[8 * j + 6], v[8 * j + 7], p.is_bf16));
+        }
+      }
+    }
+    return;
+  }
   float run_m = -INFINITY, run_s = 0.f;
   const float stat_scale = p.stat_scale;  // log2(e) / temperature: the statistics are of logits / temperature
 #pragma unroll 1

@@ -59,11 +59,13 @@ int hilda_norm_bwd(const void* dy, const void* ds, const void* x, const void* w,
                    void* dw, float* workspace, int64_t n_rows, int64_t n_cols, int dtype, int w_dtype,
                    void* stream);
 
-/* Kernel behind hilda_norm_bwd for vectorisable shapes (no counterpart in the reference): 1
- * (default) = every CTA stages its rows through a ring of shared-memory slots filled by bulk
- * asynchronous copies, so several rows per CTA are in flight while one is reduced; 0 = the
- * register-only kernel (one row in flight per CTA). Same results. Other values only query.
- * Returns the previous choice; per host thread. Environment: HILDA_NORM_RING. */
+/* Kernel behind hilda_norm_bwd for vectorisable shapes (no counterpart in the reference). 1
+ * (default) = automatic: every CTA stages its rows through a ring of shared-memory slots filled by
+ * bulk asynchronous copies when three or more slots fit, else the register kernel (one row in
+ * flight per CTA) with a bulk L2 prefetch of the CTA's next row; 0 = register kernel, no prefetch;
+ * 2 / 3 = register kernel with the prefetch 1 / 2 rows ahead; 4 = ring whenever two slots fit. Same
+ * results bit for bit. Other values only query. Returns the previous choice; per host thread.
+ * Environment: HILDA_NORM_RING. */
 int hilda_norm_bwd_set_path(int path);
 
 /* No counterpart in the reference. hilda_norm_bwd without the workspace argument, for hosts that
@@ -218,6 +220,9 @@ int hilda_scatter_valid_f32(const float* in, const int* inv, float* out, int64_t
  * (HOST pointers, 3 entries each). enable != 0 also clears the record. */
 void hilda_flce_profile(int enable);
 int hilda_flce_profile_collect(float* ms_per_kind, int* launches_per_kind);
+/* The i-th bracketed launch since the hook was enabled: kind and device milliseconds (HOST
+ * pointers); HILDA_ERR_ARG once i is past the last recorded launch. */
+int hilda_flce_profile_entry(int i, int* kind, float* ms);
 
 /* Row moves with an index list whose length the host knows (no counterpart in the reference):
  * dst[i,:] = src[idx[i],:] and dst[idx[i],:] = src[i,:] over rows of row_bytes (multiple of 16)

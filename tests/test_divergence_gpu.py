@@ -202,3 +202,39 @@ def test_fused_linear_jsd_golden(golden):
     assert abs(float(loss) - float(c["loss"])) < 0.05 * abs(float(c["loss"])) + 1e-4
     assert float((hd.grad.float().cpu() - c["dh"]).abs().max()) < 5e-2   # :95 thresholds
     assert float((wd.grad.float().cpu() - c["dw"]).abs().max()) < 5e-1
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_kl_div_and_jsd_accept_contiguous_views_that_are_not_16_byte_aligned(dtype):
+    """A contiguous view whose storage offset is odd (the reference accepts any such tensor) takes the
+    element-wise path instead of being refused; same values as the aligned call."""
+    import hilda_kernel_b200 as hk
+    g = gen(47)
+    n, v = 6, 1000
+    yp = torch.randn(n, v, generator=g).log_softmax(-1).to(dtype)
+    yt = torch.randn(n, v, generator=g).softmax(-1).to(dtype)
+
+    def offset_view(t):
+        buf = torch.empty(t.numel() + 1, dtype=t.dtype, device=DEV)
+        view = buf[1:].view(t.shape)
+        view.copy_(t)
+        assert view.is_contiguous() and view.data_ptr() % 16 != 0
+        return view
+    a = yp.to(DEV).requires_grad_(True)
+    la = hk.hilda_kl_div(a, yt.to(DEV), "batchmean", False)
+    la.backward()
+    b = offset_view(yp).requires_grad_(True)
+    lb = hk.hilda_kl_div(b, offset_view(yt), "batchmean", False)
+    lb.backward()
+    assert_loss_close(lb.detach(), la.detach())
+    assert torch.equal(a.grad, b.grad)
+    xs = torch.randn(n, v, generator=g).log_softmax(-1).to(dtype)
+    ys = torch.randn(n, v, generator=g).log_softmax(-1).to(dtype)
+    c = xs.to(DEV).requires_grad_(True)
+    lc = hk.hilda_jsd(c, ys.to(DEV), 0.5)
+    lc.backward()
+    d = offset_view(xs).requires_grad_(True)
+    ld = hk.hilda_jsd(d, offset_view(ys), 0.5)
+    ld.backward()
+    assert_loss_close(ld.detach(), lc.detach())
+    assert_close(d.grad, c.grad.float(), dtype, what="dX", normalize=True)

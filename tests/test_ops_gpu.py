@@ -130,9 +130,9 @@ def test_rms_norm_dw_deterministic():
 
 
 def test_norm_backward_ring_and_register_kernels_agree():
-    """The backward that stages rows through a shared-memory ring (the default) and the register-only
-    kernel do the same arithmetic in the same order: bit-identical dX and dW, with and without dS and
-    dY, for row counts below, at and above the grid size."""
+    """The backward's kernels (rows staged through a shared-memory ring; register-only, with or without
+    the L2 prefetch of upcoming rows) do the same arithmetic in the same order: bit-identical dX and
+    dW, with and without dS and dY, for row counts below, at and above the grid size."""
     import hilda_kernel_b200._lib as L
     lib = L.lib()
     assert lib.hilda_norm_bwd_set_path(-1) == 1
@@ -147,7 +147,7 @@ def test_norm_backward_ring_and_register_kernels_agree():
         ws = torch.empty(lib.hilda_norm_bwd_workspace_bytes(n_rows, n_cols, L.dt(x)) // 4, dtype=torch.float32, device=DEV)
         for use_dy, use_ds in ((True, False), (True, True), (False, True)):
             res = []
-            for path in (1, 0):
+            for path in (1, 0, 4, 3):
                 lib.hilda_norm_bwd_set_path(path)
                 try:
                     dx, dw = torch.empty_like(x), torch.empty_like(w)
@@ -159,8 +159,9 @@ def test_norm_backward_ring_and_register_kernels_agree():
                     res.append((dx, dw))
                 finally:
                     lib.hilda_norm_bwd_set_path(1)
-            assert torch.equal(res[0][0], res[1][0]), (n_rows, n_cols, dtype, use_dy, use_ds)
-            assert torch.equal(res[0][1], res[1][1]), (n_rows, n_cols, dtype, use_dy, use_ds)
+            for other in res[1:]:
+                assert torch.equal(res[0][0], other[0]), (n_rows, n_cols, dtype, use_dy, use_ds)
+                assert torch.equal(res[0][1], other[1]), (n_rows, n_cols, dtype, use_dy, use_ds)
             assert bool(torch.isfinite(res[0][1].float()).all())
 
 

@@ -328,36 +328,11 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t
     } else {
       if (row < p.M) {
         float* c32 = p.C32 + row * p.ldc32 + cbase;
-        if constexpr (EPI == EPI_STORE32) {
+        if constexpr (EPI == EPI_STORE32) {  // (the accumulate epilogues returned above)
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             if (cbase + 4 * j + 4 <= p.N)
               *reinterpret_cast<uint4*>(c32 + 4 * j) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-        } else {
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (cbase + 4 * j + 4 <= p.N) o = *reinterpret_cast<const float4*>(c32 + 4 * j);
-            v[4 * j] = o.x + __uint_as_float(r[4 * j]);
-            v[4 * j + 1] = o.y + __uint_as_float(r[4 * j + 1]);
-            v[4 * j + 2] = o.z + __uint_as_float(r[4 * j + 2]);
-            v[4 * j + 3] = o.w + __uint_as_float(r[4 * j + 3]);
-          }
-          if constexpr (EPI == EPI_ACCUM32) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (cbase + 4 * j + 4 <= p.N)
-                *reinterpret_cast<float4*>(c32 + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-          } else {
-            uint16_t* dst = reinterpret_cast<uint16_t*>(p.C16) + row * p.ldc16 + cbase;
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              if (cbase + 8 * j + 8 <= p.N)
-                *reinterpret_cast<uint4*>(dst + 8 * j) =
-                    make_uint4(pack16(v[8 * j], v[8 * j + 1], p.is_bf16), pack16(v[8 * j + 2], v[8 * j + 3], p.is_bf16),
-                               pack16(v[8 * j + 4], v[8 * j + 5], p.is_bf16), pack16(v[8 * j + 6], v[8 * j + 7], p.is_bf16));
-          }
         }
       }
     }

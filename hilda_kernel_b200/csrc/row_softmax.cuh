@@ -12,7 +12,6 @@
 // the per-row scalars (loss, kl, ...) and the gradient coefficients follow from (lse, x_target):
 //     grad[j] = alpha * softmax(x/T)[j] + (j == target ? beta : 0).
 #pragma once
-#include <cstdlib>
 #include "common.cuh"
 
 namespace hilda {
@@ -144,7 +143,6 @@ __device__ __forceinline__ float vec_exp_inplace(uint4& v, float k, float m) {
 
 constexpr int ROW_THREADS_DEFAULT = 256;
 constexpr int ROW_STATUS_TARGET_RANGE = 31;  // status word: a target / token id outside [0, V)
-constexpr int ROW_STATUS_COPY_WAIT = 32;     // status word: a bounded wait for a staged row slice ran out
 
 // Register-resident, cluster-per-row kernel. Requires V % VEC == 0 and 16-byte aligned rows.
 // CTAs per SM the register budget is held to (the row slice itself takes 4*NV registers).
@@ -154,197 +152,111 @@ constexpr int row_min_blocks(int threads, int nv) {
 
 template <typename T, int ROW_THREADS, int NV, int CLUSTER, class Op>
 __global__ void __launch_bounds__(ROW_THREADS, row_min_blocks(ROW_THREADS, NV))
-row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V, Op op, int* __restrict__ status,
-                   int64_t n_rows, int prefetch_rows, int stage_next) {
+row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V, Op op, int* __restrict__ status) {
   constexpr int VEC = VT<T>::N;
-  // stage_next: this CTA's slice of its NEXT active row is copied into shared memory by one bulk
-  // asynchronous copy while the current row is reduced, exchanged and stored; a row then starts from
-  // shared memory instead of waiting a DRAM round trip with nothing else in flight. One slot suffices:
-  // the slice moves to registers at the start of the row and the slot is refilled at once.
-  extern __shared__ __align__(128) uint8_t next_slice[];
-  __shared__ __align__(8) uint64_t slice_bar;
   __shared__ float red[33];
-  __shared__ float xchg[2][2 * CLUSTER];  // two sets: a fast CTA may already write the next row's pair
+  __shared__ float xchg[2 * CLUSTER];
   const int tid = threadIdx.x;
   const uint32_t rank = (CLUSTER > 1) ? cluster_ctarank() : 0u;
+  const int64_t row = blockIdx.x / CLUSTER;
   const int n_vec = (int)(V / VEC);
   const int slice = (n_vec + CLUSTER - 1) / CLUSTER;
   const int v0 = (int)rank * slice;
   const int v1 = min(n_vec, v0 + slice);
-  const int my_vec = v1 - v0;  // vectors in this CTA's slice
+  const int64_t roff = op.row_offset(row, V);
+  const T* xr = logits + roff;
+  T* gr = grad ? grad + roff : nullptr;
   const bool writer = (rank == 0 && tid == 0);
-  const int64_t n_clusters = gridDim.x / CLUSTER;
-  // "I have started": a peer may write into this CTA's shared memory only once it knows that, so
-  // every CTA arrives here, once, and waits for the others right before its first remote stores; the
-  // wait has a whole row load and two reductions to hide under.
-  if constexpr (CLUSTER > 1) cluster_arrive_relaxed();
-  bool peers_started = false;
-  uint32_t xset = 0;
-  const bool staged = stage_next != 0 && my_vec > 0;
-  const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&slice_bar);
-  const uint32_t slot = (uint32_t)__cvta_generic_to_shared(next_slice);
-  uint32_t slice_phase = 0;
-  // thread 0: copy this CTA's slice of the first active row at or after `from` into the slot
-  auto stage_row = [&](int64_t from) {
-    int64_t tg;
-    for (int64_t r = from; r < n_rows; r += n_clusters) {
-      if (!op.begin(r, tg)) continue;
-      const T* p = logits + op.row_offset(r, V) + (int64_t)v0 * VEC;
-      const uint32_t bytes = (uint32_t)my_vec * 16u;
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                   ::"r"(slot), "l"(p), "r"(bytes), "r"(bar) : "memory");
-      return;
+
+  int64_t target = -1;
+  const bool active = op.begin(row, target);  // identical in every CTA of the cluster
+  if (!active) {
+    if (gr) {
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      for (int v = v0 + tid; v < v1; v += ROW_THREADS) st16_stream(gr + (int64_t)v * VEC, z);
     }
-  };
-  if (staged) {
-    if (tid == 0) {
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
-      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      stage_row(blockIdx.x / CLUSTER);
-    }
-    __syncthreads();
+    if (writer) op.inactive(row);
+    return;
   }
+  // "I have started": a peer may write into this CTA's shared memory only once it knows that, so
+  // every CTA of an active row arrives here and waits for the others right before its remote
+  // stores; the wait has the whole row load and two reductions to hide under.
+  if constexpr (CLUSTER > 1) cluster_arrive_relaxed();
+  // A target outside [0, V) is not "ignored": the row takes part with no target logit and no
+  // one-hot term, and the status word tells the host (the reference reads out of bounds there).
+  if (writer && status && (target < 0 || target >= V)) atomicCAS(status, 0, ROW_STATUS_TARGET_RANGE);
 
-  // A cluster owns rows cluster, cluster + n_clusters, ...: launched with one cluster per row this is
-  // a single pass; launched with as many clusters as are resident at once it is a persistent loop
-  // (no cluster launch between rows, and the next row's slice can be requested a whole row early).
-  for (int64_t row = blockIdx.x / CLUSTER; row < n_rows; row += n_clusters) {
-    // Ask the L2 for this CTA's slice of the row it (or a CTA starting soon) will process
-    // `prefetch_rows` rows from now: one bulk prefetch instruction. DRAM then streams the upcoming
-    // rows while the resident CTAs are in their reduce / exchange / store phases.
-    if (prefetch_rows > 0 && tid == 0 && my_vec > 0) {
-      const int64_t ahead = row + prefetch_rows;
-      int64_t tgt_ahead;
-      if (ahead < n_rows && op.begin(ahead, tgt_ahead)) {
-        const T* p = logits + op.row_offset(ahead, V) + (int64_t)v0 * VEC;
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"((uint32_t)my_vec * 16u) : "memory");
-      }
-    }
-    const int64_t roff = op.row_offset(row, V);
-    const T* xr = logits + roff;
-    T* gr = grad ? grad + roff : nullptr;
+  // per-thread base pointers: vector i of this thread sits at a compile-time offset from them
+  const int my_vec = v1 - v0;  // vectors in this CTA's slice
+  const uint4* src = reinterpret_cast<const uint4*>(xr) + v0 + tid;
+  uint4 xv[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+    xv[i] = (tid + i * ROW_THREADS < my_vec) ? ld16_stream(src + i * ROW_THREADS) : neg_inf_vec<T>();
+  const float inv_t = op.inv_temperature();
+  const float k = inv_t * LOG2E;  // logits -> log2 domain
+  float x_t = 0.f;
+  if (target >= 0 && target < V) x_t = VT<T>::load1(xr + target) * inv_t;
+  // the per-row scalars finish() needs are fetched now, under the row loads, not after the reduction
+  const typename Op::Pre pre = op.prefetch(row);
 
-    int64_t target = -1;
-    const bool active = op.begin(row, target);  // identical in every CTA of the cluster
-    if (!active) {
-      if (gr) {
-        const uint4 z = make_uint4(0, 0, 0, 0);
-        for (int v = v0 + tid; v < v1; v += ROW_THREADS) st16_stream(gr + (int64_t)v * VEC, z);
-      }
-      if (writer) op.inactive(row);
-      continue;
-    }
-    // A target outside [0, V) is not "ignored": the row takes part with no target logit and no
-    // one-hot term, and the status word tells the host (the reference reads out of bounds there).
-    if (writer && status && (target < 0 || target >= V)) atomicCAS(status, 0, ROW_STATUS_TARGET_RANGE);
+  // pass 1: max of the raw logits (k > 0, so the scale is applied once to the maximum)
+  typename RowMath<T>::MaxAcc macc = RowMath<T>::max_init();
+#pragma unroll
+  for (int i = 0; i < NV; ++i) RowMath<T>::vmax(macc, xv[i]);
+  float m = block_max<ROW_THREADS>(RowMath<T>::max_final(macc), red) * k;
+  const float m_safe = (m == -INFINITY) ? 0.f : m;
+  // pass 2: e = 2^(x*k - m) summed in fp32, and kept IN PLACE of x (rounded to T): the gradient
+  // pass then needs one multiply per element instead of a second exponential (the SFU would
+  // otherwise be the bottleneck at HBM speed).
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    opaque(xv[i]);
+    s += vec_exp_inplace<T>(xv[i], k, m_safe);
+    opaque(xv[i]);  // orders the iterations: at most one vector is unpacked to fp32 at a time
+  }
+  s = block_sum<ROW_THREADS>(s, red);
 
-    // per-thread base pointers: vector i of this thread sits at a compile-time offset from them
-    const uint4* src = reinterpret_cast<const uint4*>(xr) + v0 + tid;
-    uint4 xv[NV];
-    if (staged) {
-      // the slice was requested a whole row ago; the wait is bounded all the same
-      bool landed = false;
-      for (uint32_t t = 0; t < (1u << 24); ++t) {
-        uint32_t ok;
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-                     : "=r"(ok) : "r"(bar), "r"(slice_phase) : "memory");
-        if (ok) { landed = true; break; }
-      }
-      slice_phase ^= 1u;
-      const uint4* sm = reinterpret_cast<const uint4*>(next_slice) + tid;
-      if (landed) {
-#pragma unroll
-        for (int i = 0; i < NV; ++i)
-          xv[i] = (tid + i * ROW_THREADS < my_vec) ? sm[i * ROW_THREADS] : neg_inf_vec<T>();
-      } else {
-        // the copy never signalled (it always should): say so and take the row from global memory
-        if (tid == 0 && status) atomicCAS(status, 0, ROW_STATUS_COPY_WAIT);
-#pragma unroll
-        for (int i = 0; i < NV; ++i)
-          xv[i] = (tid + i * ROW_THREADS < my_vec) ? ld16_stream(src + i * ROW_THREADS) : neg_inf_vec<T>();
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < NV; ++i)
-        xv[i] = (tid + i * ROW_THREADS < my_vec) ? ld16_stream(src + i * ROW_THREADS) : neg_inf_vec<T>();
+  float M = m, S = s;
+  if constexpr (CLUSTER > 1) {
+    cluster_wait();  // every CTA of the cluster is running: its shared memory may be written
+    if (tid < CLUSTER) {
+      const uint32_t base = (uint32_t)__cvta_generic_to_shared(xchg);
+      const uint32_t remote = map_to_cta(base, (uint32_t)tid);
+      st_cluster_f32(remote + 8u * rank, m);
+      st_cluster_f32(remote + 8u * rank + 4u, s);
     }
-    const float inv_t = op.inv_temperature();
-    const float k = inv_t * LOG2E;  // logits -> log2 domain
-    float x_t = 0.f;
-    if (target >= 0 && target < V) x_t = VT<T>::load1(xr + target) * inv_t;
-    // the per-row scalars finish() needs are fetched now, under the row loads, not after the reduction
-    const typename Op::Pre pre = op.prefetch(row);
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    M = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < CLUSTER; ++c) M = fmaxf(M, xchg[2 * c]);
+    S = 0.f;
+#pragma unroll
+    for (int c = 0; c < CLUSTER; ++c) S = fmaf(xchg[2 * c + 1], ex2_approx(xchg[2 * c] - M), S);  // empty slice: 0 * 2^-inf
+  }
+  const float lse2 = M + log2f(S);
+  const float lse = lse2 * LN2;  // natural-log logsumexp of logits/T
 
-    // pass 1: max of the raw logits (k > 0, so the scale is applied once to the maximum)
-    typename RowMath<T>::MaxAcc macc = RowMath<T>::max_init();
-#pragma unroll
-    for (int i = 0; i < NV; ++i) RowMath<T>::vmax(macc, xv[i]);
-    float m = block_max<ROW_THREADS>(RowMath<T>::max_final(macc), red) * k;
-    const float m_safe = (m == -INFINITY) ? 0.f : m;
-    // the block maximum's barriers also mean: every thread has taken its vectors out of the slot
-    if (staged && tid == 0) {
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      stage_row(row + n_clusters);
-    }
-    // pass 2: e = 2^(x*k - m) summed in fp32, and kept IN PLACE of x (rounded to T): the gradient
-    // pass then needs one multiply per element instead of a second exponential (the SFU would
-    // otherwise be the bottleneck at HBM speed).
-    float s = 0.f;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      opaque(xv[i]);
-      s += vec_exp_inplace<T>(xv[i], k, m_safe);
-      opaque(xv[i]);  // orders the iterations: at most one vector is unpacked to fp32 at a time
-    }
-    s = block_sum<ROW_THREADS>(s, red);
+  const RowCoef co = op.finish(row, lse, x_t, writer, pre);
+  if (!gr) return;
 
-    float M = m, S = s;
-    if constexpr (CLUSTER > 1) {
-      if (!peers_started) {
-        cluster_wait();  // every CTA of the cluster is running: its shared memory may be written
-        peers_started = true;
-      }
-      const float* mine = xchg[xset];
-      if (tid < CLUSTER) {
-        const uint32_t base = (uint32_t)__cvta_generic_to_shared(mine);
-        const uint32_t remote = map_to_cta(base, (uint32_t)tid);
-        st_cluster_f32(remote + 8u * rank, m);
-        st_cluster_f32(remote + 8u * rank + 4u, s);
-      }
-      cluster_arrive_release();
-      cluster_wait_acquire();
-      M = -INFINITY;
+  // softmax_j = e_j * 2^(m_cta - lse2)
+  const float coef = (m == -INFINITY) ? 0.f : co.alpha * ex2_approx(m - lse2);
+  const typename RowMath<T>::Coef pc = RowMath<T>::make_coef(coef);
+  uint4* dst = reinterpret_cast<uint4*>(gr) + v0 + tid;
 #pragma unroll
-      for (int c = 0; c < CLUSTER; ++c) M = fmaxf(M, mine[2 * c]);
-      S = 0.f;
-#pragma unroll
-      for (int c = 0; c < CLUSTER; ++c) S = fmaf(mine[2 * c + 1], ex2_approx(mine[2 * c] - M), S);  // empty slice: 0 * 2^-inf
-      xset ^= 1u;
-    }
-    const float lse2 = M + log2f(S);
-    const float lse = lse2 * LN2;  // natural-log logsumexp of logits/T
-
-    const RowCoef co = op.finish(row, lse, x_t, writer, pre);
-    if (!gr) continue;
-
-    // softmax_j = e_j * 2^(m_cta - lse2)
-    const float coef = (m == -INFINITY) ? 0.f : co.alpha * ex2_approx(m - lse2);
-    const typename RowMath<T>::Coef pc = RowMath<T>::make_coef(coef);
-    uint4* dst = reinterpret_cast<uint4*>(gr) + v0 + tid;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      RowMath<T>::scale(xv[i], pc);
-      if (tid + i * ROW_THREADS < my_vec) st16_stream(dst + i * ROW_THREADS, xv[i]);
-    }
-    // The target column gets alpha*softmax + beta: the thread that stored its vector overwrites that
-    // one element afterwards (same thread, same address: program order holds).
-    if (target >= 0 && target < V) {
-      const int tv = (int)(target / VEC) - v0;
-      if (tv >= 0 && tv < my_vec && (tv % ROW_THREADS) == tid)
-        VT<T>::store1(gr + target, co.alpha * ex2_approx((x_t - lse) * LOG2E) + co.beta);
-    }
+  for (int i = 0; i < NV; ++i) {
+    RowMath<T>::scale(xv[i], pc);
+    if (tid + i * ROW_THREADS < my_vec) st16_stream(dst + i * ROW_THREADS, xv[i]);
+  }
+  // The target column gets alpha*softmax + beta: the thread that stored its vector overwrites that
+  // one element afterwards (same thread, same address: program order holds).
+  if (target >= 0 && target < V) {
+    const int tv = (int)(target / VEC) - v0;
+    if (tv >= 0 && tv < my_vec && (tv % ROW_THREADS) == tid)
+      VT<T>::store1(gr + target, co.alpha * ex2_approx((x_t - lse) * LOG2E) + co.beta);
   }
 }
 
@@ -423,21 +335,10 @@ static inline RowPlan plan_row(int64_t V, int vec, bool aligned, int force_nv, i
 
 template <typename T, int THREADS, int NV, int CLUSTER, class Op>
 static int launch_row_cfg(const T* logits, T* grad, int64_t n_rows, int64_t V, const Op& op, int* status, cudaStream_t st) {
-  // HILDA_ROW_PERSIST (default 1): launch only as many clusters as are resident at once and let each
-  // walk its rows; 0: one cluster per row. HILDA_ROW_PREFETCH: rows ahead whose slice a CTA asks the
-  // L2 for (default: the cluster's own next row when persistent, off otherwise; 0 = off).
-  static const int env_persist = []() { const char* e = getenv("HILDA_ROW_PERSIST"); return e ? atoi(e) : 1; }();
-  static const int env_pf = []() { const char* e = getenv("HILDA_ROW_PREFETCH"); return e ? atoi(e) : -1; }();
-  // HILDA_ROW_STAGE (default 1, needs the persistent launch): the next row's slice is staged in shared memory
-  static const int env_stage = []() { const char* e = getenv("HILDA_ROW_STAGE"); return e ? atoi(e) : 1; }();
-  auto kern = row_softmax_kernel<T, THREADS, NV, CLUSTER, Op>;
-  const int64_t n_vec = V / VT<T>::N;
-  const int slice_bytes = (int)((n_vec + CLUSTER - 1) / CLUSTER) * 16;
-  const int stage_next = (env_persist && env_stage) ? 1 : 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(n_rows * CLUSTER), 1, 1);
   cfg.blockDim = dim3(THREADS, 1, 1);
-  cfg.dynamicSmemBytes = stage_next ? (size_t)slice_bytes : 0;
+  cfg.dynamicSmemBytes = 0;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -446,31 +347,7 @@ static int launch_row_cfg(const T* logits, T* grad, int64_t n_rows, int64_t V, c
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (stage_next && slice_bytes > 48 * 1024 &&
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, slice_bytes) != cudaSuccess)
-    return HILDA_ERR_CUDA;
-  int prefetch_rows = env_pf > 0 ? env_pf : 0;
-  if (env_persist) {
-    // clusters resident at once, per device, for THIS instantiation and the last dynamic shared-memory size seen
-    static thread_local int resident[64] = {0};
-    static thread_local int resident_smem[64] = {0};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) dev = 0;
-    if (resident[dev] == 0 || resident_smem[dev] != (int)cfg.dynamicSmemBytes) {
-      resident_smem[dev] = (int)cfg.dynamicSmemBytes;
-      int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
-        cudaGetLastError();
-        n = sm_count() * row_min_blocks(THREADS, NV) / CLUSTER;
-      }
-      resident[dev] = n > 0 ? n : 1;
-    }
-    const int64_t clusters = n_rows < resident[dev] ? n_rows : resident[dev];
-    cfg.gridDim = dim3((unsigned)(clusters * CLUSTER), 1, 1);
-    if (env_pf < 0) prefetch_rows = stage_next ? 0 : (int)clusters;  // the cluster's own next row, unless it is staged
-  }
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, logits, grad, V, op, status, n_rows, prefetch_rows, stage_next);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, row_softmax_kernel<T, THREADS, NV, CLUSTER, Op>, logits, grad, V, op, status);
   return e == cudaSuccess ? HILDA_OK : HILDA_ERR_CUDA;
 }
 

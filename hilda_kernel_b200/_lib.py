@@ -11,7 +11,7 @@ import os
 import torch
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libhilda_b200.so")
+LIB_PATH = os.environ.get("HILDA_LIB_PATH") or os.path.join(_PKG, "libhilda_b200.so")  # HILDA_LIB_PATH: another build of the same ABI
 # HILDA_DEBUG=1 prefers the library built with -DHILDA_DEBUG (python -m hilda_kernel_b200._build --debug)
 if os.environ.get("HILDA_DEBUG", "0") not in ("", "0") and os.path.exists(os.path.join(_PKG, "libhilda_b200_debug.so")):
     LIB_PATH = os.path.join(_PKG, "libhilda_b200_debug.so")

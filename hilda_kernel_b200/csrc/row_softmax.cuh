@@ -141,6 +141,15 @@ __device__ __forceinline__ float vec_exp_inplace(uint4& v, float k, float m) {
   return s;
 }
 
+// Build-time variants, measured on B200 at the benchmark shapes (CrossEntropy [8192,128256] / GRPO
+// [16,1024,151936] bf16, us): warp-local maxima 699.5 / 1373, block maximum first 707.5 / 1372; loading
+// the vectors every thread holds without a bounds test made both slower (718.6 / 1402: more code, spills).
+#ifndef ROW_WARP_LOCAL
+#define ROW_WARP_LOCAL 1   // 1: warps work relative to their own maximum (one block barrier per row); 0: block maximum first
+#endif
+#ifndef ROW_FULL_FAST
+#define ROW_FULL_FAST 0    // 1: vectors every thread holds are loaded / stored without a bounds test
+#endif
 constexpr int ROW_THREADS_DEFAULT = 256;
 constexpr int ROW_STATUS_TARGET_RANGE = 31;  // status word: a target / token id outside [0, V)
 
@@ -154,7 +163,11 @@ template <typename T, int ROW_THREADS, int NV, int CLUSTER, class Op>
 __global__ void __launch_bounds__(ROW_THREADS, row_min_blocks(ROW_THREADS, NV))
 row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V, Op op, int* __restrict__ status) {
   constexpr int VEC = VT<T>::N;
+#if ROW_WARP_LOCAL
+  __shared__ float wpair[2 * (ROW_THREADS / 32)];  // per warp: (max in the log2 domain, sum of 2^(x - max))
+#else
   __shared__ float red[33];
+#endif
   __shared__ float xchg[2 * CLUSTER];
   const int tid = threadIdx.x;
   const uint32_t rank = (CLUSTER > 1) ? cluster_ctarank() : 0u;
@@ -188,11 +201,14 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
 
   // per-thread base pointers: vector i of this thread sits at a compile-time offset from them
   const int my_vec = v1 - v0;  // vectors in this CTA's slice
+  const int full = ROW_FULL_FAST ? my_vec / ROW_THREADS : 0;  // vectors every thread of the CTA holds: no bounds test for those
   const uint4* src = reinterpret_cast<const uint4*>(xr) + v0 + tid;
   uint4 xv[NV];
 #pragma unroll
-  for (int i = 0; i < NV; ++i)
-    xv[i] = (tid + i * ROW_THREADS < my_vec) ? ld16_stream(src + i * ROW_THREADS) : neg_inf_vec<T>();
+  for (int i = 0; i < NV; ++i) {
+    if (i < full) xv[i] = ld16_stream(src + i * ROW_THREADS);
+    else xv[i] = (tid + i * ROW_THREADS < my_vec) ? ld16_stream(src + i * ROW_THREADS) : neg_inf_vec<T>();
+  }
   const float inv_t = op.inv_temperature();
   const float k = inv_t * LOG2E;  // logits -> log2 domain
   float x_t = 0.f;
@@ -200,13 +216,16 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
   // the per-row scalars finish() needs are fetched now, under the row loads, not after the reduction
   const typename Op::Pre pre = op.prefetch(row);
 
-  // pass 1: max of the raw logits (k > 0, so the scale is applied once to the maximum)
+#if ROW_WARP_LOCAL
+  // pass 1: max of the raw logits over the WARP only (k > 0, so the scale is applied once to the
+  // maximum). Each warp works relative to its own maximum: it goes on to the exponentials as soon as
+  // its own loads have landed, and the block needs one barrier per row instead of four.
   typename RowMath<T>::MaxAcc macc = RowMath<T>::max_init();
 #pragma unroll
   for (int i = 0; i < NV; ++i) RowMath<T>::vmax(macc, xv[i]);
-  float m = block_max<ROW_THREADS>(RowMath<T>::max_final(macc), red) * k;
-  const float m_safe = (m == -INFINITY) ? 0.f : m;
-  // pass 2: e = 2^(x*k - m) summed in fp32, and kept IN PLACE of x (rounded to T): the gradient
+  const float m_w = warp_max(RowMath<T>::max_final(macc)) * k;
+  const float m_safe = (m_w == -INFINITY) ? 0.f : m_w;
+  // pass 2: e = 2^(x*k - m_w) summed in fp32, and kept IN PLACE of x (rounded to T): the gradient
   // pass then needs one multiply per element instead of a second exponential (the SFU would
   // otherwise be the bottleneck at HBM speed).
   float s = 0.f;
@@ -216,8 +235,37 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
     s += vec_exp_inplace<T>(xv[i], k, m_safe);
     opaque(xv[i]);  // orders the iterations: at most one vector is unpacked to fp32 at a time
   }
+  s = warp_sum(s);
+  // the warps' (max, sum) pairs -> the CTA's pair, computed by every thread (fixed order)
+  constexpr int NW = ROW_THREADS / 32;
+  if ((tid & 31) == 0) { wpair[2 * (tid >> 5)] = m_w; wpair[2 * (tid >> 5) + 1] = s; }
+  __syncthreads();
+  float m = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < NW; ++w) m = fmaxf(m, wpair[2 * w]);
+  s = 0.f;
+#pragma unroll
+  for (int w = 0; w < NW; ++w) s = fmaf(wpair[2 * w + 1], ex2_approx(wpair[2 * w] - m), s);  // empty warp: 0 * 2^-inf
+  if (m == -INFINITY) s = 0.f;
+
+#else
+  // pass 1: max of the raw logits (k > 0, so the scale is applied once to the maximum)
+  typename RowMath<T>::MaxAcc macc = RowMath<T>::max_init();
+#pragma unroll
+  for (int i = 0; i < NV; ++i) RowMath<T>::vmax(macc, xv[i]);
+  float m = block_max<ROW_THREADS>(RowMath<T>::max_final(macc), red) * k;
+  const float m_w = m;
+  const float m_safe = (m == -INFINITY) ? 0.f : m;
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    opaque(xv[i]);
+    s += vec_exp_inplace<T>(xv[i], k, m_safe);
+    opaque(xv[i]);
+  }
   s = block_sum<ROW_THREADS>(s, red);
 
+#endif
   float M = m, S = s;
   if constexpr (CLUSTER > 1) {
     cluster_wait();  // every CTA of the cluster is running: its shared memory may be written
@@ -242,14 +290,14 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
   const RowCoef co = op.finish(row, lse, x_t, writer, pre);
   if (!gr) return;
 
-  // softmax_j = e_j * 2^(m_cta - lse2)
-  const float coef = (m == -INFINITY) ? 0.f : co.alpha * ex2_approx(m - lse2);
+  // softmax_j = e_j * 2^(m_warp - lse2)
+  const float coef = (m_w == -INFINITY) ? 0.f : co.alpha * ex2_approx(m_w - lse2);
   const typename RowMath<T>::Coef pc = RowMath<T>::make_coef(coef);
   uint4* dst = reinterpret_cast<uint4*>(gr) + v0 + tid;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     RowMath<T>::scale(xv[i], pc);
-    if (tid + i * ROW_THREADS < my_vec) st16_stream(dst + i * ROW_THREADS, xv[i]);
+    if (i < full || tid + i * ROW_THREADS < my_vec) st16_stream(dst + i * ROW_THREADS, xv[i]);
   }
   // The target column gets alpha*softmax + beta: the thread that stored its vector overwrites that
   // one element afterwards (same thread, same address: program order holds).

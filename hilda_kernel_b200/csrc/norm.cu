@@ -445,8 +445,16 @@ dw_reduce_kernel(const float* __restrict__ partial, int P, int64_t n_cols, void*
   const int cx = threadIdx.x & 31, gy = threadIdx.x >> 5;
   const int64_t col = (int64_t)blockIdx.x * 32 + cx;
   float acc = 0.f;
-  if (col < n_cols)
-    for (int p = gy; p < P; p += 32) acc += partial[(int64_t)p * n_cols + col];
+  if (col < n_cols) {
+    // four loads in flight per thread; the order of the additions stays fixed
+    int p = gy;
+    for (; p + 96 < P; p += 128) {
+      const float a0 = partial[(int64_t)p * n_cols + col], a1 = partial[(int64_t)(p + 32) * n_cols + col];
+      const float a2 = partial[(int64_t)(p + 64) * n_cols + col], a3 = partial[(int64_t)(p + 96) * n_cols + col];
+      acc += a0; acc += a1; acc += a2; acc += a3;
+    }
+    for (; p < P; p += 32) acc += partial[(int64_t)p * n_cols + col];
+  }
   tile[gy][cx] = acc;
   __syncthreads();
   if (gy == 0 && col < n_cols) {
@@ -564,10 +572,12 @@ static int norm_bwd_t(const void* dy, const void* ds, const void* x, const void*
     // ring of row slots in shared memory: as many as fit beside the other CTAs of the SM, at most NB_MAX_STAGES
     const int per_sm = (grid + sm_count() - 1) / sm_count();
     const int64_t stage_bytes = n_cols * (int64_t)sizeof(T) * (1 + (dy ? 1 : 0) + (ds ? 1 : 0));
-    int64_t stages = ((int64_t)220 * 1024 / per_sm - 1024 - n_cols * 4) / stage_bytes;
+    // 228 KB of shared memory per SM, 1 KB of it reserved per resident CTA, a few hundred bytes static
+    int64_t stages = ((int64_t)228 * 1024 / per_sm - 1024 - 512 - n_cols * 4) / stage_bytes;
     if (stages > NB_MAX_STAGES) stages = NB_MAX_STAGES;
-    if ((g_norm_ring == 1 && stages >= 3) || (g_norm_ring == 4 && stages >= 2)) {
-      const int smem = (int)(stages * stage_bytes + n_cols * 4);
+    const int64_t min_stages = g_norm_ring == 4 ? 2 : 3;
+    if ((g_norm_ring == 1 || g_norm_ring == 4) && stages >= min_stages) {
+      int smem = 0;
       cudaError_t e = cudaSuccess;
       int occ = 0;
 #define RING_PREP(TT, TH, VP)                                                                                  \
@@ -575,11 +585,16 @@ static int norm_bwd_t(const void* dy, const void* ds, const void* x, const void*
     e = cudaFuncSetAttribute(norm_bwd_ring_kernel<TT, TH, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
     if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, norm_bwd_ring_kernel<TT, TH, VP>, TH, smem); \
   } while (0)
-      NORM_DISPATCH_TV(T, RING_PREP)
+      // one slot fewer while the planned number of CTAs per SM does not fit with this many
+      for (; stages >= min_stages; --stages) {
+        smem = (int)(stages * stage_bytes + n_cols * 4);
+        NORM_DISPATCH_TV(T, RING_PREP)
+        if (e != cudaSuccess || occ >= per_sm) break;
+      }
 #undef RING_PREP
+      if (stages < min_stages) { occ = 0; e = cudaSuccess; }
       if (e != cudaSuccess) return HILDA_ERR_CUDA;
-      if (occ >= 1) {
-        if (occ < per_sm && (int64_t)occ * sm_count() < grid) grid = occ * sm_count();
+      if (occ >= per_sm) {
 #define RING_CALL(TT, TH, VP)                                                                                  \
   norm_bwd_ring_kernel<TT, TH, VP><<<grid, TH, smem, st>>>((const TT*)dy, (const TT*)ds, (const TT*)x, w, w_dt, rstd, \
                                                            (TT*)dx, workspace, n_rows, (int)n_cols, (int)stages)

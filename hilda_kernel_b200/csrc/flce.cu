@@ -141,45 +141,48 @@ static inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * 
 // Index lists of the non-ignored rows, built on the device so that no host round trip is needed:
 // idx[j] = source row of compacted row j (-1 for j >= n_valid), inv[i] = compacted position of source
 // row i (-1 if ignored), t_c[j] = targets[idx[j]] (ignore_index for j >= n_valid), *n_valid = count.
-// One CTA; thread t owns the contiguous segment [t*seg, (t+1)*seg), so the order is kept.
+// One CTA of 32 warps; warp w owns the contiguous range [w * per_warp, (w + 1) * per_warp) and walks it
+// 32 elements at a time (coalesced), positions from ballot + popcount, so the order is kept.
 __global__ void __launch_bounds__(1024)
 flce_compact_kernel(const int64_t* __restrict__ targets, int64_t n, int64_t ignore_index, int64_t* __restrict__ idx,
                     int* __restrict__ inv, int64_t* __restrict__ t_c, int* __restrict__ n_valid) {
-  __shared__ int warp_tot[32];
+  __shared__ int warp_base[33];
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-  const int64_t seg = (n + 1023) / 1024;
-  const int64_t b = (int64_t)tid * seg, e = (b + seg < n) ? b + seg : n;
+  const int64_t per_warp = ((n + 31) / 32 + 31) / 32 * 32;
+  const int64_t w0 = (int64_t)wid * per_warp;
+  const int64_t w1 = (w0 + per_warp < n) ? w0 + per_warp : n;
   int cnt = 0;
-  for (int64_t i = b; i < e; ++i) cnt += (targets[i] != ignore_index) ? 1 : 0;
-  int incl = cnt;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int v = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += v;
+  for (int64_t base = w0; base < w1; base += 32) {
+    const int64_t e = base + lane;
+    const bool valid = e < w1 && targets[e] != ignore_index;
+    cnt += __popc(__ballot_sync(0xffffffffu, valid));
   }
-  if (lane == 31) warp_tot[wid] = incl;
+  if (lane == 0) warp_base[wid] = cnt;
   __syncthreads();
   if (wid == 0) {
-    int w = warp_tot[lane], wi = w;
+    const int c = warp_base[lane];
+    int incl = c;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const int v = __shfl_up_sync(0xffffffffu, wi, o);
-      if (lane >= o) wi += v;
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
     }
-    warp_tot[lane] = wi - w;  // exclusive
-    if (lane == 31) *n_valid = wi;
+    warp_base[lane] = incl - c;  // exclusive
+    if (lane == 31) { warp_base[32] = incl; *n_valid = incl; }
   }
   __syncthreads();
-  int64_t pos = warp_tot[wid] + incl - cnt;
-  for (int64_t i = b; i < e; ++i) {
-    const int64_t t = targets[i];
-    if (t != ignore_index) { idx[pos] = i; t_c[pos] = t; inv[i] = (int)pos; ++pos; }
-    else inv[i] = -1;
+  int pos = warp_base[wid];
+  for (int64_t base = w0; base < w1; base += 32) {
+    const int64_t e = base + lane;
+    const int64_t t = e < w1 ? targets[e] : ignore_index;
+    const bool valid = e < w1 && t != ignore_index;
+    const unsigned mask = __ballot_sync(0xffffffffu, valid);
+    const int mine = pos + __popc(mask & ((1u << lane) - 1u));
+    if (valid) { idx[mine] = e; t_c[mine] = t; inv[e] = mine; }
+    else if (e < w1) inv[e] = -1;
+    pos += __popc(mask);
   }
-  __shared__ int total_s;
-  if (tid == 1023) total_s = (int)pos;  // the last thread's end position = number of valid rows
-  __syncthreads();
-  for (int64_t j = (int64_t)total_s + tid; j < n; j += 1024) { idx[j] = -1; t_c[j] = ignore_index; }
+  for (int64_t j = (int64_t)warp_base[32] + tid; j < n; j += 1024) { idx[j] = -1; t_c[j] = ignore_index; }
 }
 
 // dst[j, :] = src[idx[j], :] for idx[j] >= 0; rows j in [n_valid, round_up(n_valid, 256)) are cleared (the

@@ -890,6 +890,30 @@ def run_ours(args):
     lib.hilda_flce_profile(0)
     del out
 
+    # ---- optional: device time of every kernel of the step (CUPTI through torch.profiler), NCCL's included
+    step_trace = None
+    if args.trace:
+        from torch.profiler import ProfilerActivity, profile
+        n_tr = 3
+        barrier()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(n_tr):
+                out = step()
+            torch.cuda.synchronize()
+        barrier()
+        if rank == 0:
+            rows_ = []
+            for ev in prof.key_averages():
+                t_us = getattr(ev, "device_time_total", None)
+                if t_us is None:
+                    t_us = getattr(ev, "cuda_time_total", 0.0)
+                if t_us > 0:
+                    rows_.append([ev.key[:90], round(t_us / n_tr, 1), ev.count // n_tr])
+            rows_.sort(key=lambda r: -r[1])
+            step_trace = {"unit": "us per step on rank 0, summed over launches; kernels on different streams overlap",
+                          "kernels": rows_[:24], "sum_us": round(sum(r[1] for r in rows_), 1)}
+        del out
+
     # ---- parity of this very configuration, outside any timed region, at every N
     parity = None
     if not args.no_parity:
@@ -1057,6 +1081,8 @@ def run_ours(args):
     }
     if parity is not None:
         result["parity"] = parity
+    if step_trace is not None:
+        result["step_trace"] = step_trace
     if sharded is not None:
         result["ops_row_sharded"] = sharded
     if world == 1:
@@ -1137,6 +1163,8 @@ def main():
                          "(0 = no overlap; default: 16 at 8 GPUs, where the all-reduce's share of the step exceeds what the narrower GEMM costs)")
     ap.add_argument("--settle-seconds", type=float, default=0.0,
                     help="seconds of untimed steps before the warm-up steps, so that the power-capped clock is in its steady state (0 = none)")
+    ap.add_argument("--trace", action="store_true",
+                    help="add the device time of every kernel of the step (torch.profiler / CUPTI, rank 0, after the timed passes)")
     ap.add_argument("--no-parity", action="store_true", help="skip the parity block (plain PyTorch fp32 on the device)")
     ap.add_argument("--no-comparators", action="store_true",
                     help="skip the reference-Triton / Liger / eager comparators of the per-op table (N = 1)")

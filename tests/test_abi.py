@@ -158,3 +158,32 @@ def test_debug_flag_compiles(tmp_path):
         assert "-DHILDA_DEBUG" in cmd
         r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
         assert r.returncode == 0 and os.path.getsize(obj) > 0, r.stderr[-2000:]
+
+
+def test_bench_reference_arm_prints_the_contract_line(tmp_path):
+    """`bench.py --impl reference` runs the CPU restatement of the reference on a row sample of the
+    same workload and prints ONE JSON line whose metric, unit and config.workload are the ones the
+    GPU arm prints (a small shape here, so that it takes seconds)."""
+    import json
+    import subprocess
+    import sys
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0",
+                        "--bt", "256", "--vocab", "4096", "--hidden", "256"], capture_output=True, text=True, timeout=600,
+                       cwd=str(tmp_path))
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [l for l in r.stdout.splitlines() if l.strip().startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["metric"] == "FusedLinearCE fwd+bwd tokens/s" and d["unit"] == "tokens/s"
+    assert d["higher_is_better"] is True and d["value"] > 0 and d["vs_baseline"] is None
+    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
+    assert d["e2e"] == {"value": d["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    sys.path.insert(0, ROOT)
+    import bench
+    bench.BT, bench.V, bench.H = 256, 4096, 256
+    try:
+        assert d["config"]["workload"] == bench.workload_name()
+        t = bench.make_targets()
+        assert t.shape == (256,) and int((t == -100).sum()) == round(0.05 * 256)
+    finally:
+        bench.BT, bench.H, bench.V = 16384, 4096, 128256

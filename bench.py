@@ -410,15 +410,6 @@ def per_op_table(device, pk, only=None, small=False):
         fns = [(lambda q=q, kc=kc, vc=vc, bt=bt, cl=cl: hilda_paged_attention_fp8_decode(q, kc, vc, bt, cl, 128 ** -0.5))
                for q, kc, vc, bt, cl in sets]
         add("paged_attention_fp8_decode", timed(fns), 2 * batch * ctx * nkv * 128, batch)
-        # the other of the two kernels behind the same entry point, for comparison
-        import hilda_kernel_b200._lib as L
-        default_path = L.lib().hilda_paged_attention_set_path(-1)
-        L.lib().hilda_paged_attention_set_path(1 - default_path)
-        try:
-            add("paged_attention_fp8_decode_" + ("cuda_core_kernel" if default_path == 1 else "tensor_core_kernel"),
-                timed(fns), 2 * batch * ctx * nkv * 128, batch)
-        finally:
-            L.lib().hilda_paged_attention_set_path(default_path)
         del sets, fns
     # ---- the divergence losses (reference bench shapes: bench_kl_div.py:158, bench_jsd.py:175,
     # bench_fused_linear_jsd.py:165, in bf16)
@@ -1047,8 +1038,11 @@ def run_ours(args):
                    f"W vocab-sharded over {world} ranks, hidden replicated",
                    "ignored_rows": f"compacted away on the device before the GEMMs ({n_valid} of {BT} rows computed; no host sync)"
                    if FL.SKIP_IGNORED_ROWS else "computed like any other row",
-                   "power_settle": f"{n_settle} untimed steps before the warm-up steps (the step runs at the power cap; "
-                                   f"the clock needs about a second of load to reach the steady state the sustained peak is measured in)",
+                   "power_cap": "the step runs at the board's power cap: a short pass right after an idle period runs up to "
+                                "6 % faster than the same steps under seconds of continuous load, which is why the 5-step "
+                                "per-launch pass and the end-to-end loop (one host synchronisation per step, copies beside it) "
+                                "can beat the headline pass" + (f"; {n_settle} untimed settle steps ran before the warm-up"
+                                                               if n_settle else ""),
                    "row_chunks": n_chunks, "chunk_rows": chunk_rows, "l2": "inputs (1.05 GB W per pass) exceed the 126 MB L2; no flush needed"},
         "tflops_whole_step": 6.0 * rows_alg * V * H / world / (ms_step * 1e-3) / 1e12,
         # box-to-box spread is mostly the SM clock the 1000 W cap settles at: ms x MHz is comparable across boxes

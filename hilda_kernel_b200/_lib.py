@@ -62,7 +62,6 @@ SIGNATURES = {
     "hilda_kl_div_fwd": (_i32, [_p, _p, _p, _p, _i64, _i64, _i32, _i32, _f32, _i32, _p]),
     "hilda_kl_div_bwd": (_i32, [_p, _p, _p, _i64, _i64, _i32, _i32, _i32, _p]),
     "hilda_jsd_fwd": (_i32, [_p, _p, _p, _p, _p, _p, _i64, _p, _i64, _i64, _f32, _i32, _p]),    "hilda_paged_attention_fp8_workspace_bytes": (_i64, [_i64] * 5),
-    "hilda_paged_attention_set_path": (_i32, [_i32]),
     "hilda_paged_attention_fp8_decode": (_i32, [_p, _i64, _i64, _p, _i64, _i64, _i64, _p, _i64, _i64, _i64, _p, _i64, _i64,
                                                 _p, _i64, _p, _p, _f32, _i64, _i64, _i64, _i64, _i64, _i64, _p]),
 

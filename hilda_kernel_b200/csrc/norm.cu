@@ -217,6 +217,7 @@ norm_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __r
       }
     }
   }
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the second pass may start launching
   float* pr = partial + (int64_t)blockIdx.x * n_cols;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
@@ -396,6 +397,7 @@ norm_bwd_ring_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T
 #pragma unroll
       for (int j = 0; j < VEC; ++j) dw[i][j] = __int_as_float(0x7fc00000);
   }
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the second pass may start launching
   float* pr = partial + (int64_t)blockIdx.x * n_cols;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
@@ -442,6 +444,9 @@ norm_bwd_generic_kernel(const T* __restrict__ dY, const T* __restrict__ dS, cons
 __global__ void __launch_bounds__(1024)
 dw_reduce_kernel(const float* __restrict__ partial, int P, int64_t n_cols, void* __restrict__ dW, int w_dt) {
   __shared__ float tile[32][33];
+  // launched with programmatic stream serialisation: its CTAs may become resident while the backward
+  // kernel drains; nothing is read before that kernel has completed and its writes are visible
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int cx = threadIdx.x & 31, gy = threadIdx.x >> 5;
   const int64_t col = (int64_t)blockIdx.x * 32 + cx;
   float acc = 0.f;
@@ -538,6 +543,22 @@ static int norm_bwd_ctas(int64_t n_rows, int64_t n_cols, bool al) {
   return (int)ctas;
 }
 
+// The second pass, launched so that it may be scheduled while the backward kernel is still draining
+// (programmatic dependent launch; the kernel itself waits for the backward's completion).
+static int launch_dw_reduce(const float* partial, int P, int64_t n_cols, void* dw, int w_dt, cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((n_cols + 31) / 32), 1, 1);
+  cfg.blockDim = dim3(1024, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, dw_reduce_kernel, partial, P, n_cols, dw, w_dt) == cudaSuccess ? HILDA_OK : HILDA_ERR_CUDA;
+}
+
 // Kernel choice of the backward for vectorisable shapes (per host thread; HILDA_NORM_RING presets it):
 //   1 (default) automatic: the shared-memory ring (norm_bwd_ring_kernel) when three or more row slots
 //     fit beside the SM's other CTAs, else the register kernel with an L2 bulk prefetch one row ahead.
@@ -601,9 +622,7 @@ static int norm_bwd_t(const void* dy, const void* ds, const void* x, const void*
         NORM_DISPATCH_TV(T, RING_CALL)
 #undef RING_CALL
         HILDA_LAUNCH_CHECK();
-        dw_reduce_kernel<<<(unsigned)((n_cols + 31) / 32), 1024, 0, st>>>(workspace, grid, n_cols, dw, w_dt);
-        HILDA_LAUNCH_CHECK();
-        return HILDA_OK;
+        return launch_dw_reduce(workspace, grid, n_cols, dw, w_dt, st);
       }
     }
 #define BWD_CALL(TT, TH, VP)                                                                               \
@@ -614,9 +633,7 @@ static int norm_bwd_t(const void* dy, const void* ds, const void* x, const void*
 #undef BWD_CALL
   }
   HILDA_LAUNCH_CHECK();
-  dw_reduce_kernel<<<(unsigned)((n_cols + 31) / 32), 1024, 0, st>>>(workspace, grid, n_cols, dw, w_dt);
-  HILDA_LAUNCH_CHECK();
-  return HILDA_OK;
+  return launch_dw_reduce(workspace, grid, n_cols, dw, w_dt, st);
 }
 
 // ---- scratch for the entry point that allocates nothing ------------------------------------

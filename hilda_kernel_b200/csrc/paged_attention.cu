@@ -6,13 +6,10 @@
 // HBM-bound on the KV cache, which is read ONCE per kv head: a warp serves all query heads of one
 // (sequence, kv head) (the reference launches one program per query head and re-reads K / V for
 // every head of a GQA group) over a slice of the context (split-KV: slices are merged by a second
-// small kernel when there is more than one). Two kernels sit behind the entry point:
-//  * the tensor-core kernel (default, second half of this file): q.k and p.v as mma.sync over 16
-//    tokens x up to 8 query heads, K / V staged through shared memory with cp.async;
-//  * the CUDA-core kernel: eight lanes share a token, each loads 16 bytes (16 fp8) of its K row and
-//    its V row, so a warp touches four whole 128-byte rows per load; the dot product is reduced
-//    over the eight lanes with three shuffles; every lane group keeps its own online-softmax state
-//    (max, sum, 16 output dims per head), merged at the end. One FMA per (query head, element).
+// small kernel when there is more than one). q.k and p.v run as mma.sync over 16 tokens x up to 8
+// query heads, K / V staged through shared memory with cp.async. (A CUDA-core formulation, one FMA
+// per query head and element with eight lanes sharing a token, took 87 us where this takes 58 and
+// was removed: it covered no shape this kernel does not.)
 #include <cuda_fp8.h>
 
 #include <cstdlib>
@@ -24,8 +21,6 @@ namespace hilda {
 
 constexpr int PA_HEAD_DIM = 128;
 constexpr int PA_MAX_WARPS = 8;          // head groups (kv head x pass) per CTA, one warp each
-constexpr int PA_TOKENS_PER_STEP = 4;    // tokens a warp takes per step (eight lanes each)
-constexpr int PA_UNROLL = 2;             // steps whose loads are in flight together (4 measured slower)
 constexpr int PA_PARTIAL = PA_HEAD_DIM + 2;  // per (sequence, head, split): m, l, 128 unnormalised sums
 
 struct PaParams {
@@ -41,176 +36,8 @@ struct PaParams {
   int passes;  // tensor-core kernel: passes of up to eight query heads per kv head
 };
 
-// 16 fp8 (e4m3) values in a uint4 -> 8 packed half2 (exact: e4m3 is a subset of fp16).
-__device__ __forceinline__ void fp8x16_to_half2(const uint4& raw, uint32_t* h) {
-  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] & 0xffffu), __NV_E4M3);
-    const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] >> 16), __NV_E4M3);
-    h[2 * i] = *reinterpret_cast<const uint32_t*>(&lo);
-    h[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&hi);
-  }
-}
-// acc += a.lo * b.lo + a.hi * b.hi with fp16 inputs and an fp32 accumulator (mixed-precision FMA:
-// the products of two fp16 values are exact in fp32, so nothing is lost against converting first).
-__device__ __forceinline__ float fma2_f32_f16(uint32_t a, uint32_t b, float acc) {
-  asm("{\n.reg .b16 al, ah, bl, bh;\n"
-      "mov.b32 {al, ah}, %1;\n mov.b32 {bl, bh}, %2;\n"
-      "fma.rn.f32.f16 %0, al, bl, %0;\n"
-      "fma.rn.f32.f16 %0, ah, bh, %0;\n}"
-      : "+f"(acc) : "r"(a), "r"(b));
-  return acc;
-}
-// acc0 += v.lo * p, acc1 += v.hi * p (p an fp16 scalar replicated in both halves of pp).
-__device__ __forceinline__ void fma_pv(uint32_t v, uint32_t pp, float& acc0, float& acc1) {
-  asm("{\n.reg .b16 vl, vh, pl, ph;\n"
-      "mov.b32 {vl, vh}, %2;\n mov.b32 {pl, ph}, %3;\n"
-      "fma.rn.f32.f16 %0, vl, pl, %0;\n"
-      "fma.rn.f32.f16 %1, vh, ph, %1;\n}"
-      : "+f"(acc0), "+f"(acc1) : "r"(v), "r"(pp));
-}
-
-// G query heads of one kv head per pass. Grid (CTAs of head groups, batch, context splits); one
-// WARP per head group (kv head x pass), no cross-warp merge, and all the head groups of a sequence
-// side by side in a CTA, so that the 128-byte rows of the different kv heads of a token (adjacent
-// in the cache) are requested at about the same time. Measured against one CTA of four warps per
-// kv head with a shared-memory merge: 87 instead of 105 us at batch 32 x 4096 tokens; letting one
-// warp cover four adjacent kv heads of a single token (512 contiguous bytes per load) was slower.
-template <int G>
-__global__ void __launch_bounds__(PA_MAX_WARPS * 32, G <= 2 ? 2 : 1)
-paged_attention_fp8_kernel(const PaParams p) {
-  const int passes = p.group / G;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int hg = blockIdx.x * (blockDim.x >> 5) + warp;     // head group of this warp
-  if (hg >= p.n_kv_heads * passes) return;                   // no block-wide barrier below
-  const int kv_head = hg / passes, pass = hg % passes;
-  const int b = blockIdx.y, split = blockIdx.z;
-  const int head0 = kv_head * p.group + pass * G;  // first query head of this warp
-  const int sub = lane >> 3, part = lane & 7;      // token within the step, 16-dim slice
-  int ctx = p.context_lens[b];
-  if (ctx > p.max_blocks * p.block_size) ctx = p.max_blocks * p.block_size;  // never index past the block table
-  const int t_begin = split * p.tokens_per_split;
-  int t_end = t_begin + p.tokens_per_split;
-  if (t_end > ctx) t_end = ctx;
-
-  // q * scale as fp16 pairs: bf16 -> fp16 is exact except below fp16's normal range (|q| < 6e-5,
-  // where the product with a key no longer matters) and the scale is folded in before rounding
-  uint32_t q[G][8];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    const __nv_bfloat16* qp = p.q + (int64_t)b * p.q_sb + (int64_t)(head0 + g) * p.q_sh + part * 16;
-#pragma unroll
-    for (int d = 0; d < 8; ++d) {
-      const __half2 h = __floats2half2_rn(__bfloat162float(qp[2 * d]) * p.scale, __bfloat162float(qp[2 * d + 1]) * p.scale);
-      q[g][d] = *reinterpret_cast<const uint32_t*>(&h);
-    }
-  }
-  float m[G], l[G], acc[G][16];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    m[g] = -INFINITY; l[g] = 0.f;
-#pragma unroll
-    for (int d = 0; d < 16; ++d) acc[g][d] = 0.f;
-  }
-  const int32_t* table = p.block_tables + (int64_t)b * p.bt_sb;
-  // Software pipeline: the loads of the NEXT iteration (PA_UNROLL steps) are issued before this
-  // iteration's values are used, so that every warp always has loads in flight; the kernel is
-  // bound by the bytes it keeps in flight, not by arithmetic.
-  auto load_steps = [&](int t0, uint4* kr, uint4* vr) {
-#pragma unroll
-    for (int u = 0; u < PA_UNROLL; ++u) {
-      const int t = t0 + u * PA_TOKENS_PER_STEP + sub;
-      kr[u] = make_uint4(0, 0, 0, 0); vr[u] = make_uint4(0, 0, 0, 0);
-      if (t < t_end) {
-        const int64_t blk = table[t / p.block_size];
-        const int64_t tok = t % p.block_size;
-        kr[u] = ld16_stream(p.k + blk * p.k_sblk + tok * p.k_stok + (int64_t)kv_head * p.k_sh + part * 16);
-        vr[u] = ld16_stream(p.v + blk * p.v_sblk + tok * p.v_stok + (int64_t)kv_head * p.v_sh + part * 16);
-      }
-    }
-  };
-  constexpr int PA_ITER = PA_TOKENS_PER_STEP * PA_UNROLL;
-  uint4 kraw[PA_UNROLL], vraw[PA_UNROLL], knext[PA_UNROLL], vnext[PA_UNROLL];
-  load_steps(t_begin, kraw, vraw);
-  for (int t0 = t_begin; t0 < t_end; t0 += PA_ITER) {
-    load_steps(t0 + PA_ITER, knext, vnext);  // past t_end: nothing is loaded
-#pragma unroll
-    for (int u = 0; u < PA_UNROLL; ++u) {
-      const bool valid = t0 + u * PA_TOKENS_PER_STEP + sub < t_end;
-      uint32_t kh[8], vh[8];
-      fp8x16_to_half2(kraw[u], kh);
-      fp8x16_to_half2(vraw[u], vh);
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        float s = 0.f;
-#pragma unroll
-        for (int d = 0; d < 8; ++d) s = fma2_f32_f16(q[g][d], kh[d], s);
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        s += __shfl_xor_sync(0xffffffffu, s, 4);
-        if (valid) {  // uniform over the eight lanes of a token
-          if (s > m[g]) {  // a new maximum (rare after the first tokens): rescale what is there
-            const float corr = __expf(m[g] - s);
-            l[g] *= corr;
-#pragma unroll
-            for (int d = 0; d < 16; ++d) acc[g][d] *= corr;
-            m[g] = s;
-          }
-          const float pw = __expf(s - m[g]);
-          l[g] += pw;
-          const __half2 ph = __float2half2_rn(pw);
-          const uint32_t pp = *reinterpret_cast<const uint32_t*>(&ph);
-#pragma unroll
-          for (int d = 0; d < 8; ++d) fma_pv(vh[d], pp, acc[g][2 * d], acc[g][2 * d + 1]);
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < PA_UNROLL; ++u) { kraw[u] = knext[u]; vraw[u] = vnext[u]; }
-  }
-  // merge the four lane groups of the warp (lanes with the same 16-dim slice)
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-#pragma unroll
-    for (int o = 8; o <= 16; o <<= 1) {
-      const float m_o = __shfl_xor_sync(0xffffffffu, m[g], o);
-      const float l_o = __shfl_xor_sync(0xffffffffu, l[g], o);
-      const float m_new = fmaxf(m[g], m_o);
-      const float c_s = m_new == -INFINITY ? 0.f : __expf(m[g] - m_new);
-      const float c_o = m_new == -INFINITY ? 0.f : __expf(m_o - m_new);
-      l[g] = l[g] * c_s + l_o * c_o;
-#pragma unroll
-      for (int d = 0; d < 16; ++d) {
-        const float a_o = __shfl_xor_sync(0xffffffffu, acc[g][d], o);
-        acc[g][d] = acc[g][d] * c_s + a_o * c_o;
-      }
-      m[g] = m_new;
-    }
-  }
-  // lanes 0-7 hold the warp's result for their 16 dims
-  if (sub == 0) {
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const int head = head0 + g;
-      if (p.splits == 1) {
-        const float inv = l[g] > 0.f ? 1.0f / l[g] : 0.f;
-        __nv_bfloat16* dst = p.out + (int64_t)b * p.o_sb + (int64_t)head * p.o_sh + part * 16;
-#pragma unroll
-        for (int d = 0; d < 16; ++d) dst[d] = __float2bfloat16_rn(acc[g][d] * inv);
-      } else {
-        float* dst = p.partial + (((int64_t)b * p.n_heads + head) * p.splits + split) * PA_PARTIAL;
-#pragma unroll
-        for (int d = 0; d < 16; ++d) dst[2 + part * 16 + d] = acc[g][d];
-        if (part == 0) { dst[0] = m[g]; dst[1] = l[g]; }
-      }
-    }
-  }
-}
-
-// ------------------------------------------------------------------------- tensor-core variant
-// The kernel above spends its issue slots on one FMA per (query head, element) for q.k and again
-// for p.v. This variant gives both contractions to mma.sync (m16n8k16, fp16 inputs, fp32
+// ------------------------------------------------------------------------- the kernel
+// Both contractions go to mma.sync (m16n8k16, fp16 inputs, fp32
 // accumulators) with the KV TOKENS in the M dimension and the query heads of the kv head (up to
 // eight per pass) in N, so that a GQA group of any size up to eight costs the same instructions:
 //   S^T [16 tokens x 8 heads] = K [16 tokens x 128] . Q^T          (8 MMAs over 128 dims)
@@ -509,13 +336,7 @@ static void pa_plan(int64_t batch, int64_t n_kv_heads, int64_t passes, int64_t m
   *tokens_per_split = (int)tps;
 }
 
-static int pa_group_unit(int group) { return group % 4 == 0 ? 4 : (group % 2 == 0 ? 2 : 1); }
-constexpr int64_t PA_QUANTUM = PA_TOKENS_PER_STEP * PA_UNROLL;
-
-// 0: CUDA-core kernel, 1: tensor-core kernel, the default (HILDA_PA_PATH, hilda_paged_attention_set_path)
-static int g_pa_path = []() { const char* e = getenv("HILDA_PA_PATH"); return e ? atoi(e) : 1; }();
-
-// Tensor-core kernel: warps per CTA and CTAs per SM (shared memory and the 128-register bound of
+// Warps per CTA and CTAs per SM (shared memory and the 128-register bound of
 // its launch bounds both allow sixteen warps per SM).
 static void pm_shape(int64_t head_groups, int* warps, int* ctas_per_sm) {
   *warps = (int)(head_groups < PA_MAX_WARPS ? head_groups : PA_MAX_WARPS);
@@ -541,11 +362,8 @@ int64_t hilda_paged_attention_fp8_workspace_bytes(int64_t batch, int64_t n_heads
                                                   int64_t block_size) {
   if (batch <= 0 || n_heads <= 0 || n_kv_heads <= 0 || max_blocks <= 0 || block_size <= 0 || n_heads % n_kv_heads) return 256;
   const int group = (int)(n_heads / n_kv_heads);
-  int splits, tps, passes, splits_tc;
-  const int unit = pa_group_unit(group);
-  pa_plan(batch, n_kv_heads, group / unit, max_blocks * block_size, unit <= 2 ? 2 : 1, PA_QUANTUM, &splits, &tps);
-  pm_plan(batch, n_kv_heads, group, max_blocks * block_size, &passes, &splits_tc, &tps);
-  if (splits_tc > splits) splits = splits_tc;  // enough for either kernel
+  int splits, tps, passes;
+  pm_plan(batch, n_kv_heads, group, max_blocks * block_size, &passes, &splits, &tps);
   return splits > 1 ? batch * n_heads * splits * PA_PARTIAL * 4 + 256 : 256;
 }
 
@@ -575,46 +393,21 @@ int hilda_paged_attention_fp8_decode(const void* q, int64_t q_sb, int64_t q_sh, 
   p.scale = scale; p.n_heads = (int)n_heads; p.n_kv_heads = (int)n_kv_heads; p.group = (int)(n_heads / n_kv_heads);
   p.block_size = (int)block_size; p.max_blocks = (int)max_blocks;
   cudaStream_t st = (cudaStream_t)stream;
-  if (g_pa_path == 1) {
-    pm_plan(batch, n_kv_heads, p.group, max_blocks * block_size, &p.passes, &p.splits, &p.tokens_per_split);
-    if (max_blocks == 0) { p.splits = 1; p.tokens_per_split = PM_STEP; }
-    p.partial = nullptr;
-    if (p.splits > 1) {
-      if (!workspace) return HILDA_ERR_NULL;
-      p.partial = reinterpret_cast<float*>(workspace);
-    }
-    const int head_groups = (int)n_kv_heads * p.passes;
-    int warps, ctas;
-    pm_shape(head_groups, &warps, &ctas);
-    const int smem = warps * PM_WARP_SMEM;
-    void (*kern)(const PaParams) = paged_attention_fp8_mma_kernel;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return HILDA_ERR_CUDA;
-    const dim3 grid((unsigned)((head_groups + warps - 1) / warps), (unsigned)batch, (unsigned)p.splits);
-    kern<<<grid, warps * 32, smem, st>>>(p);
-    HILDA_LAUNCH_CHECK();
-    if (p.splits > 1) {
-      paged_attention_merge_kernel<<<dim3((unsigned)n_heads, (unsigned)batch), PA_HEAD_DIM, 0, st>>>(p.partial, p.out, o_sb, o_sh,
-                                                                                                     p.n_heads, p.splits);
-      HILDA_LAUNCH_CHECK();
-    }
-    return HILDA_OK;
-  }
-  const int G = pa_group_unit(p.group);
-  const int passes = p.group / G;
-  p.passes = passes;
-  pa_plan(batch, n_kv_heads, passes, max_blocks * block_size, G <= 2 ? 2 : 1, PA_QUANTUM, &p.splits, &p.tokens_per_split);
-  if (max_blocks == 0) { p.splits = 1; p.tokens_per_split = PA_TOKENS_PER_STEP; }
+  pm_plan(batch, n_kv_heads, p.group, max_blocks * block_size, &p.passes, &p.splits, &p.tokens_per_split);
+  if (max_blocks == 0) { p.splits = 1; p.tokens_per_split = PM_STEP; }
   p.partial = nullptr;
   if (p.splits > 1) {
     if (!workspace) return HILDA_ERR_NULL;
     p.partial = reinterpret_cast<float*>(workspace);
   }
-  const int head_groups = (int)n_kv_heads * passes;
-  const int warps = head_groups < PA_MAX_WARPS ? head_groups : PA_MAX_WARPS;
+  const int head_groups = (int)n_kv_heads * p.passes;
+  int warps, ctas;
+  pm_shape(head_groups, &warps, &ctas);
+  const int smem = warps * PM_WARP_SMEM;
+  void (*kern)(const PaParams) = paged_attention_fp8_mma_kernel;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return HILDA_ERR_CUDA;
   const dim3 grid((unsigned)((head_groups + warps - 1) / warps), (unsigned)batch, (unsigned)p.splits);
-  if (G == 4) paged_attention_fp8_kernel<4><<<grid, warps * 32, 0, st>>>(p);
-  else if (G == 2) paged_attention_fp8_kernel<2><<<grid, warps * 32, 0, st>>>(p);
-  else paged_attention_fp8_kernel<1><<<grid, warps * 32, 0, st>>>(p);
+  kern<<<grid, warps * 32, smem, st>>>(p);
   HILDA_LAUNCH_CHECK();
   if (p.splits > 1) {
     paged_attention_merge_kernel<<<dim3((unsigned)n_heads, (unsigned)batch), PA_HEAD_DIM, 0, st>>>(p.partial, p.out, o_sb, o_sh,
@@ -622,13 +415,6 @@ int hilda_paged_attention_fp8_decode(const void* q, int64_t q_sb, int64_t q_sh, 
     HILDA_LAUNCH_CHECK();
   }
   return HILDA_OK;
-}
-
-// 0: CUDA-core kernel, 1: tensor-core (mma.sync) kernel; returns the previous choice.
-int hilda_paged_attention_set_path(int path) {
-  const int old = g_pa_path;
-  if (path == 0 || path == 1) g_pa_path = path;
-  return old;
 }
 
 }  // extern "C"

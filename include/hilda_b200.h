@@ -328,11 +328,7 @@ int hilda_paged_attention_fp8_decode(const void* q, int64_t q_sb, int64_t q_sh, 
                                      void* workspace, float scale, int64_t batch, int64_t n_heads,
                                      int64_t n_kv_heads, int64_t head_dim, int64_t block_size, int64_t max_blocks,
                                      void* stream);
-/* Kernel behind hilda_paged_attention_fp8_decode: 0 = CUDA-core kernel (one FMA per query head and
- * element), 1 = tensor-core kernel (mma.sync over 16 tokens x up to 8 query heads, K / V staged
- * through shared memory with cp.async). Same results within the rounding of p to fp16; the
- * workspace size covers both. Environment: HILDA_PA_PATH. Returns the previous choice. */
-int hilda_paged_attention_set_path(int path);
+
 
 /* ---- GRPO --------------------------------------------------------------------------------- */
 int64_t hilda_grpo_workspace_bytes(int64_t B);

@@ -107,7 +107,7 @@ def test_kernel_choice_setters_and_split_plan_without_a_gpu():
     slice of the plan; host-side arithmetic only, no launch."""
     import hilda_kernel_b200._lib as L
     lib = L.lib()
-    for setter in (lib.hilda_paged_attention_set_path, lib.hilda_attn_res_set_path):
+    for setter in (lib.hilda_attn_res_set_path,):
         assert setter(-1) == 1          # out of range: unchanged, returns the current choice
         assert setter(0) == 1 and setter(-1) == 0
         assert setter(1) == 0 and setter(-1) == 1

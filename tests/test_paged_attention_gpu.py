@@ -10,15 +10,6 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-@pytest.fixture(params=[0, 1], ids=["cuda_core", "tensor_core"], autouse=True)
-def kernel_path(request):
-    """Every test runs on both kernels behind the entry point (hilda_paged_attention_set_path)."""
-    import hilda_kernel_b200._lib as L
-    old = L.lib().hilda_paged_attention_set_path(request.param)
-    yield request.param
-    L.lib().hilda_paged_attention_set_path(old)
-
-
 def gen(seed):
     return torch.Generator().manual_seed(seed)
 

@@ -608,9 +608,11 @@ def sharded_ops_table(device, world, pk):
         bsz = max(4 // div, 1)
         seq = 4096 if div <= 4 else 4096 * 4 // div
         inv = 1.0 / (500000.0 ** (torch.arange(0, 128, 2, device=device).float() / 128))
-        pos0 = (dist.get_rank() * seq) % 4096 if div > 4 else 0
-        fr = torch.outer(torch.arange(pos0, pos0 + seq, device=device).float(), inv)
+        fr = torch.outer(torch.arange(4096, device=device).float(), inv)
         cos, sin = fr.cos()[None].bfloat16(), fr.sin()[None].bfloat16()
+        if div > 4:  # the sequence axis is split too: this rank's positions
+            cos, sin = P.rope_tables_for_sequence_shard(cos, sin, seq, rank=dist.get_rank() % (4096 // seq), world=4096 // seq)
+            cos, sin = cos.contiguous(), sin.contiguous()
         q = rn(bsz, seq, 32, 128).bfloat16().transpose(1, 2)
         k = rn(bsz, seq, 8, 128).bfloat16().transpose(1, 2)
 

@@ -116,6 +116,19 @@ def allreduce_weight_grad(dW: torch.Tensor, group=None) -> torch.Tensor:
     return buf.to(dW.dtype)
 
 
+def rope_tables_for_sequence_shard(cos, sin, seq_local, rank=None, world=None, group=None):
+    """RoPE with the SEQUENCE axis split over ranks (long context): rank r holds positions
+    [r * seq_local, (r + 1) * seq_local), so it rotates with that slice of the half-width tables
+    (..., seq_total, head_dim / 2). Returns views (no copy); the operator itself needs no exchange."""
+    w, r = _world(group)
+    world = w if world is None else world
+    rank = r if rank is None else rank
+    p0, p1 = rank * seq_local, (rank + 1) * seq_local
+    if p1 > cos.shape[-2] or world * seq_local > cos.shape[-2]:
+        raise ValueError(f"tables cover {cos.shape[-2]} positions, the {world} shards of {seq_local} need {world * seq_local}")
+    return cos[..., p0:p1, :], sin[..., p0:p1, :]
+
+
 def sharded_cross_entropy(logits_local, targets_local, ignore_index=-100, group=None):
     """Mean cross entropy over ALL ranks' rows; each rank holds a row shard. Returns (loss,
     dlogits_local). The valid-row count is all-reduced first (one int), so the kernel writes the

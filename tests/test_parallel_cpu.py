@@ -30,6 +30,24 @@ def test_shard_bounds_cover_and_align():
         shard_bounds(10, 2, 2)
 
 
+def test_rope_tables_for_sequence_shard_are_the_positions_of_the_shard():
+    from hilda_kernel_b200.parallel import rope_tables_for_sequence_shard
+    from oracle import reference_ops as R
+    cos, sin = R.rope_tables(64, 16)
+    q = torch.randn(2, 3, 64, 16, generator=torch.Generator().manual_seed(3))
+    k = torch.randn(2, 1, 64, 16, generator=torch.Generator().manual_seed(4))
+    q_full, k_full = R.rope(q, k, cos, sin)
+    for world in (1, 2, 4):
+        n = 64 // world
+        for rank in range(world):
+            c, s_ = rope_tables_for_sequence_shard(cos, sin, n, rank=rank, world=world)
+            assert c.shape == (1, n, 8) and c.data_ptr() == cos[:, rank * n:].data_ptr()
+            q_r, k_r = R.rope(q[:, :, rank * n:(rank + 1) * n], k[:, :, rank * n:(rank + 1) * n], c, s_)
+            assert torch.equal(q_r, q_full[:, :, rank * n:(rank + 1) * n]) and torch.equal(k_r, k_full[:, :, rank * n:(rank + 1) * n])
+    with pytest.raises(ValueError):
+        rope_tables_for_sequence_shard(cos, sin, 40, rank=1, world=2)
+
+
 def _shard_stats(logits, targets, v0, v1):
     x = logits[:, v0:v1]
     m = x.max(dim=1).values

@@ -334,6 +334,13 @@ def per_op_table(device, pk, only=None, small=False):
                    [(lambda q=q, k=k: RP.rope_backward(q, k, cos, sin)) for q, k in sets]),
             4 * (4 * 4096 * 40 * 128) * 2, 16384)
         del sets
+        # the same tensors in the reference bench script's own memory order, contiguous (B,H,S,D)
+        sets = [(rn(4, 32, 4096, 128).bfloat16(), rn(4, 8, 4096, 128).bfloat16()) for _ in range(4)]
+        add("rope_bf16_bhsd_fwd+bwd",
+            timed2([(lambda q=q, k=k: RP.rope_forward(q, k, cos, sin, inplace=True)) for q, k in sets],
+                   [(lambda q=q, k=k: RP.rope_backward(q, k, cos, sin)) for q, k in sets]),
+            4 * (4 * 4096 * 40 * 128) * 2, 16384)
+        del sets
     # config 2c: SwiGLU bf16 [16384, 14336] fwd+bwd (3 + 5 passes)
     if want("swiglu"):
         nr = 16384 // div

@@ -161,7 +161,7 @@ def op_fused_add_rms_norm(ref, g):
     return "fused_add_rms_norm_bf16_fwd+bwd", out
 
 
-def op_rope(ref, g):
+def op_rope(ref, g, bhsd=False):
     out = {}
     inv = 1.0 / (500000.0 ** (torch.arange(0, 128, 2, device=DEV).float() / 128))
     fr = torch.outer(torch.arange(4096, device=DEV).float(), inv)
@@ -169,8 +169,12 @@ def op_rope(ref, g):
     cos_full, sin_full = torch.cat([cos, cos], -1), torch.cat([sin, sin], -1)
     sets = []
     for _ in range(4):
-        q = rn(g, 4, 4096, 32, 128).bfloat16().transpose(1, 2).requires_grad_(True)
-        k = rn(g, 4, 4096, 8, 128).bfloat16().transpose(1, 2).requires_grad_(True)
+        if bhsd:  # the reference bench script's own memory order
+            q = rn(g, 4, 32, 4096, 128).bfloat16().requires_grad_(True)
+            k = rn(g, 4, 8, 4096, 128).bfloat16().requires_grad_(True)
+        else:
+            q = rn(g, 4, 4096, 32, 128).bfloat16().transpose(1, 2).requires_grad_(True)
+            k = rn(g, 4, 4096, 8, 128).bfloat16().transpose(1, 2).requires_grad_(True)
         sets.append((q, k, torch.randn_like(q), torch.randn_like(k)))
 
     def mk(fn):
@@ -194,7 +198,11 @@ def op_rope(ref, g):
         c, s = cos_full[:, None], sin_full[:, None]
         return q * c + rot(q) * s, k * c + rot(k) * s
     measure(out, "eager", mk(eager))
-    return "rope_bf16_fwd+bwd", out
+    return ("rope_bf16_bhsd_fwd+bwd" if bhsd else "rope_bf16_fwd+bwd"), out
+
+
+def op_rope_bhsd(ref, g):
+    return op_rope(ref, g, bhsd=True)
 
 
 def op_swiglu(ref, g):
@@ -300,7 +308,7 @@ def op_flce(ref, g):
     return "fused_linear_cross_entropy_bf16_fwd+bwd", out
 
 
-OPS = {"rms_norm": op_rms_norm, "fused_add_rms_norm": op_fused_add_rms_norm, "rope": op_rope, "swiglu": op_swiglu,
+OPS = {"rms_norm": op_rms_norm, "fused_add_rms_norm": op_fused_add_rms_norm, "rope": op_rope, "rope_bhsd": op_rope_bhsd, "swiglu": op_swiglu,
        "cross_entropy": op_cross_entropy, "fused_linear_cross_entropy": op_flce, "grpo": op_grpo}
 
 

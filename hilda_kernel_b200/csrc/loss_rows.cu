@@ -13,14 +13,14 @@
 
 namespace hilda {
 
-int g_row_force_nv = 0, g_row_force_cluster = 0;
+int g_row_force_nv = 0, g_row_force_cluster = 0, g_row_force_ns = 0;
 
-// Tuning runs may preset the plan through the environment: HILDA_ROW_ENGINE="nv,cluster".
+// Tuning runs may preset the plan through the environment: HILDA_ROW_ENGINE="nv,cluster[,ns]".
 static const bool g_row_env_applied = []() {
   const char* e = getenv("HILDA_ROW_ENGINE");
   if (e) {
-    int a = 0, b = 0;
-    if (sscanf(e, "%d,%d", &a, &b) == 2) { g_row_force_nv = a; g_row_force_cluster = b; }
+    int a = 0, b = 0, c = 0;
+    if (sscanf(e, "%d,%d,%d", &a, &b, &c) >= 2) { g_row_force_nv = a; g_row_force_cluster = b; g_row_force_ns = c; }
   }
   return true;
 }();
@@ -232,8 +232,11 @@ using namespace hilda;
 
 extern "C" {
 
-// Tuning hook: force (vectors per thread, cluster size) of the row engine; (0,0) restores automatic.
-void hilda_row_engine_force(int nv, int cluster) { g_row_force_nv = nv; g_row_force_cluster = cluster; }
+// Tuning hook: force (register vectors per thread, cluster size, shared-memory vectors per thread) of the
+// row engine; (0,0,0) restores automatic.
+void hilda_row_engine_force(int nv, int cluster, int ns) {
+  g_row_force_nv = nv; g_row_force_cluster = cluster; g_row_force_ns = ns;
+}
 int64_t hilda_cross_entropy_workspace_bytes(int64_t n_rows) { return 16 + (n_rows > 0 ? n_rows : 0) * 4; }
 
 // workspace layout: int n_valid at byte 0, int status at byte 8, float loss_rows[n_rows] at byte 16 (only used when the

@@ -47,6 +47,13 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+__device__ __forceinline__ void row_cp_async16(void* smem_dst, const void* gsrc) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void row_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void row_cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 
@@ -159,10 +166,18 @@ constexpr int row_min_blocks(int threads, int nv) {
   return nv <= 10 ? (threads <= 256 ? 4 : (threads <= 320 ? 3 : 2)) : 2;
 }
 
-template <typename T, int ROW_THREADS, int NV, int CLUSTER, class Op>
+//
+// NS > 0: besides its NV register vectors a thread owns NS more vectors of the row in dynamic shared
+// memory (slot [j][tid], private to the thread, filled by 16-byte cp.async): the register file limits
+// a CTA to NV vectors per thread at four CTAs per SM, the idle shared memory holds the rest, so a row
+// needs a smaller cluster, more bytes are in flight per SM, and the per-row fixed work (reductions,
+// cluster exchange, loss terms) is spread over more elements per thread.
+template <typename T, int ROW_THREADS, int NV, int CLUSTER, class Op, int NS = 0>
 __global__ void __launch_bounds__(ROW_THREADS, row_min_blocks(ROW_THREADS, NV))
 row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V, Op op, int* __restrict__ status) {
   constexpr int VEC = VT<T>::N;
+  extern __shared__ __align__(16) unsigned char row_stage_raw[];
+  uint4* const stage = reinterpret_cast<uint4*>(row_stage_raw) + threadIdx.x;  // slot j at stage[j * ROW_THREADS]
 #if ROW_WARP_LOCAL
   __shared__ float wpair[2 * (ROW_THREADS / 32)];  // per warp: (max in the log2 domain, sum of 2^(x - max))
 #else
@@ -209,6 +224,14 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
     if (i < full) xv[i] = ld16_stream(src + i * ROW_THREADS);
     else xv[i] = (tid + i * ROW_THREADS < my_vec) ? ld16_stream(src + i * ROW_THREADS) : neg_inf_vec<T>();
   }
+  if constexpr (NS > 0) {
+#pragma unroll
+    for (int j = 0; j < NS; ++j) {
+      if (tid + (NV + j) * ROW_THREADS < my_vec) row_cp_async16(stage + j * ROW_THREADS, src + (NV + j) * ROW_THREADS);
+      else stage[j * ROW_THREADS] = neg_inf_vec<T>();
+    }
+    row_cp_async_commit();
+  }
   const float inv_t = op.inv_temperature();
   const float k = inv_t * LOG2E;  // logits -> log2 domain
   float x_t = 0.f;
@@ -223,6 +246,11 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
   typename RowMath<T>::MaxAcc macc = RowMath<T>::max_init();
 #pragma unroll
   for (int i = 0; i < NV; ++i) RowMath<T>::vmax(macc, xv[i]);
+  if constexpr (NS > 0) {
+    row_cp_async_wait_all();  // the thread reads only the slots it filled itself
+#pragma unroll
+    for (int j = 0; j < NS; ++j) RowMath<T>::vmax(macc, stage[j * ROW_THREADS]);
+  }
   const float m_w = warp_max(RowMath<T>::max_final(macc)) * k;
   const float m_safe = (m_w == -INFINITY) ? 0.f : m_w;
   // pass 2: e = 2^(x*k - m_w) summed in fp32, and kept IN PLACE of x (rounded to T): the gradient
@@ -234,6 +262,14 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
     opaque(xv[i]);
     s += vec_exp_inplace<T>(xv[i], k, m_safe);
     opaque(xv[i]);  // orders the iterations: at most one vector is unpacked to fp32 at a time
+  }
+  if constexpr (NS > 0) {
+#pragma unroll
+    for (int j = 0; j < NS; ++j) {
+      uint4 v = stage[j * ROW_THREADS];
+      s += vec_exp_inplace<T>(v, k, m_safe);
+      stage[j * ROW_THREADS] = v;
+    }
   }
   s = warp_sum(s);
   // the warps' (max, sum) pairs -> the CTA's pair, computed by every thread (fixed order)
@@ -249,6 +285,7 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
   if (m == -INFINITY) s = 0.f;
 
 #else
+  static_assert(NS == 0, "shared-memory vectors need the warp-local variant");
   // pass 1: max of the raw logits (k > 0, so the scale is applied once to the maximum)
   typename RowMath<T>::MaxAcc macc = RowMath<T>::max_init();
 #pragma unroll
@@ -298,6 +335,14 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
   for (int i = 0; i < NV; ++i) {
     RowMath<T>::scale(xv[i], pc);
     if (i < full || tid + i * ROW_THREADS < my_vec) st16_stream(dst + i * ROW_THREADS, xv[i]);
+  }
+  if constexpr (NS > 0) {
+#pragma unroll
+    for (int j = 0; j < NS; ++j) {
+      uint4 v = stage[j * ROW_THREADS];
+      RowMath<T>::scale(v, pc);
+      if (tid + (NV + j) * ROW_THREADS < my_vec) st16_stream(dst + (NV + j) * ROW_THREADS, v);
+    }
   }
   // The target column gets alpha*softmax + beta: the thread that stored its vector overwrites that
   // one element afterwards (same thread, same address: program order holds).
@@ -350,44 +395,62 @@ row_softmax_generic_kernel(const T* __restrict__ logits, T* __restrict__ grad, i
   }
 }
 
-struct RowPlan { int threads; int nv; int cluster; bool generic; };
+struct RowPlan { int threads; int nv; int cluster; bool generic; int ns; };
 
-// Pick (threads, vectors per thread, cluster size) so that cluster * threads * nv vectors cover the
-// row with as few idle slots as possible. force_nv may carry the thread count as threads*100 + nv.
-static inline RowPlan plan_row(int64_t V, int vec, bool aligned, int force_nv, int force_cluster) {
-  RowPlan p{ROW_THREADS_DEFAULT, 0, 1, true};
+// Pick (threads, register vectors and shared-memory vectors per thread, cluster size). Rows of up to
+// 2048 vectors stay in the registers of one CTA. Longer rows take the smallest cluster of 1, 2, 4 or 8
+// CTAs whose threads then hold at most 19 vectors each, 8 or 10 of them in registers and the rest in
+// shared memory. Measured on B200 (CrossEntropy, bf16, every row active, TB/s of read + write) against
+// the register-only plans with twice the cluster size: V = 32000: 6.59 against 5.90; 65536: 6.27 against
+// 5.74; 128256: 6.30 against 5.67; 151936: 6.27 against 5.76. More than 9 shared-memory vectors (36 KB per
+// CTA, four CTAs per SM) was slower than none: the carve-out then leaves the L1 too small for the register
+// loads in flight (11 vectors 5.56, 12 vectors 5.50 at V = 151936; 8 vectors with the largest carve-out
+// forced 5.63 at V = 128256 against 6.30 with the default one).
+// force_nv may carry the thread count as threads*100 + nv.
+static inline RowPlan plan_row(int64_t V, int vec, bool aligned, int force_nv, int force_cluster, int force_ns) {
+  RowPlan p{ROW_THREADS_DEFAULT, 0, 1, true, 0};
   if (!aligned || V % vec != 0 || V / vec > 0x7fffffff) return p;
   const int64_t n_vec = V / vec;
   if (force_nv > 0 && force_cluster > 0) {
     const int th = force_nv >= 100 ? force_nv / 100 : ROW_THREADS_DEFAULT;
     const int nv = force_nv % 100;
-    if ((int64_t)nv * force_cluster * th >= n_vec) { p.threads = th; p.nv = nv; p.cluster = force_cluster; p.generic = false; }
+    if ((int64_t)(nv + force_ns) * force_cluster * th >= n_vec) {
+      p.threads = th; p.nv = nv; p.cluster = force_cluster; p.ns = force_ns; p.generic = false;
+    }
     return p;
   }
   const int64_t per = ROW_THREADS_DEFAULT;
-  if (n_vec <= per * 1) { p.nv = 1; }
-  else if (n_vec <= per * 2) { p.nv = 2; }
-  else if (n_vec <= per * 4) { p.nv = 4; }
-  else if (n_vec <= per * 8) { p.nv = 8; }
-  else if (n_vec <= per * 8 * 2) { p.nv = 8; p.cluster = 2; }
-  else if (n_vec <= per * 8 * 4) { p.nv = 8; p.cluster = 4; }
-  else if (n_vec <= per * 8 * 8) { p.nv = 8; p.cluster = 8; }
-  else if (n_vec <= per * 10 * 8) { p.nv = 10; p.cluster = 8; }
-  else if (n_vec <= 320 * 8 * 8) { p.threads = 320; p.nv = 8; p.cluster = 8; }
-  else if (n_vec <= 384 * 8 * 8) { p.threads = 384; p.nv = 8; p.cluster = 8; }
-  else if (n_vec <= 512 * 8 * 8) { p.threads = 512; p.nv = 8; p.cluster = 8; }
-  else return p;
-  p.generic = false;
+  if (n_vec <= per * 8) {
+    p.nv = n_vec <= per ? 1 : (n_vec <= per * 2 ? 2 : (n_vec <= per * 4 ? 4 : 8));
+    p.generic = false;
+    return p;
+  }
+  for (int th = ROW_THREADS_DEFAULT; th <= 512; th *= 2) {
+    for (int c = (th == ROW_THREADS_DEFAULT ? 1 : 8); c <= 8; c *= 2) {
+      const int64_t slots = (n_vec + (int64_t)th * c - 1) / ((int64_t)th * c);
+      if (slots > 19) continue;
+      p.threads = th; p.cluster = c; p.generic = false;
+      if (th == 512 || slots > 16) { p.nv = 10; p.ns = 9; }
+      else if (slots > 12) { p.nv = 8; p.ns = 8; }
+      else { p.nv = 8; p.ns = 4; }
+      return p;
+    }
+  }
   return p;
 }
 
-template <typename T, int THREADS, int NV, int CLUSTER, class Op>
+template <typename T, int THREADS, int NV, int CLUSTER, class Op, int NS = 0>
 static int launch_row_cfg(const T* logits, T* grad, int64_t n_rows, int64_t V, const Op& op, int* status, cudaStream_t st) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(n_rows * CLUSTER), 1, 1);
   cfg.blockDim = dim3(THREADS, 1, 1);
-  cfg.dynamicSmemBytes = 0;
+  cfg.dynamicSmemBytes = (size_t)NS * THREADS * sizeof(uint4);
   cfg.stream = st;
+  if (NS * THREADS * sizeof(uint4) + 1024 > 48 * 1024) {  // static shared memory counts toward the 48 KB default
+    if (cudaFuncSetAttribute(row_softmax_kernel<T, THREADS, NV, CLUSTER, Op, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)(NS * THREADS * sizeof(uint4))) != cudaSuccess)
+      return HILDA_ERR_CUDA;
+  }
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CLUSTER;
@@ -395,12 +458,12 @@ static int launch_row_cfg(const T* logits, T* grad, int64_t n_rows, int64_t V, c
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, row_softmax_kernel<T, THREADS, NV, CLUSTER, Op>, logits, grad, V, op, status);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, row_softmax_kernel<T, THREADS, NV, CLUSTER, Op, NS>, logits, grad, V, op, status);
   return e == cudaSuccess ? HILDA_OK : HILDA_ERR_CUDA;
 }
 
 // Process-wide override of the plan, for tuning runs (0 = automatic).
-extern int g_row_force_nv, g_row_force_cluster;
+extern int g_row_force_nv, g_row_force_cluster, g_row_force_ns;
 
 template <typename T, class Op>
 static int launch_rows(const void* logits_v, void* grad_v, int64_t n_rows, int64_t V, const Op& op, int* status,
@@ -410,18 +473,23 @@ static int launch_rows(const void* logits_v, void* grad_v, int64_t n_rows, int64
   if (n_rows == 0) return HILDA_OK;
   if (n_rows * 8 > 0x7fffffffLL) return HILDA_ERR_SIZE;
   const bool al = aligned16(logits) && (!grad || aligned16(grad)) && op.rows_aligned(V, VT<T>::N);
-  const RowPlan p = plan_row(V, VT<T>::N, al, g_row_force_nv, g_row_force_cluster);
+  const RowPlan p = plan_row(V, VT<T>::N, al, g_row_force_nv, g_row_force_cluster, g_row_force_ns);
   if (p.generic) {
     row_softmax_generic_kernel<T, Op><<<(unsigned)n_rows, 512, 0, st>>>(logits, grad, V, op, status);
     HILDA_LAUNCH_CHECK();
     return HILDA_OK;
   }
-#define ROW_CFG(TH_, NV_, CL_) \
-  if (p.threads == TH_ && p.nv == NV_ && p.cluster == CL_)  \
-    return launch_row_cfg<T, TH_, NV_, CL_, Op>(logits, grad, n_rows, V, op, status, st);
-  ROW_CFG(256, 1, 1) ROW_CFG(256, 2, 1) ROW_CFG(256, 4, 1) ROW_CFG(256, 8, 1) ROW_CFG(256, 8, 2) ROW_CFG(256, 8, 4)
-  ROW_CFG(256, 8, 8) ROW_CFG(256, 10, 8) ROW_CFG(256, 12, 8) ROW_CFG(256, 16, 8) ROW_CFG(256, 16, 4)
-  ROW_CFG(256, 16, 2) ROW_CFG(320, 8, 8) ROW_CFG(384, 8, 8) ROW_CFG(512, 8, 8) ROW_CFG(512, 4, 8)
+#define ROW_CFG(TH_, NV_, CL_, NS_) \
+  if (p.threads == TH_ && p.nv == NV_ && p.cluster == CL_ && p.ns == NS_)  \
+    return launch_row_cfg<T, TH_, NV_, CL_, Op, NS_>(logits, grad, n_rows, V, op, status, st);
+  ROW_CFG(256, 1, 1, 0) ROW_CFG(256, 2, 1, 0) ROW_CFG(256, 4, 1, 0) ROW_CFG(256, 8, 1, 0)
+  ROW_CFG(256, 8, 1, 4) ROW_CFG(256, 8, 1, 8) ROW_CFG(256, 10, 1, 9)
+  ROW_CFG(256, 8, 2, 4) ROW_CFG(256, 8, 2, 8) ROW_CFG(256, 10, 2, 9)
+  ROW_CFG(256, 8, 4, 4) ROW_CFG(256, 8, 4, 8) ROW_CFG(256, 10, 4, 9)
+  ROW_CFG(256, 8, 8, 4) ROW_CFG(256, 8, 8, 8) ROW_CFG(256, 10, 8, 9)
+  ROW_CFG(512, 10, 8, 9)
+  // the register-only cluster plans the shared-memory ones replaced, kept for comparisons through the override
+  ROW_CFG(256, 8, 8, 0) ROW_CFG(256, 10, 8, 0)
 #undef ROW_CFG
   return HILDA_ERR_SIZE;
 }

@@ -349,9 +349,10 @@ int hilda_grpo_loss_fwd(const void* logits, const int64_t* ids, const float* adv
 int hilda_selective_log_softmax(const void* logits, const int64_t* ids, const float* mask, float* logp,
                                 int64_t B, int64_t L, int64_t V, float temperature, int dtype, void* stream);
 
-/* Tuning hook for the row engine behind CrossEntropy/GRPO: force (vectors per thread, CTAs per
- * cluster); (0, 0) restores the automatic plan. No counterpart in the reference. */
-void hilda_row_engine_force(int nv, int cluster);
+/* Tuning hook for the row engine behind CrossEntropy/GRPO: force (register vectors per thread, CTAs
+ * per cluster, shared-memory vectors per thread); (0, 0, 0) restores the automatic plan. No counterpart
+ * in the reference. */
+void hilda_row_engine_force(int nv, int cluster, int ns);
 
 #ifdef __cplusplus
 }

@@ -14,6 +14,7 @@
 namespace hilda {
 
 int g_row_force_nv = 0, g_row_force_cluster = 0, g_row_force_ns = 0;
+int g_row_cluster_policy = 2;
 
 // Tuning runs may preset the plan through the environment: HILDA_ROW_ENGINE="nv,cluster[,ns]".
 static const bool g_row_env_applied = []() {
@@ -22,6 +23,7 @@ static const bool g_row_env_applied = []() {
     int a = 0, b = 0, c = 0;
     if (sscanf(e, "%d,%d,%d", &a, &b, &c) >= 2) { g_row_force_nv = a; g_row_force_cluster = b; g_row_force_ns = c; }
   }
+  if (const char* pol = getenv("HILDA_ROW_POLICY")) g_row_cluster_policy = atoi(pol);
   return true;
 }();
 

@@ -157,6 +157,9 @@ __device__ __forceinline__ float vec_exp_inplace(uint4& v, float k, float m) {
 #ifndef ROW_FULL_FAST
 #define ROW_FULL_FAST 0    // 1: vectors every thread holds are loaded / stored without a bounds test
 #endif
+#ifndef ROW_ARRIVE_SPLIT
+#define ROW_ARRIVE_SPLIT 1  // 1: only the warp that wrote to the peers arrives with release (651 / 774 us against 673 / 800)
+#endif
 constexpr int ROW_THREADS_DEFAULT = 256;
 constexpr int ROW_STATUS_TARGET_RANGE = 31;  // status word: a target / token id outside [0, V)
 
@@ -312,7 +315,12 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
       st_cluster_f32(remote + 8u * rank, m);
       st_cluster_f32(remote + 8u * rank + 4u, s);
     }
+    // only warp 0 stored anything a peer must see: the other warps arrive without the release fence
+#if ROW_ARRIVE_SPLIT
+    if (tid < 32) cluster_arrive_release(); else cluster_arrive_relaxed();
+#else
     cluster_arrive_release();
+#endif
     cluster_wait_acquire();
     M = -INFINITY;
 #pragma unroll
@@ -431,13 +439,19 @@ static inline RowPlan plan_row(int64_t V, int vec, bool aligned, int force_nv, i
       if (slots > 19) continue;
       p.threads = th; p.cluster = c; p.generic = false;
       if (th == 512 || slots > 16) { p.nv = 10; p.ns = 9; }
-      else if (slots > 12) { p.nv = 8; p.ns = 8; }
+      else if (slots > 14) { p.nv = 8; p.ns = 8; }
+      else if (slots > 12) { p.nv = 8; p.ns = 6; }
       else { p.nv = 8; p.ns = 4; }
       return p;
     }
   }
   return p;
 }
+
+// Cluster scheduling preference: 0 the driver's default, 1 spread, 2 load balancing (the default here; HILDA_ROW_POLICY
+// presets it). Measured on B200, CrossEntropy bf16 [8192,128256] / [8192,151936], every row active: 644.9 / 770.7 us
+// with load balancing, 651 / 774 with the default or spread.
+extern int g_row_cluster_policy;
 
 template <typename T, int THREADS, int NV, int CLUSTER, class Op, int NS = 0>
 static int launch_row_cfg(const T* logits, T* grad, int64_t n_rows, int64_t V, const Op& op, int* status, cudaStream_t st) {
@@ -451,13 +465,19 @@ static int launch_row_cfg(const T* logits, T* grad, int64_t n_rows, int64_t V, c
                              (int)(NS * THREADS * sizeof(uint4))) != cudaSuccess)
       return HILDA_ERR_CUDA;
   }
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CLUSTER;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (g_row_cluster_policy > 0 && CLUSTER > 1) {
+    attr[1].id = cudaLaunchAttributeClusterSchedulingPolicyPreference;
+    attr[1].val.clusterSchedulingPolicyPreference =
+        g_row_cluster_policy == 1 ? cudaClusterSchedulingPolicySpread : cudaClusterSchedulingPolicyLoadBalancing;
+    cfg.numAttrs = 2;
+  }
   cudaError_t e = cudaLaunchKernelEx(&cfg, row_softmax_kernel<T, THREADS, NV, CLUSTER, Op, NS>, logits, grad, V, op, status);
   return e == cudaSuccess ? HILDA_OK : HILDA_ERR_CUDA;
 }
@@ -483,10 +503,10 @@ static int launch_rows(const void* logits_v, void* grad_v, int64_t n_rows, int64
   if (p.threads == TH_ && p.nv == NV_ && p.cluster == CL_ && p.ns == NS_)  \
     return launch_row_cfg<T, TH_, NV_, CL_, Op, NS_>(logits, grad, n_rows, V, op, status, st);
   ROW_CFG(256, 1, 1, 0) ROW_CFG(256, 2, 1, 0) ROW_CFG(256, 4, 1, 0) ROW_CFG(256, 8, 1, 0)
-  ROW_CFG(256, 8, 1, 4) ROW_CFG(256, 8, 1, 8) ROW_CFG(256, 10, 1, 9)
-  ROW_CFG(256, 8, 2, 4) ROW_CFG(256, 8, 2, 8) ROW_CFG(256, 10, 2, 9)
-  ROW_CFG(256, 8, 4, 4) ROW_CFG(256, 8, 4, 8) ROW_CFG(256, 10, 4, 9)
-  ROW_CFG(256, 8, 8, 4) ROW_CFG(256, 8, 8, 8) ROW_CFG(256, 10, 8, 9)
+  ROW_CFG(256, 8, 1, 4) ROW_CFG(256, 8, 1, 6) ROW_CFG(256, 8, 1, 8) ROW_CFG(256, 10, 1, 9)
+  ROW_CFG(256, 8, 2, 4) ROW_CFG(256, 8, 2, 6) ROW_CFG(256, 8, 2, 8) ROW_CFG(256, 10, 2, 9)
+  ROW_CFG(256, 8, 4, 4) ROW_CFG(256, 8, 4, 6) ROW_CFG(256, 8, 4, 8) ROW_CFG(256, 10, 4, 9)
+  ROW_CFG(256, 8, 8, 4) ROW_CFG(256, 8, 8, 6) ROW_CFG(256, 8, 8, 8) ROW_CFG(256, 10, 8, 9)
   ROW_CFG(512, 10, 8, 9)
   // the register-only cluster plans the shared-memory ones replaced, kept for comparisons through the override
   ROW_CFG(256, 8, 8, 0) ROW_CFG(256, 10, 8, 0)

@@ -384,7 +384,8 @@ def _ce_inputs(n, v, dtype, ignore_frac=0.1, seed=7):
 @pytest.mark.parametrize("nv", [(64, 32000), (32, 128256), (64, 4096), (16, 151936), (40, 1000), (9, 50257), (3, 7),
                                 (5, 200000), (4, 300000),
                                 # one vocabulary per remaining (cluster, register + shared-memory vectors) plan
-                                (6, 20000), (6, 36000), (6, 40000), (4, 65536), (4, 73728), (4, 81920)])
+                                (6, 20000), (6, 28000), (6, 36000), (6, 40000), (6, 50304), (4, 65536), (4, 73728), (4, 81920),
+                                (4, 102400)])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
 def test_cross_entropy(nv, dtype, reduction):
@@ -448,7 +449,7 @@ def test_cross_entropy_golden_and_edges(golden):
     lr = logits.float().clone().requires_grad_(True)
     R.cross_entropy_clamped(lr, targets).backward()
     try:
-        for nv_, cl, ns_ in [(8, 1, 0), (8, 8, 0), (10, 8, 0), (8, 1, 4), (8, 1, 8), (10, 1, 9), (8, 2, 4), (8, 2, 8),
+        for nv_, cl, ns_ in [(8, 1, 0), (8, 8, 0), (10, 8, 0), (8, 1, 4), (8, 1, 6), (8, 2, 6), (8, 4, 6), (8, 8, 6), (8, 1, 8), (10, 1, 9), (8, 2, 4), (8, 2, 8),
                              (10, 2, 9), (8, 4, 4), (8, 4, 8), (10, 4, 9), (8, 8, 4), (8, 8, 8), (10, 8, 9), (51210, 8, 9)]:
             L.lib().hilda_row_engine_force(nv_, cl, ns_)
             ld = logits.to(DEV).requires_grad_(True)

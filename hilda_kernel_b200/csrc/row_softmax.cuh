@@ -2,11 +2,11 @@
 //
 // A vocabulary row (128K-152K logits, 256-304 KB in bf16) does not fit one SM's registers or
 // shared memory, so a row is owned by a thread-block CLUSTER: each of the CLUSTER CTAs (on
-// different SMs) loads a contiguous slice of the row into registers with 128-bit loads, reduces
-// its own (max, sum-exp) pair, and the pairs are exchanged through distributed shared memory
-// with a single cluster barrier. Every CTA then knows the row's logsumexp and writes the
-// gradient of its slice straight from registers. HBM traffic is therefore exactly one read of
-// the row and one write of the gradient row.
+// different SMs) loads a contiguous slice of the row with 128-bit loads, part of it into registers
+// and part into thread-private slots of shared memory, reduces its own (max, sum-exp) pair, and the
+// pairs are exchanged through distributed shared memory with a single cluster barrier. Every CTA
+// then knows the row's logsumexp and writes the gradient of its slice straight from where it holds
+// it. HBM traffic is therefore exactly one read of the row and one write of the gradient row.
 //
 // The per-row "Op" supplies: which rows are active, the target column, 1/temperature, and how
 // the per-row scalars (loss, kl, ...) and the gradient coefficients follow from (lse, x_target):

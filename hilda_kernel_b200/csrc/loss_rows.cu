@@ -13,19 +13,24 @@
 
 namespace hilda {
 
-int g_row_force_nv = 0, g_row_force_cluster = 0, g_row_force_ns = 0;
-int g_row_cluster_policy = 2;
-
-// Tuning runs may preset the plan through the environment: HILDA_ROW_ENGINE="nv,cluster[,ns]".
-static const bool g_row_env_applied = []() {
-  const char* e = getenv("HILDA_ROW_ENGINE");
-  if (e) {
-    int a = 0, b = 0, c = 0;
-    if (sscanf(e, "%d,%d,%d", &a, &b, &c) >= 2) { g_row_force_nv = a; g_row_force_cluster = b; g_row_force_ns = c; }
-  }
-  if (const char* pol = getenv("HILDA_ROW_POLICY")) g_row_cluster_policy = atoi(pol);
-  return true;
-}();
+// Plan override and cluster scheduling preference of the row engine: per host thread, so that threads
+// driving different GPUs do not disturb each other. Tuning runs may preset them through the environment
+// (read once): HILDA_ROW_ENGINE="nv,cluster[,ns]", HILDA_ROW_POLICY=0|1|2.
+struct RowEnv { int nv = 0, cluster = 0, ns = 0, policy = 2; };
+static const RowEnv& row_env() {
+  static const RowEnv env = []() {
+    RowEnv r;
+    if (const char* e = getenv("HILDA_ROW_ENGINE")) {
+      int a = 0, b = 0, c = 0;
+      if (sscanf(e, "%d,%d,%d", &a, &b, &c) >= 2) { r.nv = a; r.cluster = b; r.ns = c; }
+    }
+    if (const char* pol = getenv("HILDA_ROW_POLICY")) r.policy = atoi(pol);
+    return r;
+  }();
+  return env;
+}
+thread_local int g_row_force_nv = row_env().nv, g_row_force_cluster = row_env().cluster, g_row_force_ns = row_env().ns;
+thread_local int g_row_cluster_policy = row_env().policy;
 
 // ---------------------------------------------------------------- CrossEntropy
 struct CEOp {

@@ -451,7 +451,7 @@ static inline RowPlan plan_row(int64_t V, int vec, bool aligned, int force_nv, i
 // Cluster scheduling preference: 0 the driver's default, 1 spread, 2 load balancing (the default here; HILDA_ROW_POLICY
 // presets it). Measured on B200, CrossEntropy bf16 [8192,128256] / [8192,151936], every row active: 644.9 / 770.7 us
 // with load balancing, 651 / 774 with the default or spread.
-extern int g_row_cluster_policy;
+extern thread_local int g_row_cluster_policy;
 
 template <typename T, int THREADS, int NV, int CLUSTER, class Op, int NS = 0>
 static int launch_row_cfg(const T* logits, T* grad, int64_t n_rows, int64_t V, const Op& op, int* status, cudaStream_t st) {
@@ -482,8 +482,8 @@ static int launch_row_cfg(const T* logits, T* grad, int64_t n_rows, int64_t V, c
   return e == cudaSuccess ? HILDA_OK : HILDA_ERR_CUDA;
 }
 
-// Process-wide override of the plan, for tuning runs (0 = automatic).
-extern int g_row_force_nv, g_row_force_cluster, g_row_force_ns;
+// Override of the plan on the calling host thread, for tuning runs (0 = automatic).
+extern thread_local int g_row_force_nv, g_row_force_cluster, g_row_force_ns;
 
 template <typename T, class Op>
 static int launch_rows(const void* logits_v, void* grad_v, int64_t n_rows, int64_t V, const Op& op, int* status,

@@ -350,8 +350,8 @@ int hilda_selective_log_softmax(const void* logits, const int64_t* ids, const fl
                                 int64_t B, int64_t L, int64_t V, float temperature, int dtype, void* stream);
 
 /* Tuning hook for the row engine behind CrossEntropy/GRPO: force (register vectors per thread, CTAs
- * per cluster, shared-memory vectors per thread); (0, 0, 0) restores the automatic plan. No counterpart
- * in the reference. */
+ * per cluster, shared-memory vectors per thread); (0, 0, 0) restores the automatic plan. Acts on the
+ * calling host thread only. No counterpart in the reference. */
 void hilda_row_engine_force(int nv, int cluster, int ns);
 
 #ifdef __cplusplus

@@ -1215,7 +1215,7 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="skip the parity block (plain PyTorch fp32 on the device)")
     ap.add_argument("--no-comparators", action="store_true",
                     help="skip the reference-Triton / Liger / eager comparators of the per-op table (N = 1)")
-    ap.add_argument("--comparators-budget", type=int, default=420,
+    ap.add_argument("--comparators-budget", type=int, default=600,
                     help="seconds the comparator child process may take (Triton compiles and autotunes on first use)")
     ap.add_argument("--e2e-full-copy", action="store_true",
                     help="N > 1 end to end: every rank copies the whole replicated hidden from the host (default: 1/N + all-gather)")

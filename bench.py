@@ -379,6 +379,16 @@ def per_op_table(device, pk, only=None, small=False):
             L.check(lib.hilda_swiglu_bwd(a.data_ptr(), b.data_ptr(), dc.data_ptr(), da.data_ptr(), db.data_ptr(),
                                          a.numel(), L.dt(a), L.stream(a.device)), "swiglu_bwd")
         add("swiglu_bf16_fwd+bwd", timed2(sw_fwd, sw_bwd), 8 * a.numel() * 2, nr)
+
+        # GeGLU (tanh-approximated GELU gate, kernels/geglu.py) at the same shape and byte count
+        def ge_fwd():
+            L.check(lib.hilda_geglu_fwd(a.data_ptr(), b.data_ptr(), c_out.data_ptr(), a.numel(), L.dt(a),
+                                        L.stream(a.device)), "geglu_fwd")
+
+        def ge_bwd():
+            L.check(lib.hilda_geglu_bwd(a.data_ptr(), b.data_ptr(), dc.data_ptr(), da.data_ptr(), db.data_ptr(),
+                                        a.numel(), L.dt(a), L.stream(a.device)), "geglu_bwd")
+        add("geglu_bf16_fwd+bwd", timed2(ge_fwd, ge_bwd), 8 * a.numel() * 2, nr)
         del c_out, da, db
         del a, b, dc
     # config 3: CrossEntropy bf16 [8192, 128256], 10 % ignored: read valid rows once, write all grad rows

@@ -236,6 +236,26 @@ def op_swiglu(ref, g):
     return "swiglu_bf16_fwd+bwd", out
 
 
+def op_geglu(ref, g):
+    out = {}
+    a = rn(g, 16384, 14336).bfloat16().requires_grad_(True)
+    b = rn(g, 16384, 14336).bfloat16().requires_grad_(True)
+    dc = rn(g, 16384, 14336).bfloat16()
+
+    def mk(fn):  # as for SwiGLU: the reference's backward overwrites the saved a, b (kernels/geglu.py:146-159)
+        return lambda: [lambda: grads([fn(a, b)], [a, b], [dc])]
+    if ref:
+        from kernels.geglu import hilda_geglu
+        measure(out, "triton", mk(hilda_geglu))
+    try:
+        from liger_kernel.ops.geglu import LigerGELUMulFunction
+        measure(out, "liger", mk(LigerGELUMulFunction.apply))
+    except ImportError as e:
+        out["liger_error"] = str(e)
+    measure(out, "eager", mk(lambda a_, b_: F.gelu(a_, approximate="tanh") * b_))
+    return "geglu_bf16_fwd+bwd", out
+
+
 def op_cross_entropy(ref, g):
     out = {}
     n, v = 8192, 128256
@@ -451,7 +471,7 @@ def op_fused_linear_jsd(ref, g):
     return "fused_linear_jsd_bf16_fwd+bwd", out
 
 
-OPS = {"rms_norm": op_rms_norm, "fused_add_rms_norm": op_fused_add_rms_norm, "rope": op_rope, "rope_bhsd": op_rope_bhsd, "swiglu": op_swiglu,
+OPS = {"rms_norm": op_rms_norm, "fused_add_rms_norm": op_fused_add_rms_norm, "rope": op_rope, "rope_bhsd": op_rope_bhsd, "swiglu": op_swiglu, "geglu": op_geglu,
        "cross_entropy": op_cross_entropy, "fused_linear_cross_entropy": op_flce, "grpo": op_grpo,
        "attn_res": op_attn_res, "paged_attention": op_paged_attention, "kl_div": op_kl_div, "jsd": op_jsd,
        "fused_linear_jsd": op_fused_linear_jsd}

@@ -186,6 +186,24 @@ class VocabParallelFLCE:
         self.overlap_sms = int(overlap_sms)
         self.last_status = None
         self._side = {}
+        self._reduce_group = None
+
+    def _overlap_group(self):
+        """Communicator of the overlapped d(hidden) all-reduce: a group of its own over the same ranks,
+        so that the collective neither queues behind the row-statistics all-gathers of the main group
+        nor ahead of them, with NCCL held to ``overlap_sms`` CTAs: the d(W) GEMM beside it leaves exactly
+        that many SMs free, and a collective whose CTAs do not all fit waits for the GEMM to end
+        instead of running beside it. Created on first use (a collective call: every rank gets here)."""
+        if self._reduce_group is None:
+            if dist.get_backend(self.group) != "nccl":
+                self._reduce_group = self.group if self.group is not None else dist.group.WORLD
+            else:
+                ranks = dist.get_process_group_ranks(self.group if self.group is not None else dist.group.WORLD)
+                opts = dist.ProcessGroupNCCL.Options()
+                opts.config.max_ctas = max(1, self.overlap_sms)
+                opts.config.min_ctas = 1
+                self._reduce_group = dist.new_group(ranks, backend="nccl", pg_options=opts)
+        return self._reduce_group
 
     def _side_stream(self, dev):
         key = torch.device(dev).index
@@ -300,7 +318,7 @@ class VocabParallelFLCE:
                     side = self._side_stream(dev)
                     side.wait_stream(torch.cuda.current_stream(dev))
                     with torch.cuda.stream(side):
-                        dist.all_reduce(dh[r0:r0 + rows], op=dist.ReduceOp.SUM, group=self.group)
+                        dist.all_reduce(dh[r0:r0 + rows], op=dist.ReduceOp.SUM, group=self._overlap_group())
                     lib.hilda_gemm_set_sm_limit(self._sm_count(dev) - self.overlap_sms)
                 try:
                     L.check(lib.hilda_flce_grad_weight(L.ptr(scratch), L.ptr(hc), L.ptr(dw32), L.ptr(dw), mode, rows, H,

@@ -43,7 +43,7 @@ struct CEOp {
   int scale_loss;       // 0: leave the per-row loss unscaled (inference 'mean' divides afterwards)
 
   __device__ __forceinline__ int64_t row_offset(int64_t row, int64_t V) const { return row * V; }
-  __host__ bool rows_aligned(int64_t V, int vec) const { return V % vec == 0; }
+  __host__ bool rows_aligned(int64_t, int) const { return true; }  // rows start at row * V: any V
   __device__ __forceinline__ float inv_temperature() const { return 1.0f; }
   __device__ __forceinline__ bool begin(int64_t row, int64_t& target) const {
     target = targets[row];
@@ -108,7 +108,7 @@ struct GRPOOp {
   int logp_only;             // selective log-softmax: write logp_out only
 
   __device__ __forceinline__ int64_t row_offset(int64_t row, int64_t V) const { return row * V; }
-  __host__ bool rows_aligned(int64_t V, int vec) const { return V % vec == 0; }
+  __host__ bool rows_aligned(int64_t, int) const { return true; }  // rows start at row * V: any V
   __device__ __forceinline__ float inv_temperature() const { return inv_t; }
   __device__ __forceinline__ bool begin(int64_t row, int64_t& target) const {
     const int64_t b = row / (L + 1), l = row - b * (L + 1);

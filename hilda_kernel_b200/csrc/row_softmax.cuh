@@ -163,7 +163,7 @@ __device__ __forceinline__ float vec_exp_inplace(uint4& v, float k, float m) {
 constexpr int ROW_THREADS_DEFAULT = 256;
 constexpr int ROW_STATUS_TARGET_RANGE = 31;  // status word: a target / token id outside [0, V)
 
-// Register-resident, cluster-per-row kernel. Requires V % VEC == 0 and 16-byte aligned rows.
+// Register-resident, cluster-per-row kernel. Requires 16-byte aligned tensors; any V of four vectors or more.
 // CTAs per SM the register budget is held to (the row slice itself takes 4*NV registers).
 constexpr int row_min_blocks(int threads, int nv) {
   return nv <= 10 ? (threads <= 256 ? 4 : (threads <= 320 ? 3 : 2)) : 2;
@@ -190,21 +190,29 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
   const int tid = threadIdx.x;
   const uint32_t rank = (CLUSTER > 1) ? cluster_ctarank() : 0u;
   const int64_t row = blockIdx.x / CLUSTER;
-  const int n_vec = (int)(V / VEC);
+  const int64_t roff = op.row_offset(row, V);
+  // A row need not start or end on a 16-byte boundary (V = 50257, say): the vectors are the aligned
+  // body of the row, and the up to VEC - 1 elements before and after it are held one each, as scalars,
+  // by the first threads of the cluster's first CTA. The tensors' base addresses are 16-byte aligned.
+  const int head = (int)((VEC - (roff & (VEC - 1))) & (VEC - 1));
+  const int n_vec = (int)((V - head) / VEC);
+  const int n_extra = (int)(V - (int64_t)n_vec * VEC);  // head + tail elements, < 2 * VEC
   const int slice = (n_vec + CLUSTER - 1) / CLUSTER;
   const int v0 = (int)rank * slice;
   const int v1 = min(n_vec, v0 + slice);
-  const int64_t roff = op.row_offset(row, V);
   const T* xr = logits + roff;
   T* gr = grad ? grad + roff : nullptr;
   const bool writer = (rank == 0 && tid == 0);
+  const bool has_x = (rank == 0 && tid < n_extra);
+  const int64_t xi = tid < head ? (int64_t)tid : (int64_t)n_vec * VEC + tid;  // head + n_vec * VEC + (tid - head)
 
   int64_t target = -1;
   const bool active = op.begin(row, target);  // identical in every CTA of the cluster
   if (!active) {
     if (gr) {
       const uint4 z = make_uint4(0, 0, 0, 0);
-      for (int v = v0 + tid; v < v1; v += ROW_THREADS) st16_stream(gr + (int64_t)v * VEC, z);
+      for (int v = v0 + tid; v < v1; v += ROW_THREADS) st16_stream(gr + head + (int64_t)v * VEC, z);
+      if (has_x) VT<T>::store1(gr + xi, 0.f);
     }
     if (writer) op.inactive(row);
     return;
@@ -220,7 +228,8 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
   // per-thread base pointers: vector i of this thread sits at a compile-time offset from them
   const int my_vec = v1 - v0;  // vectors in this CTA's slice
   const int full = ROW_FULL_FAST ? my_vec / ROW_THREADS : 0;  // vectors every thread of the CTA holds: no bounds test for those
-  const uint4* src = reinterpret_cast<const uint4*>(xr) + v0 + tid;
+  const uint4* src = reinterpret_cast<const uint4*>(xr + head) + v0 + tid;
+  const float xe = has_x ? VT<T>::load1(xr + xi) : -INFINITY;
   uint4 xv[NV];
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
@@ -254,7 +263,7 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
 #pragma unroll
     for (int j = 0; j < NS; ++j) RowMath<T>::vmax(macc, stage[j * ROW_THREADS]);
   }
-  const float m_w = warp_max(RowMath<T>::max_final(macc)) * k;
+  const float m_w = warp_max(fmaxf(RowMath<T>::max_final(macc), xe)) * k;
   const float m_safe = (m_w == -INFINITY) ? 0.f : m_w;
   // pass 2: e = 2^(x*k - m_w) summed in fp32, and kept IN PLACE of x (rounded to T): the gradient
   // pass then needs one multiply per element instead of a second exponential (the SFU would
@@ -274,6 +283,8 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
       stage[j * ROW_THREADS] = v;
     }
   }
+  const float ee = ex2_approx(fmaf(xe, k, -m_safe));  // 0 for a thread without a scalar element
+  s += ee;
   s = warp_sum(s);
   // the warps' (max, sum) pairs -> the CTA's pair, computed by every thread (fixed order)
   constexpr int NW = ROW_THREADS / 32;
@@ -293,7 +304,7 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
   typename RowMath<T>::MaxAcc macc = RowMath<T>::max_init();
 #pragma unroll
   for (int i = 0; i < NV; ++i) RowMath<T>::vmax(macc, xv[i]);
-  float m = block_max<ROW_THREADS>(RowMath<T>::max_final(macc), red) * k;
+  float m = block_max<ROW_THREADS>(fmaxf(RowMath<T>::max_final(macc), xe), red) * k;
   const float m_w = m;
   const float m_safe = (m == -INFINITY) ? 0.f : m;
   float s = 0.f;
@@ -303,6 +314,8 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
     s += vec_exp_inplace<T>(xv[i], k, m_safe);
     opaque(xv[i]);
   }
+  const float ee = ex2_approx(fmaf(xe, k, -m_safe));
+  s += ee;
   s = block_sum<ROW_THREADS>(s, red);
 
 #endif
@@ -338,7 +351,7 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
   // softmax_j = e_j * 2^(m_warp - lse2)
   const float coef = (m_w == -INFINITY) ? 0.f : co.alpha * ex2_approx(m_w - lse2);
   const typename RowMath<T>::Coef pc = RowMath<T>::make_coef(coef);
-  uint4* dst = reinterpret_cast<uint4*>(gr) + v0 + tid;
+  uint4* dst = reinterpret_cast<uint4*>(gr + head) + v0 + tid;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     RowMath<T>::scale(xv[i], pc);
@@ -354,11 +367,15 @@ row_softmax_kernel(const T* __restrict__ logits, T* __restrict__ grad, int64_t V
   }
   // The target column gets alpha*softmax + beta: the thread that stored its vector overwrites that
   // one element afterwards (same thread, same address: program order holds).
-  if (target >= 0 && target < V) {
-    const int tv = (int)(target / VEC) - v0;
+  const bool t_ok = target >= 0 && target < V;
+  const bool t_body = t_ok && target >= head && target < head + (int64_t)n_vec * VEC;
+  if (t_body) {
+    const int tv = (int)((target - head) / VEC) - v0;
     if (tv >= 0 && tv < my_vec && (tv % ROW_THREADS) == tid)
       VT<T>::store1(gr + target, co.alpha * ex2_approx((x_t - lse) * LOG2E) + co.beta);
   }
+  // the scalar head / tail elements: gradient straight from fp32
+  if (has_x) VT<T>::store1(gr + xi, coef * ee + ((t_ok && xi == target) ? co.beta : 0.f));
 }
 
 // Any V / alignment: one CTA per row, scalar access, row read twice (second read from L2).
@@ -417,8 +434,8 @@ struct RowPlan { int threads; int nv; int cluster; bool generic; int ns; };
 // force_nv may carry the thread count as threads*100 + nv.
 static inline RowPlan plan_row(int64_t V, int vec, bool aligned, int force_nv, int force_cluster, int force_ns) {
   RowPlan p{ROW_THREADS_DEFAULT, 0, 1, true, 0};
-  if (!aligned || V % vec != 0 || V / vec > 0x7fffffff) return p;
-  const int64_t n_vec = V / vec;
+  if (!aligned || V / vec > 0x7fffffff || V < 4 * vec) return p;
+  const int64_t n_vec = V / vec;  // a row that does not start on a 16-byte boundary has one vector fewer
   if (force_nv > 0 && force_cluster > 0) {
     const int th = force_nv >= 100 ? force_nv / 100 : ROW_THREADS_DEFAULT;
     const int nv = force_nv % 100;

@@ -459,6 +459,34 @@ def test_cross_entropy_golden_and_edges(golden):
         L.lib().hilda_row_engine_force(0, 0, 0)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("v", [50257, 1003, 32001])
+def test_cross_entropy_rows_off_the_16_byte_grid(dtype, v):
+    """A vocabulary that is not a multiple of the vector width: rows start and end between 16-byte
+    boundaries (a different offset in every row). The targets sit on the first and last elements of the
+    rows, which the kernel holds as scalars beside the aligned vectors."""
+    hk = ops()
+    n = 24
+    g = gen(31)
+    logits = (2.0 * torch.randn(n, v, generator=g)).to(dtype)
+    edge = list(range(8)) + [v - 1 - i for i in range(8)]
+    targets = torch.tensor([edge[i % len(edge)] for i in range(n)])
+    targets[5] = -100
+    lr = logits.float().clone().requires_grad_(True)
+    loss_ref = R.cross_entropy_clamped(lr, targets, -100, "mean")
+    loss_ref.backward()
+    ld = logits.to(DEV).requires_grad_(True)
+    loss = hk.hilda_cross_entropy(ld, targets.to(DEV), -100, "mean")
+    loss.backward()
+    assert_loss_close(loss, loss_ref)
+    assert_close(ld.grad, lr.grad, dtype, what="dlogits", normalize=True)
+    assert float(ld.grad[5].abs().max()) == 0.0
+    # the gradient at the target column is softmax - 1: negative, and the largest magnitude of its row
+    rows = torch.arange(n)[targets != -100]
+    at_t = ld.grad.float().cpu()[rows, targets[rows]]
+    assert bool((at_t < 0).all())
+
+
 # ------------------------------------------------------------------ GRPO
 def _grpo_inputs(B, L, V, dtype, seed=9, masked=True):
     g = gen(seed)

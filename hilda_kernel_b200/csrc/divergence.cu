@@ -41,20 +41,30 @@ kl_div_fwd_kernel(const T* __restrict__ y_pred, const T* __restrict__ y_true, fl
                   int64_t n_rows, int64_t n_cols, float eps, int log_target, int aligned) {
   constexpr int VEC = VT<T>::N;
   __shared__ float red[33];
-  const bool vec_ok = aligned && (n_cols % VEC) == 0;  // misaligned views take the element-wise path
+  const bool vec_ok = aligned != 0;  // misaligned views take the element-wise path
   for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
     const T* yp = y_pred + row * n_cols;
     const T* yt = y_true + row * n_cols;
     float acc = 0.f;
     if (vec_ok) {
-      const int64_t n_vec = n_cols / VEC;
+      // a row whose length is no multiple of the vector width starts and ends between 16-byte
+      // boundaries: vectors over its aligned body, the few elements before and after one by one
+      const int64_t head = min((int64_t)((VEC - ((row * n_cols) & (VEC - 1))) & (VEC - 1)), n_cols);
+      const int64_t n_vec = (n_cols - head) / VEC;
+      const int64_t rest = head + n_vec * VEC;
       for (int64_t v = threadIdx.x; v < n_vec; v += DV_THREADS) {
         float y[VEC], t[VEC];
-        VT<T>::unpack(ld16_stream(yp + v * VEC), y);
-        VT<T>::unpack(ld16_stream(yt + v * VEC), t);
+        VT<T>::unpack(ld16_stream(yp + head + v * VEC), y);
+        VT<T>::unpack(ld16_stream(yt + head + v * VEC), t);
 #pragma unroll
         for (int j = 0; j < VEC; ++j)
           acc += log_target ? kl_exp<T>(t[j]) * (t[j] - y[j]) : t[j] * (kl_log<T>(fmaxf(t[j], eps)) - y[j]);
+      }
+      const int64_t n_edge = head + (n_cols - rest);
+      if ((int64_t)threadIdx.x < n_edge) {
+        const int64_t c = (int64_t)threadIdx.x < head ? (int64_t)threadIdx.x : rest + ((int64_t)threadIdx.x - head);
+        const float y = VT<T>::load1(yp + c), t = VT<T>::load1(yt + c);
+        acc += log_target ? kl_exp<T>(t) * (t - y) : t * (kl_log<T>(fmaxf(t, eps)) - y);
       }
     } else {
       for (int64_t c = threadIdx.x; c < n_cols; c += DV_THREADS) {
@@ -148,15 +158,30 @@ jsd_rows_kernel(const T* __restrict__ X, const T* __restrict__ Y, T* __restrict_
   __shared__ float red[33];
   const int mode = jsd_mode(beta);
   const float inv_n = 1.0f / (n_valid ? fmaxf((float)(*n_valid), 1.0f) : (float)n_rows);
-  const bool vec_ok = aligned && (V % VEC) == 0;
+  const bool vec_ok = aligned != 0;
   for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
-    const T* x = X + row * V;
-    const T* y = Y + row * V;
-    T* d = dX + row * V;
     const bool ignored = labels && labels[row] == ignore_index;
     float acc = 0.f;
     if (vec_ok) {
-      const int64_t n_vec = V / VEC;
+      // vectors over the aligned body of the row; the elements before and after it one by one
+      const int64_t head = min((int64_t)((VEC - ((row * V) & (VEC - 1))) & (VEC - 1)), V);
+      const int64_t n_vec = (V - head) / VEC;
+      const int64_t rest = head + n_vec * VEC;
+      const int64_t n_edge = head + (V - rest);
+      if ((int64_t)threadIdx.x < n_edge) {
+        const int64_t c = (int64_t)threadIdx.x < head ? (int64_t)threadIdx.x : rest + ((int64_t)threadIdx.x - head);
+        const int64_t at = row * V + c;
+        if (ignored) {
+          VT<T>::store1(dX + at, 0.f);
+        } else {
+          const JsdTerm t = jsd_term<sizeof(T) == 4>(VT<T>::load1(X + at), VT<T>::load1(Y + at), beta, mode);
+          acc += t.loss;
+          VT<T>::store1(dX + at, t.dx * inv_n);
+        }
+      }
+      const T* x = X + row * V + head;
+      const T* y = Y + row * V + head;
+      T* d = dX + row * V + head;
       if (ignored) {
         const uint4 z = make_uint4(0, 0, 0, 0);
         for (int64_t v = threadIdx.x; v < n_vec; v += DV_THREADS) st16_stream(d + v * VEC, z);
@@ -192,6 +217,9 @@ jsd_rows_kernel(const T* __restrict__ X, const T* __restrict__ Y, T* __restrict_
         }
       }
     } else {
+      const T* x = X + row * V;
+      const T* y = Y + row * V;
+      T* d = dX + row * V;
       for (int64_t c = threadIdx.x; c < V; c += DV_THREADS) {
         if (ignored) { VT<T>::store1(d + c, 0.f); continue; }
         const JsdTerm t = jsd_term<sizeof(T) == 4>(VT<T>::load1(x + c), VT<T>::load1(y + c), beta, mode);

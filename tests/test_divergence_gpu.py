@@ -31,7 +31,7 @@ def fp16_grad_underflows(dtype, expected, actual):
 
 
 # ------------------------------------------------------------------ KLDiv
-@pytest.mark.parametrize("shape", [(64, 32000), (16, 128256), (7, 200), (5, 33), (3, 4, 1000), (1, 1)])
+@pytest.mark.parametrize("shape", [(64, 32000), (16, 128256), (7, 200), (5, 33), (3, 4, 1000), (1, 1), (6, 50257), (9, 1003)])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("reduction", ["batchmean", "sum", "mean", "none"])
 @pytest.mark.parametrize("log_target", [False, True])
@@ -76,7 +76,7 @@ def test_kl_div_golden_and_module(golden):
 
 
 # ------------------------------------------------------------------ JSD
-@pytest.mark.parametrize("nv", [(64, 32000), (16, 128256), (9, 700), (5, 33)])
+@pytest.mark.parametrize("nv", [(64, 32000), (16, 128256), (9, 700), (5, 33), (6, 50257), (9, 1003)])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("beta", [0.5, 0.0, 1.0, 0.1])
 @pytest.mark.parametrize("with_labels", [False, True])

@@ -478,7 +478,7 @@ static NormPlan plan_norm(int64_t n_cols, int vec, int pref_vpt, bool all_aligne
   if (!all_aligned || n_cols % vec != 0) return p;
   const int64_t n_vec = n_cols / vec;
   int vpt = pref_vpt;
-  while (vpt > 1 && n_vec / vpt < 128) vpt >>= 1;
+  while (vpt > 1 && n_vec <= 128 * (vpt / 2)) vpt >>= 1;  // fewer vectors per thread only if 128 threads still cover the row
   while (vpt < 8 && n_vec > (int64_t)vpt * 1024) vpt <<= 1;
   if (n_vec > (int64_t)vpt * 1024) return p;
   int threads = 128;
@@ -504,7 +504,10 @@ template <typename T>
 static int norm_fwd_t(const void* x, const void* r, const void* w, int w_dt, void* y, void* s, float* rstd,
                       int64_t n_rows, int64_t n_cols, float eps, cudaStream_t st) {
   const bool al = aligned16(x) && aligned16(y) && aligned16(w) && (!r || (aligned16(r) && aligned16(s)));
-  const int pref = (sizeof(T) == 4) ? 4 : 2;
+  // 16-bit rows without the residual stream keep four vectors per thread in flight (half as many threads
+  // per row, twice as many rows per SM): bf16 [16384,4096] 5.90 against 4.98 TB/s, [8192,8192] 5.43 against
+  // 3.89, [13107,5120] 4.49 against 2.94; with the residual stream two per thread measured best
+  const int pref = (sizeof(T) == 4) ? 4 : (r ? 2 : 4);
   NormPlan plan = plan_norm(n_cols, VT<T>::N, pref, al);
   const int64_t max_grid = (int64_t)sm_count() * 64;
   if (plan.generic) {
@@ -560,8 +563,9 @@ static int launch_dw_reduce(const float* partial, int P, int64_t n_cols, void* d
 }
 
 // Kernel choice of the backward for vectorisable shapes (per host thread; HILDA_NORM_RING presets it):
-//   1 (default) automatic: the shared-memory ring (norm_bwd_ring_kernel) when three or more row slots
-//     fit beside the SM's other CTAs, else the register kernel with an L2 bulk prefetch one row ahead.
+//   1 (default) automatic: for 32-bit rows the shared-memory ring (norm_bwd_ring_kernel) when three or more
+//     row slots fit beside the SM's other CTAs; else, and for 16-bit rows always, the register kernel with
+//     an L2 bulk prefetch one row ahead.
 //     Measured on B200: fp32 [4096,4096] (3 slots, 2 CTAs per SM) ring 37.6 us, register kernel 42.0,
 //     with prefetch 38.8; bf16 [16384,4096] with dS (2 slots, 4 CTAs per SM) ring 101.7 us, register
 //     kernel 100.5, with prefetch one row ahead 93.5, two rows ahead 96.7.
@@ -597,7 +601,11 @@ static int norm_bwd_t(const void* dy, const void* ds, const void* x, const void*
     int64_t stages = ((int64_t)228 * 1024 / per_sm - 1024 - 512 - n_cols * 4) / stage_bytes;
     if (stages > NB_MAX_STAGES) stages = NB_MAX_STAGES;
     const int64_t min_stages = g_norm_ring == 4 ? 2 : 3;
-    if ((g_norm_ring == 1 || g_norm_ring == 4) && stages >= min_stages) {
+    // automatic choice: the ring for 32-bit rows only. For 16-bit rows the register kernel with the L2
+    // prefetch measured faster wherever the ring fits (bf16, dY and x: H = 3072 4.35 against 3.76 TB/s,
+    // 5120 3.90 against 3.35, 7168 4.60 against 4.15)
+    const bool ring_auto = g_norm_ring == 1 && sizeof(T) == 4;
+    if ((ring_auto || g_norm_ring == 4) && stages >= min_stages) {
       int smem = 0;
       cudaError_t e = cudaSuccess;
       int occ = 0;

@@ -10,6 +10,7 @@
 // owns, written as one fp32 partial row per CTA, and reduced by a second small kernel (fixed
 // order, no atomics, bit-reproducible).
 #include <cstdlib>
+#include <type_traits>
 #include "common.cuh"
 
 namespace hilda {
@@ -227,6 +228,92 @@ norm_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __r
       for (int j = 0; j < VEC; j += 4)
         st16(pr + (int64_t)v * VEC + j, VT<float>::pack(&dw[i][j]));
     }
+  }
+}
+
+// ---- 16-bit backward for rows that fill the plan exactly -----------------------------------------
+// The general kernel above spends about as many instructions on bounds tests, 64-bit row offsets and the
+// per-vector fetch of w as on the arithmetic, and for 16-bit rows it is instruction issue, not HBM,
+// that bounds it (28 instructions per element, 60 % of the issue slots busy at 0.89 of HBM). This
+// kernel serves the common case only: n_cols == 8 * THREADS * VPT, w in the data's own dtype, dY present.
+// w is unpacked once into registers, the row pointers advance by a constant, nothing is predicated.
+// Same arithmetic in the same order as norm_bwd_kernel: bit-identical dX; dW is summed over this kernel's
+// own, smaller grid (three CTAs per SM instead of four), so it differs from the other kernels' by the
+// grouping of the partial sums. Measured on B200, bf16: [16384,4096] with dS 88.8 us against 91.9,
+// without dS 69.6 against 83.0, [32768,2048] 68.7 against 80.7.
+template <typename T, int THREADS, int VPT, bool HAS_DS>
+__global__ void __launch_bounds__(THREADS, 768 / THREADS)
+norm_bwd16_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __restrict__ X,
+                  const T* __restrict__ W, const float* __restrict__ RSTD, T* __restrict__ dX,
+                  float* __restrict__ partial, int64_t n_rows, int prefetch_rows) {
+  constexpr int VEC = 8;
+  constexpr int N_COLS = VEC * THREADS * VPT;
+  __shared__ float red[33];
+  const int tid = threadIdx.x;
+  const float inv_n = 1.0f / (float)N_COLS;
+  float w[VPT][VEC], dw[VPT][VEC];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    VT<T>::unpack(ld16(W + (tid + i * THREADS) * VEC), w[i]);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) dw[i][j] = 0.f;
+  }
+  const int64_t step = (int64_t)gridDim.x * N_COLS;
+  int64_t off = (int64_t)blockIdx.x * N_COLS + (int64_t)tid * VEC;
+  constexpr uint32_t ROW_BYTES = (uint32_t)N_COLS * (uint32_t)sizeof(T);
+  for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x, off += step) {
+    if (prefetch_rows > 0 && tid == 0) {
+      const int64_t ahead = row + (int64_t)prefetch_rows * gridDim.x;
+      if (ahead < n_rows) {
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(X + ahead * N_COLS), "r"(ROW_BYTES) : "memory");
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(dY + ahead * N_COLS), "r"(ROW_BYTES) : "memory");
+        if (HAS_DS) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(dS + ahead * N_COLS), "r"(ROW_BYTES) : "memory");
+      }
+    }
+    uint4 dyv[VPT], xv[VPT], dsv[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      dyv[i] = ld16_stream(dY + off + i * (THREADS * VEC));
+      xv[i] = ld16_stream(X + off + i * (THREADS * VEC));
+      if (HAS_DS) dsv[i] = ld16_stream(dS + off + i * (THREADS * VEC));
+    }
+    const float rstd = RSTD[row];
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      float dy[VEC], x[VEC];
+      VT<T>::unpack(dyv[i], dy);
+      VT<T>::unpack(xv[i], x);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) acc = fmaf(dy[j] * w[i][j], x[j], acc);
+    }
+    acc = block_sum<THREADS>(acc, red);
+    const float coef = rstd * rstd * rstd * (acc * inv_n);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      float dy[VEC], x[VEC], dx[VEC];
+      VT<T>::unpack(dyv[i], dy);
+      VT<T>::unpack(xv[i], x);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        dx[j] = rstd * (dy[j] * w[i][j]) - coef * x[j];
+        dw[i][j] = fmaf(dy[j], x[j] * rstd, dw[i][j]);
+      }
+      if (HAS_DS) {
+        float ds[VEC];
+        VT<T>::unpack(dsv[i], ds);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) dx[j] += ds[j];
+      }
+      st16(dX + off + i * (THREADS * VEC), VT<T>::pack(dx));
+    }
+  }
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the second pass may start launching
+  float* pr = partial + (int64_t)blockIdx.x * N_COLS + (int64_t)tid * VEC;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+#pragma unroll
+    for (int j = 0; j < VEC; j += 4) st16(pr + i * (THREADS * VEC) + j, VT<float>::pack(&dw[i][j]));
   }
 }
 
@@ -565,7 +652,8 @@ static int launch_dw_reduce(const float* partial, int P, int64_t n_cols, void* d
 // Kernel choice of the backward for vectorisable shapes (per host thread; HILDA_NORM_RING presets it):
 //   1 (default) automatic: for 32-bit rows the shared-memory ring (norm_bwd_ring_kernel) when three or more
 //     row slots fit beside the SM's other CTAs; else, and for 16-bit rows always, the register kernel with
-//     an L2 bulk prefetch one row ahead.
+//     an L2 bulk prefetch one row ahead (16-bit rows that fill the plan exactly: its lean form,
+//     norm_bwd16_kernel).
 //     Measured on B200: fp32 [4096,4096] (3 slots, 2 CTAs per SM) ring 37.6 us, register kernel 42.0,
 //     with prefetch 38.8; bf16 [16384,4096] with dS (2 slots, 4 CTAs per SM) ring 101.7 us, register
 //     kernel 100.5, with prefetch one row ahead 93.5, two rows ahead 96.7.
@@ -594,6 +682,26 @@ static int norm_bwd_t(const void* dy, const void* ds, const void* x, const void*
     norm_bwd_generic_kernel<T><<<grid, 256, 0, st>>>((const T*)dy, (const T*)ds, (const T*)x, w, w_dt, rstd,
                                                        (T*)dx, workspace, n_rows, n_cols);
   } else {
+    // 16-bit rows that fill the plan exactly, w in the data's dtype: the lean kernel (automatic choice only)
+    if constexpr (sizeof(T) == 2) {
+      if (g_norm_ring == 1 && dy && w_dt == (std::is_same<T, __nv_bfloat16>::value ? HILDA_BF16 : HILDA_F16) && plan.vpt == 2 && n_cols == (int64_t)8 * plan.threads * plan.vpt &&
+          (plan.threads == 128 || plan.threads == 256)) {  // 512 threads: no faster than the general kernel (4.62 against 4.71 TB/s)
+#define B16_CALL(TH, DS)                                                                                      \
+  do {                                                                                                        \
+    int occ = 0;  /* a persistent grid: no more CTAs than are resident at once */                             \
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, norm_bwd16_kernel<T, TH, 2, DS>, TH, 0) == cudaSuccess && \
+        occ > 0 && grid > occ * sm_count())                                                                   \
+      grid = occ * sm_count();                                                                                \
+    norm_bwd16_kernel<T, TH, 2, DS><<<grid, TH, 0, st>>>((const T*)dy, (const T*)ds, (const T*)x, (const T*)w, rstd, \
+                                                          (T*)dx, workspace, n_rows, 1);                       \
+  } while (0)
+        if (plan.threads == 128) { if (ds) B16_CALL(128, true); else B16_CALL(128, false); }
+        else { if (ds) B16_CALL(256, true); else B16_CALL(256, false); }
+#undef B16_CALL
+        HILDA_LAUNCH_CHECK();
+        return launch_dw_reduce(workspace, grid, n_cols, dw, w_dt, st);
+      }
+    }
     // ring of row slots in shared memory: as many as fit beside the other CTAs of the SM, at most NB_MAX_STAGES
     const int per_sm = (grid + sm_count() - 1) / sm_count();
     const int64_t stage_bytes = n_cols * (int64_t)sizeof(T) * (1 + (dy ? 1 : 0) + (ds ? 1 : 0));

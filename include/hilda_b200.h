@@ -62,9 +62,11 @@ int hilda_norm_bwd(const void* dy, const void* ds, const void* x, const void* w,
 /* Kernel behind hilda_norm_bwd for vectorisable shapes (no counterpart in the reference). 1
  * (default) = automatic: for 32-bit rows every CTA stages its rows through a ring of shared-memory
  * slots filled by bulk asynchronous copies when three or more slots fit; else, and for 16-bit rows
- * always, the register kernel (one row in flight per CTA) with a bulk L2 prefetch of the CTA's next row; 0 = register kernel, no prefetch;
- * 2 / 3 = register kernel with the prefetch 1 / 2 rows ahead; 4 = ring whenever two slots fit. Same
- * results bit for bit. Other values only query. Returns the previous choice; per host thread.
+ * always, the register kernel (one row in flight per CTA) with a bulk L2 prefetch of the CTA's next
+ * row, in a lean form when a 16-bit row fills the plan exactly; 0 = register kernel, no prefetch;
+ * 2 / 3 = register kernel with the prefetch 1 / 2 rows ahead; 4 = ring whenever two slots fit. dX is
+ * the same bit for bit on every path, dW on every path that runs the same grid (the lean 16-bit
+ * kernel runs fewer CTAs: its dW differs by the grouping of the partial sums). Other values only query. Returns the previous choice; per host thread.
  * Environment: HILDA_NORM_RING. */
 int hilda_norm_bwd_set_path(int path);
 

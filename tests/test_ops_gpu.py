@@ -161,7 +161,14 @@ def test_norm_backward_ring_and_register_kernels_agree():
                     lib.hilda_norm_bwd_set_path(1)
             for other in res[1:]:
                 assert torch.equal(res[0][0], other[0]), (n_rows, n_cols, dtype, use_dy, use_ds)
-                assert torch.equal(res[0][1], other[1]), (n_rows, n_cols, dtype, use_dy, use_ds)
+            # dW: the explicitly chosen kernels run the same grid and agree bit for bit; the automatic choice
+            # may be the lean 16-bit kernel on a smaller grid, whose partial sums are grouped differently
+            for other in res[2:]:
+                assert torch.equal(res[1][1], other[1]), (n_rows, n_cols, dtype, use_dy, use_ds)
+            if dtype == torch.float32:
+                assert torch.equal(res[0][1], res[1][1]), (n_rows, n_cols, dtype, use_dy, use_ds)
+            else:
+                torch.testing.assert_close(res[0][1].float(), res[1][1].float(), rtol=1.6e-2, atol=1e-2 * n_rows ** 0.5)
             assert bool(torch.isfinite(res[0][1].float()).all())
 
 

@@ -235,47 +235,54 @@ norm_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __r
 // The general kernel above spends about as many instructions on bounds tests, 64-bit row offsets and the
 // per-vector fetch of w as on the arithmetic, and for 16-bit rows it is instruction issue, not HBM,
 // that bounds it (28 instructions per element, 60 % of the issue slots busy at 0.89 of HBM). This
-// kernel serves the common case only: n_cols == 8 * THREADS * VPT, w in the data's own dtype, dY present.
-// w is unpacked once into registers, the row pointers advance by a constant, nothing is predicated.
-// Same arithmetic in the same order as norm_bwd_kernel: bit-identical dX; dW is summed over this kernel's
-// own, smaller grid (three CTAs per SM instead of four), so it differs from the other kernels' by the
-// grouping of the partial sums. Measured on B200, bf16: [16384,4096] with dS 88.8 us against 91.9,
-// without dS 69.6 against 83.0, [32768,2048] 68.7 against 80.7.
-template <typename T, int THREADS, int VPT, bool HAS_DS>
-__global__ void __launch_bounds__(THREADS, 768 / THREADS)
+// kernel serves the common case only: 16-bit rows of up to 8192 elements, w in the data's own dtype, dY
+// present. w is unpacked once into registers, the row pointers advance by a constant, and the bounds
+// tests are per-thread flags set once (none at all when the row fills the plan exactly).
+// Same arithmetic as norm_bwd_kernel; the sums are grouped by this kernel's own thread plan and its own,
+// smaller grid (three or two CTAs per SM), so dX and dW agree with the other kernels' within rounding, not
+// bit for bit. Measured on B200, bf16 (TB/s of dY, x and dX): [16384,4096] 5.77 against 4.85 (with dS 88.7 us
+// against 91.9), [32768,2048] 5.86 against 4.99, H = 3072 5.12 against 4.33, 5120 4.94 against 3.90, 7168 5.56
+// against 4.58, 8192 5.02 against 4.71.
+template <typename T, int THREADS, int VPT, bool HAS_DS, bool FULL>
+__global__ void __launch_bounds__(THREADS, (VPT <= 2 ? 768 : 512) / THREADS)
 norm_bwd16_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* __restrict__ X,
                   const T* __restrict__ W, const float* __restrict__ RSTD, T* __restrict__ dX,
-                  float* __restrict__ partial, int64_t n_rows, int prefetch_rows) {
+                  float* __restrict__ partial, int64_t n_rows, int n_cols_rt, int prefetch_rows) {
   constexpr int VEC = 8;
-  constexpr int N_COLS = VEC * THREADS * VPT;
+  // FULL: the row fills the plan exactly (n_cols == 8 * THREADS * VPT), nothing is predicated
+  const int n_cols = FULL ? VEC * THREADS * VPT : n_cols_rt;
+  const int n_vec = n_cols / VEC;
   __shared__ float red[33];
   const int tid = threadIdx.x;
-  const float inv_n = 1.0f / (float)N_COLS;
+  const float inv_n = 1.0f / (float)n_cols;
+  bool ok[VPT];
   float w[VPT][VEC], dw[VPT][VEC];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    VT<T>::unpack(ld16(W + (tid + i * THREADS) * VEC), w[i]);
+    ok[i] = FULL || (tid + i * THREADS < n_vec);
 #pragma unroll
-    for (int j = 0; j < VEC; ++j) dw[i][j] = 0.f;
+    for (int j = 0; j < VEC; ++j) { w[i][j] = 0.f; dw[i][j] = 0.f; }
+    if (ok[i]) VT<T>::unpack(ld16(W + (tid + i * THREADS) * VEC), w[i]);
   }
-  const int64_t step = (int64_t)gridDim.x * N_COLS;
-  int64_t off = (int64_t)blockIdx.x * N_COLS + (int64_t)tid * VEC;
-  constexpr uint32_t ROW_BYTES = (uint32_t)N_COLS * (uint32_t)sizeof(T);
+  const int64_t step = (int64_t)gridDim.x * n_cols;
+  int64_t off = (int64_t)blockIdx.x * n_cols + (int64_t)tid * VEC;
+  const uint32_t row_bytes = (uint32_t)n_cols * (uint32_t)sizeof(T);
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
   for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x, off += step) {
     if (prefetch_rows > 0 && tid == 0) {
       const int64_t ahead = row + (int64_t)prefetch_rows * gridDim.x;
       if (ahead < n_rows) {
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(X + ahead * N_COLS), "r"(ROW_BYTES) : "memory");
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(dY + ahead * N_COLS), "r"(ROW_BYTES) : "memory");
-        if (HAS_DS) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(dS + ahead * N_COLS), "r"(ROW_BYTES) : "memory");
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(X + ahead * n_cols), "r"(row_bytes) : "memory");
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(dY + ahead * n_cols), "r"(row_bytes) : "memory");
+        if (HAS_DS) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(dS + ahead * n_cols), "r"(row_bytes) : "memory");
       }
     }
     uint4 dyv[VPT], xv[VPT], dsv[VPT];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      dyv[i] = ld16_stream(dY + off + i * (THREADS * VEC));
-      xv[i] = ld16_stream(X + off + i * (THREADS * VEC));
-      if (HAS_DS) dsv[i] = ld16_stream(dS + off + i * (THREADS * VEC));
+      dyv[i] = ok[i] ? ld16_stream(dY + off + i * (THREADS * VEC)) : zero4;
+      xv[i] = ok[i] ? ld16_stream(X + off + i * (THREADS * VEC)) : zero4;
+      if (HAS_DS) dsv[i] = ok[i] ? ld16_stream(dS + off + i * (THREADS * VEC)) : zero4;
     }
     const float rstd = RSTD[row];
     float acc = 0.f;
@@ -284,8 +291,10 @@ norm_bwd16_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* _
       float dy[VEC], x[VEC];
       VT<T>::unpack(dyv[i], dy);
       VT<T>::unpack(xv[i], x);
+      if (ok[i]) {
 #pragma unroll
-      for (int j = 0; j < VEC; ++j) acc = fmaf(dy[j] * w[i][j], x[j], acc);
+        for (int j = 0; j < VEC; ++j) acc = fmaf(dy[j] * w[i][j], x[j], acc);
+      }
     }
     acc = block_sum<THREADS>(acc, red);
     const float coef = rstd * rstd * rstd * (acc * inv_n);
@@ -294,26 +303,30 @@ norm_bwd16_kernel(const T* __restrict__ dY, const T* __restrict__ dS, const T* _
       float dy[VEC], x[VEC], dx[VEC];
       VT<T>::unpack(dyv[i], dy);
       VT<T>::unpack(xv[i], x);
+      if (ok[i]) {
 #pragma unroll
-      for (int j = 0; j < VEC; ++j) {
-        dx[j] = rstd * (dy[j] * w[i][j]) - coef * x[j];
-        dw[i][j] = fmaf(dy[j], x[j] * rstd, dw[i][j]);
-      }
-      if (HAS_DS) {
-        float ds[VEC];
-        VT<T>::unpack(dsv[i], ds);
+        for (int j = 0; j < VEC; ++j) {
+          dx[j] = rstd * (dy[j] * w[i][j]) - coef * x[j];
+          dw[i][j] = fmaf(dy[j], x[j] * rstd, dw[i][j]);
+        }
+        if (HAS_DS) {
+          float ds[VEC];
+          VT<T>::unpack(dsv[i], ds);
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) dx[j] += ds[j];
+          for (int j = 0; j < VEC; ++j) dx[j] += ds[j];
+        }
+        st16(dX + off + i * (THREADS * VEC), VT<T>::pack(dx));
       }
-      st16(dX + off + i * (THREADS * VEC), VT<T>::pack(dx));
     }
   }
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the second pass may start launching
-  float* pr = partial + (int64_t)blockIdx.x * N_COLS + (int64_t)tid * VEC;
+  float* pr = partial + (int64_t)blockIdx.x * n_cols + (int64_t)tid * VEC;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
+    if (ok[i]) {
 #pragma unroll
-    for (int j = 0; j < VEC; j += 4) st16(pr + i * (THREADS * VEC) + j, VT<float>::pack(&dw[i][j]));
+      for (int j = 0; j < VEC; j += 4) st16(pr + i * (THREADS * VEC) + j, VT<float>::pack(&dw[i][j]));
+    }
   }
 }
 
@@ -682,21 +695,30 @@ static int norm_bwd_t(const void* dy, const void* ds, const void* x, const void*
     norm_bwd_generic_kernel<T><<<grid, 256, 0, st>>>((const T*)dy, (const T*)ds, (const T*)x, w, w_dt, rstd,
                                                        (T*)dx, workspace, n_rows, n_cols);
   } else {
-    // 16-bit rows that fill the plan exactly, w in the data's dtype: the lean kernel (automatic choice only)
+    // 16-bit rows of 129 to 1024 vectors, w in the data's dtype: the lean kernel (automatic choice only)
     if constexpr (sizeof(T) == 2) {
-      if (g_norm_ring == 1 && dy && w_dt == (std::is_same<T, __nv_bfloat16>::value ? HILDA_BF16 : HILDA_F16) && plan.vpt == 2 && n_cols == (int64_t)8 * plan.threads * plan.vpt &&
-          (plan.threads == 128 || plan.threads == 256)) {  // 512 threads: no faster than the general kernel (4.62 against 4.71 TB/s)
-#define B16_CALL(TH, DS)                                                                                      \
+      const int64_t n_vec16 = n_cols / 8;
+      if (g_norm_ring == 1 && dy && w_dt == (std::is_same<T, __nv_bfloat16>::value ? HILDA_BF16 : HILDA_F16) &&
+          n_vec16 > 128 && n_vec16 <= 1024) {
+#define B16_CALL(TH, VP, DS, FU)                                                                              \
   do {                                                                                                        \
     int occ = 0;  /* a persistent grid: no more CTAs than are resident at once */                             \
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, norm_bwd16_kernel<T, TH, 2, DS>, TH, 0) == cudaSuccess && \
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, norm_bwd16_kernel<T, TH, VP, DS, FU>, TH, 0) == cudaSuccess && \
         occ > 0 && grid > occ * sm_count())                                                                   \
       grid = occ * sm_count();                                                                                \
-    norm_bwd16_kernel<T, TH, 2, DS><<<grid, TH, 0, st>>>((const T*)dy, (const T*)ds, (const T*)x, (const T*)w, rstd, \
-                                                          (T*)dx, workspace, n_rows, 1);                       \
+    norm_bwd16_kernel<T, TH, VP, DS, FU><<<grid, TH, 0, st>>>((const T*)dy, (const T*)ds, (const T*)x, (const T*)w, rstd, \
+                                                              (T*)dx, workspace, n_rows, (int)n_cols, 1);      \
   } while (0)
-        if (plan.threads == 128) { if (ds) B16_CALL(128, true); else B16_CALL(128, false); }
-        else { if (ds) B16_CALL(256, true); else B16_CALL(256, false); }
+#define B16_PICK(TH, VP)                                                                                      \
+  do {                                                                                                        \
+    const bool fu = n_vec16 == (int64_t)(TH) * (VP);                                                          \
+    if (ds) { if (fu) B16_CALL(TH, VP, true, true); else B16_CALL(TH, VP, true, false); }                     \
+    else { if (fu) B16_CALL(TH, VP, false, true); else B16_CALL(TH, VP, false, false); }                      \
+  } while (0)
+        if (n_vec16 <= 256) B16_PICK(128, 2);
+        else if (n_vec16 <= 512) B16_PICK(256, 2);
+        else B16_PICK(256, 4);
+#undef B16_PICK
 #undef B16_CALL
         HILDA_LAUNCH_CHECK();
         return launch_dw_reduce(workspace, grid, n_cols, dw, w_dt, st);

@@ -64,9 +64,10 @@ int hilda_norm_bwd(const void* dy, const void* ds, const void* x, const void* w,
  * slots filled by bulk asynchronous copies when three or more slots fit; else, and for 16-bit rows
  * always, the register kernel (one row in flight per CTA) with a bulk L2 prefetch of the CTA's next
  * row, in a lean form when a 16-bit row fills the plan exactly; 0 = register kernel, no prefetch;
- * 2 / 3 = register kernel with the prefetch 1 / 2 rows ahead; 4 = ring whenever two slots fit. dX is
- * the same bit for bit on every path, dW on every path that runs the same grid (the lean 16-bit
- * kernel runs fewer CTAs: its dW differs by the grouping of the partial sums). Other values only query. Returns the previous choice; per host thread.
+ * 2 / 3 = register kernel with the prefetch 1 / 2 rows ahead; 4 = ring whenever two slots fit. The
+ * explicitly chosen kernels (0, 2, 3, 4) and, for 32-bit rows, the automatic choice give the same dX
+ * and dW bit for bit; the lean 16-bit kernel of the automatic choice has a thread plan and a grid of
+ * its own, so its sums are grouped differently (same values within rounding). Other values only query. Returns the previous choice; per host thread.
  * Environment: HILDA_NORM_RING. */
 int hilda_norm_bwd_set_path(int path);
 

@@ -107,6 +107,69 @@ norm_fwd_kernel(const T* __restrict__ X, const T* __restrict__ R, const void* __
   }
 }
 
+// 16-bit rows without the residual stream, w in the data's dtype: the next row's loads are issued before
+// the current row is reduced (one row per CTA is in flight the whole time, not only while it loads), w
+// is held packed in registers, and the second rounding is the packed multiply itself:
+// round_T(round_T(x * rstd) * w) == hmul2(pack(x * rstd), w), the exact product rounded once.
+template <typename T, int THREADS, int VPT, bool FULL>
+__global__ void __launch_bounds__(THREADS)
+norm_fwd16_kernel(const T* __restrict__ X, const T* __restrict__ W, T* __restrict__ Y, float* __restrict__ RSTD,
+                  int64_t n_rows, int n_cols_rt, float eps) {
+  using P2 = typename std::conditional<std::is_same<T, __nv_bfloat16>::value, __nv_bfloat162, __half2>::type;
+  constexpr int VEC = 8;
+  const int n_cols = FULL ? VEC * THREADS * VPT : n_cols_rt;
+  const int n_vec = n_cols / VEC;
+  __shared__ float red[33];
+  const int tid = threadIdx.x;
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+  bool ok[VPT];
+  uint4 wv[VPT], cur[VPT], nxt[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    ok[i] = FULL || (tid + i * THREADS < n_vec);
+    wv[i] = ok[i] ? ld16(W + (tid + i * THREADS) * VEC) : zero4;
+  }
+  const int64_t step = (int64_t)gridDim.x * n_cols;
+  int64_t off = (int64_t)blockIdx.x * n_cols + (int64_t)tid * VEC;
+  if ((int64_t)blockIdx.x < n_rows) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) cur[i] = ok[i] ? ld16_stream(X + off + i * (THREADS * VEC)) : zero4;
+  }
+  for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x, off += step) {
+    const bool more = row + gridDim.x < n_rows;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) nxt[i] = (more && ok[i]) ? ld16_stream(X + off + step + i * (THREADS * VEC)) : zero4;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      float a[VEC];
+      VT<T>::unpack(cur[i], a);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) ss = fmaf(a[j], a[j], ss);
+    }
+    ss = block_sum<THREADS>(ss, red);
+    const float rstd = 1.0f / sqrtf(ss / (float)n_cols + eps);
+    if (tid == 0) RSTD[row] = rstd;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      if (ok[i]) {
+        float a[VEC];
+        VT<T>::unpack(cur[i], a);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) a[j] *= rstd;
+        uint4 n4 = VT<T>::pack(a);
+        P2* n2 = reinterpret_cast<P2*>(&n4);
+        const P2* w2 = reinterpret_cast<const P2*>(&wv[i]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) n2[j] = __hmul2(n2[j], w2[j]);
+        st16(Y + off + i * (THREADS * VEC), n4);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) cur[i] = nxt[i];
+  }
+}
+
 // Any n_cols (no alignment requirement): scalar access, row re-read from L1/L2.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -600,6 +663,14 @@ static NormPlan plan_norm(int64_t n_cols, int vec, int pref_vpt, bool all_aligne
     default: return HILDA_ERR_SIZE;                                                   \
   }
 
+// HILDA_NORM_FWD16=0 keeps the general forward kernel for every shape (comparisons). Measured on B200, bf16,
+// TB/s of x and y, lean against general: H = 3072 5.91 / 5.33, 4096 6.14 / 5.94, 5120 5.42 / 4.49, 7168 6.03 / 5.18,
+// 8192 6.13 / 5.42.
+static bool norm_fwd16_enabled() {
+  static const bool v = []() { const char* e = getenv("HILDA_NORM_FWD16"); return e ? atoi(e) != 0 : true; }();
+  return v;
+}
+
 template <typename T>
 static int norm_fwd_t(const void* x, const void* r, const void* w, int w_dt, void* y, void* s, float* rstd,
                       int64_t n_rows, int64_t n_cols, float eps, cudaStream_t st) {
@@ -618,6 +689,28 @@ static int norm_fwd_t(const void* x, const void* r, const void* w, int w_dt, voi
     return HILDA_OK;
   }
   int grid = (int)(n_rows < max_grid ? n_rows : max_grid);
+  if constexpr (sizeof(T) == 2) {
+    const int64_t nv16 = n_cols / 8;
+    if (!r && w_dt == (std::is_same<T, __nv_bfloat16>::value ? HILDA_BF16 : HILDA_F16) && nv16 > 128 && nv16 <= 1024 &&
+        ((plan.vpt == 4 && (plan.threads == 128 || plan.threads == 256)) || (plan.vpt == 2 && plan.threads == 128)) &&
+        norm_fwd16_enabled()) {
+#define F16_CALL(TH, VP, FU)                                                                                \
+  do {                                                                                                      \
+    int occ = 0;  /* rows are walked with a grid stride and prefetched: a grid of resident CTAs */           \
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, norm_fwd16_kernel<T, TH, VP, FU>, TH, 0) == cudaSuccess && \
+        occ > 0 && grid > occ * sm_count())                                                                 \
+      grid = occ * sm_count();                                                                              \
+    norm_fwd16_kernel<T, TH, VP, FU><<<grid, TH, 0, st>>>((const T*)x, (const T*)w, (T*)y, rstd, n_rows, (int)n_cols, eps); \
+  } while (0)
+      const bool fu = nv16 == (int64_t)plan.threads * plan.vpt;
+      if (plan.vpt == 2) { if (fu) F16_CALL(128, 2, true); else F16_CALL(128, 2, false); }
+      else if (plan.threads == 128) { if (fu) F16_CALL(128, 4, true); else F16_CALL(128, 4, false); }
+      else { if (fu) F16_CALL(256, 4, true); else F16_CALL(256, 4, false); }
+#undef F16_CALL
+      HILDA_LAUNCH_CHECK();
+      return HILDA_OK;
+    }
+  }
 #define FWD_CALL(TT, TH, VP)                                                                            \
   norm_fwd_kernel<TT, TH, VP><<<grid, TH, 0, st>>>((const TT*)x, (const TT*)r, w, w_dt, (TT*)y, (TT*)s, rstd, \
                                                     n_rows, (int)n_cols, eps)

@@ -242,7 +242,9 @@ static int rope_launch(const RopeArgs& a, bool vec_ok, cudaStream_t st) {
     if (vec_ok && tok > 0 && !a.s_inner && a.cs_dtype == Pk<T>::DT && inner <= 512) {
       const int threads = (int)((inner + 31) / 32 * 32);
       const int64_t n_tokens = outer;
-      const int per = tok >= 4 ? 4 : (tok >= 2 ? 2 : 1);
+      // four tokens per CTA take 92 registers per thread: above 341 threads only one such CTA fits an SM,
+      // and two tokens per CTA (50 registers, three CTAs) keep more loads in flight
+      const int per = (tok >= 4 && threads * 96 * 2 <= 65536) ? 4 : (tok >= 2 ? 2 : 1);
       const int64_t ctas = (n_tokens + per - 1) / per;
       if (per == 4) rope_tokens_kernel<T, 4><<<(unsigned)ctas, threads, 0, st>>>(a, (int)inner, n_tokens);
       else if (per == 2) rope_tokens_kernel<T, 2><<<(unsigned)ctas, threads, 0, st>>>(a, (int)inner, n_tokens);

@@ -678,7 +678,7 @@ static int norm_fwd_t(const void* x, const void* r, const void* w, int w_dt, voi
   // 16-bit rows without the residual stream keep four vectors per thread in flight (half as many threads
   // per row, twice as many rows per SM): bf16 [16384,4096] 5.90 against 4.98 TB/s, [8192,8192] 5.43 against
   // 3.89, [13107,5120] 4.49 against 2.94; with the residual stream two per thread measured best
-  const int pref = (sizeof(T) == 4) ? 4 : (r ? 2 : 4);
+  const int pref = (sizeof(T) == 4) ? 4 : ((r && n_cols <= 4096) ? 2 : 4);
   NormPlan plan = plan_norm(n_cols, VT<T>::N, pref, al);
   const int64_t max_grid = (int64_t)sm_count() * 64;
   if (plan.generic) {
@@ -802,16 +802,21 @@ static int norm_bwd_t(const void* dy, const void* ds, const void* x, const void*
     norm_bwd16_kernel<T, TH, VP, DS, FU><<<grid, TH, 0, st>>>((const T*)dy, (const T*)ds, (const T*)x, (const T*)w, rstd, \
                                                               (T*)dx, workspace, n_rows, (int)n_cols, 1);      \
   } while (0)
-#define B16_PICK(TH, VP)                                                                                      \
+        // The form without bounds flags only where it measured faster: two vectors per thread, no dS (bf16
+        // [16384,4096] 69.8 against 71.8 us). With dS, and with four vectors per thread, the compiler spills
+        // in that form and the flagged one is faster ([16384,4096] with dS 85.5 against 88.4 us, [8192,8192]
+        // 70.0 against 80.4, with dS 87.5 against 105.8).
+#define B16_PICK2(TH)                                                                                         \
   do {                                                                                                        \
-    const bool fu = n_vec16 == (int64_t)(TH) * (VP);                                                          \
-    if (ds) { if (fu) B16_CALL(TH, VP, true, true); else B16_CALL(TH, VP, true, false); }                     \
-    else { if (fu) B16_CALL(TH, VP, false, true); else B16_CALL(TH, VP, false, false); }                      \
+    if (ds) B16_CALL(TH, 2, true, false);                                                                     \
+    else if (n_vec16 == (int64_t)(TH) * 2) B16_CALL(TH, 2, false, true);                                      \
+    else B16_CALL(TH, 2, false, false);                                                                       \
   } while (0)
-        if (n_vec16 <= 256) B16_PICK(128, 2);
-        else if (n_vec16 <= 512) B16_PICK(256, 2);
-        else B16_PICK(256, 4);
-#undef B16_PICK
+        if (n_vec16 <= 256) B16_PICK2(128);
+        else if (n_vec16 <= 512) B16_PICK2(256);
+        else if (ds) B16_CALL(256, 4, true, false);
+        else B16_CALL(256, 4, false, false);
+#undef B16_PICK2
 #undef B16_CALL
         HILDA_LAUNCH_CHECK();
         return launch_dw_reduce(workspace, grid, n_cols, dw, w_dt, st);

@@ -222,6 +222,61 @@ __global__ void __launch_bounds__(512) rope_tokens_kernel(const RopeArgs a, int 
   }
 }
 
+// The same token structure for 16-bit q / k with fp32 tables (what the reference's RotaryEmbedding module
+// hands out: its cos / sin caches are fp32): arithmetic in fp32 with one rounding per operation, as the
+// reference does after casting x to the tables' dtype, result rounded to q's dtype.
+template <typename T, int TOK>
+__global__ void __launch_bounds__(512) rope_tokens_f32cs_kernel(const RopeArgs a, int items, int64_t n_tokens) {
+  const int i = threadIdx.x;
+  if (i >= items) return;
+  const unsigned vph = a.half / 8;
+  const unsigned mid = (unsigned)i / vph;
+  const int v = (int)((unsigned)i - mid * vph);
+  const int ti = ((int)mid >= a.t[0].n_heads) ? 1 : 0;
+  const RopeTensor& t = a.t[ti];
+  const int hh = ti ? (int)mid - a.t[0].n_heads : (int)mid;
+  const T* in = reinterpret_cast<const T*>(t.in) + hh * t.stride_h + (int64_t)v * 8;
+  T* out = reinterpret_cast<T*>(t.out) + hh * t.ostride_h + (int64_t)v * 8;
+  const float* cosp = reinterpret_cast<const float*>(a.cos) + (int64_t)v * 8;
+  const float* sinp = reinterpret_cast<const float*>(a.sin) + (int64_t)v * 8;
+  const float sign = a.sin_sign;
+  const int64_t tok0 = (int64_t)blockIdx.x * TOK;
+  uint4 X1[TOK], X2[TOK], C0[TOK], C1[TOK], S0[TOK], S1[TOK];
+  int64_t oo[TOK];
+#pragma unroll
+  for (int k = 0; k < TOK; ++k) {
+    const int64_t tok = tok0 + k;
+    if (tok < n_tokens) {
+      const int64_t b = tok / a.seq, s_ = tok - b * a.seq;
+      const T* p = in + b * t.stride_b + s_ * t.stride_s;
+      oo[k] = b * t.ostride_b + s_ * t.ostride_s;
+      X1[k] = ld16_once(p);
+      X2[k] = ld16_once(p + a.half);
+      const int64_t coff = b * a.cos_stride_b + s_ * a.cos_stride_s;
+      C0[k] = ld16(cosp + coff); C1[k] = ld16(cosp + coff + 4);
+      S0[k] = ld16(sinp + coff); S1[k] = ld16(sinp + coff + 4);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < TOK; ++k) {
+    if (tok0 + k < n_tokens) {
+      float x1[8], x2[8], c[8], sn[8], y1[8], y2[8];
+      VT<T>::unpack(X1[k], x1);
+      VT<T>::unpack(X2[k], x2);
+      VT<float>::unpack(C0[k], c); VT<float>::unpack(C1[k], c + 4);
+      VT<float>::unpack(S0[k], sn); VT<float>::unpack(S1[k], sn + 4);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float sj = sn[j] * sign;
+        y1[j] = __fsub_rn(__fmul_rn(x1[j], c[j]), __fmul_rn(x2[j], sj));
+        y2[j] = __fadd_rn(__fmul_rn(x2[j], c[j]), __fmul_rn(x1[j], sj));
+      }
+      st16(out + oo[k], VT<T>::pack(y1));
+      st16(out + oo[k] + a.half, VT<T>::pack(y2));
+    }
+  }
+}
+
 // tokens per CTA of the fast path: 0 = the general kernel; HILDA_ROPE_TOK presets it
 static int rope_tok_default() {
   static const int v = []() { const char* e = getenv("HILDA_ROPE_TOK"); return e ? atoi(e) : 4; }();
@@ -249,6 +304,13 @@ static int rope_launch(const RopeArgs& a, bool vec_ok, cudaStream_t st) {
       if (per == 4) rope_tokens_kernel<T, 4><<<(unsigned)ctas, threads, 0, st>>>(a, (int)inner, n_tokens);
       else if (per == 2) rope_tokens_kernel<T, 2><<<(unsigned)ctas, threads, 0, st>>>(a, (int)inner, n_tokens);
       else rope_tokens_kernel<T, 1><<<(unsigned)ctas, threads, 0, st>>>(a, (int)inner, n_tokens);
+      HILDA_LAUNCH_CHECK();
+      return HILDA_OK;
+    }
+    if (vec_ok && tok > 0 && !a.s_inner && a.cs_dtype == HILDA_F32 && inner <= 512) {
+      const int threads = (int)((inner + 31) / 32 * 32);
+      const int64_t ctas = (outer + 1) / 2;
+      rope_tokens_f32cs_kernel<T, 2><<<(unsigned)ctas, threads, 0, st>>>(a, (int)inner, outer);
       HILDA_LAUNCH_CHECK();
       return HILDA_OK;
     }

@@ -199,11 +199,28 @@ grpo_reduce_kernel(const float* __restrict__ loss, const float* __restrict__ kl,
   float a_loss = 0.f, a_kl = 0.f, a_clip = 0.f, a_mask = 0.f;
   for (int64_t b = wid; b < B; b += 32) {
     float sl = 0.f, sk = 0.f, sc = 0.f, sm = 0.f;
-    for (int64_t l = lane; l < L; l += 32) {
-      const int64_t i = b * L + l;
-      const float mv = mask ? mask[i] : 1.0f;
-      sl += loss[i] * mv; sc += clipped[i] * mv; sm += mv;
-      if (kl) sk += kl[i] * mv;
+    // eight positions of the lane at a time: their loads are all issued before the first sum (one CTA
+    // walks every sequence, so the chain of dependent round trips is what this kernel's time is made of);
+    // the sums stay in ascending position order
+    for (int64_t l0 = lane; l0 < L; l0 += 32 * 8) {
+      float vl[8], vk[8], vc[8], vm[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int64_t l = l0 + 32 * u;
+        const bool in = l < L;
+        const int64_t i = b * L + (in ? l : 0);
+        vm[u] = in ? (mask ? mask[i] : 1.0f) : 0.f;
+        vl[u] = in ? loss[i] : 0.f;
+        vc[u] = in ? clipped[i] : 0.f;
+        vk[u] = (in && kl) ? kl[i] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (l0 + 32 * u < L) {
+          sl += vl[u] * vm[u]; sc += vc[u] * vm[u]; sm += vm[u];
+          if (kl) sk += vk[u] * vm[u];
+        }
+      }
     }
     sl = warp_sum(sl); sk = warp_sum(sk); sc = warp_sum(sc); sm = warp_sum(sm);
     a_loss += sl / seq_len[b]; a_kl += sk; a_clip += sc; a_mask += sm;

@@ -147,6 +147,23 @@ __device__ __forceinline__ JsdTerm jsd_term(float x, float y, float beta, int mo
 
 __device__ __forceinline__ int jsd_mode(float beta) { return beta == 0.0f ? 0 : (beta == 1.0f ? 1 : 2); }
 
+// The general-beta term of 16-bit data in the log2 domain, with the constants taken out of the element:
+// with x2 = x log2(e), y2 = y log2(e), q = 2^x2, p = 2^y2, l = log2(beta p + (1 - beta) q),
+//   t = q (x2 - l), u = p (y2 - l):  loss = ln2 (beta u + (1 - beta) t),  dx = ln2 (1 - beta) t.
+// The kernel sums t and u and applies the constants once per row: 15 instructions per element instead of 18.
+// m is clamped to the smallest normal number instead of tested against 0: where both probabilities
+// underflow, t and u are 0 x finite = 0 as before.
+struct JsdFast { float t, u; };
+__device__ __forceinline__ JsdFast jsd_fast(float x, float y, float bp, float bq) {
+  const float x2 = x * DV_LOG2E, y2 = y * DV_LOG2E;
+  float q, p, l;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(q) : "f"(x2));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p) : "f"(y2));
+  const float m = fmaxf(fmaf(bp, p, bq * q), 1.17549435e-38f);
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(l) : "f"(m));
+  return JsdFast{q * (x2 - l), p * (y2 - l)};
+}
+
 // Stand-alone JSD (jsd.py:30-90): X, Y log-probs [n_rows, V]; one sweep writes dX = dx / n and the
 // row's loss / n, n = number of rows whose label is not ignore_index (all rows without labels).
 template <typename T>
@@ -161,7 +178,9 @@ jsd_rows_kernel(const T* __restrict__ X, const T* __restrict__ Y, T* __restrict_
   const bool vec_ok = aligned != 0;
   for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
     const bool ignored = labels && labels[row] == ignore_index;
-    float acc = 0.f;
+    float acc = 0.f, acc_t = 0.f, acc_u = 0.f;
+    const bool fast = sizeof(T) == 2 && mode == 2;
+    const float dx_c = DV_LN2 * (1.0f - beta) * inv_n;
     if (vec_ok) {
       // vectors over the aligned body of the row; the elements before and after it one by one
       const int64_t head = min((int64_t)((VEC - ((row * V) & (VEC - 1))) & (VEC - 1)), V);
@@ -196,21 +215,39 @@ jsd_rows_kernel(const T* __restrict__ X, const T* __restrict__ Y, T* __restrict_
           float xf[VEC], yf[VEC];
           VT<T>::unpack(xa, xf);
           VT<T>::unpack(ya, yf);
+          if (fast) {
 #pragma unroll
-          for (int j = 0; j < VEC; ++j) {
-            const JsdTerm t = jsd_term<sizeof(T) == 4>(xf[j], yf[j], beta, mode);
-            acc += t.loss;
-            xf[j] = t.dx * inv_n;
-          }
-          st16_stream(d + v * VEC, VT<T>::pack(xf));
-          if (has2) {
-            VT<T>::unpack(xb, xf);
-            VT<T>::unpack(yb, yf);
+            for (int j = 0; j < VEC; ++j) {
+              const JsdFast f = jsd_fast(xf[j], yf[j], beta, 1.0f - beta);
+              acc_t += f.t; acc_u += f.u;
+              xf[j] = f.t * dx_c;
+            }
+          } else {
 #pragma unroll
             for (int j = 0; j < VEC; ++j) {
               const JsdTerm t = jsd_term<sizeof(T) == 4>(xf[j], yf[j], beta, mode);
               acc += t.loss;
               xf[j] = t.dx * inv_n;
+            }
+          }
+          st16_stream(d + v * VEC, VT<T>::pack(xf));
+          if (has2) {
+            VT<T>::unpack(xb, xf);
+            VT<T>::unpack(yb, yf);
+            if (fast) {
+#pragma unroll
+              for (int j = 0; j < VEC; ++j) {
+                const JsdFast f = jsd_fast(xf[j], yf[j], beta, 1.0f - beta);
+                acc_t += f.t; acc_u += f.u;
+                xf[j] = f.t * dx_c;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < VEC; ++j) {
+                const JsdTerm t = jsd_term<sizeof(T) == 4>(xf[j], yf[j], beta, mode);
+                acc += t.loss;
+                xf[j] = t.dx * inv_n;
+              }
             }
             st16_stream(d + v2 * VEC, VT<T>::pack(xf));
           }
@@ -227,6 +264,7 @@ jsd_rows_kernel(const T* __restrict__ X, const T* __restrict__ Y, T* __restrict_
         VT<T>::store1(d + c, t.dx * inv_n);
       }
     }
+    acc += DV_LN2 * (beta * acc_u + (1.0f - beta) * acc_t);
     acc = block_sum<DV_THREADS>(acc, red);
     if (threadIdx.x == 0) loss_rows[row] = ignored ? 0.f : acc * inv_n;
   }

@@ -53,6 +53,8 @@ SIGNATURES = {
     "hilda_grpo_loss_fwd": (_i32, [_p] * 13 + [_i64, _i64, _i64, _i64, _f32, _f32, _f32, _f32, _i32, _p]),
     "hilda_selective_log_softmax": (_i32, [_p, _p, _p, _p, _i64, _i64, _i64, _f32, _i32, _p]),
     "hilda_row_engine_force": (None, [_i32, _i32, _i32]),
+    "hilda_row_engine_plan": (_i32, [_i64, _i32, _p]),
+    "hilda_row_engine_has_kernel": (_i32, [_i32, _i32, _i32, _i32]),
     "hilda_count_valid": (_i32, [_p, _i64, _i64, _p, _p]),
     "hilda_flce_logits_pitch": (_i64, [_i64]),
     "hilda_flce_padded_rows": (_i64, [_i64]),

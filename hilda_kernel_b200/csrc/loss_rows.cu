@@ -261,6 +261,22 @@ extern "C" {
 void hilda_row_engine_force(int nv, int cluster, int ns) {
   g_row_force_nv = nv; g_row_force_cluster = cluster; g_row_force_ns = ns;
 }
+// The plan the row engine takes for a vocabulary of V elements of `dtype` on aligned tensors (host only, no
+// GPU needed): out = {threads, register vectors, cluster, shared-memory vectors}. Returns 1, or 0 when
+// the scalar kernel serves the shape. hilda_row_engine_has_kernel says whether a plan is instantiated.
+int hilda_row_engine_plan(int64_t V, int dtype, int* out) {
+  const int vec = dtype == HILDA_F32 ? 4 : 8;
+  const RowPlan p = plan_row(V, vec, true, 0, 0, 0);
+  if (out) { out[0] = p.threads; out[1] = p.nv; out[2] = p.cluster; out[3] = p.ns; }
+  return p.generic ? 0 : 1;
+}
+int hilda_row_engine_has_kernel(int threads, int nv, int cluster, int ns) {
+#define ROW_HAS(TH_, NV_, CL_, NS_) if (threads == TH_ && nv == NV_ && cluster == CL_ && ns == NS_) return 1;
+  ROW_CFG_LIST(ROW_HAS)
+#undef ROW_HAS
+  return 0;
+}
+
 int64_t hilda_cross_entropy_workspace_bytes(int64_t n_rows) { return 16 + (n_rows > 0 ? n_rows : 0) * 4; }
 
 // workspace layout: int n_valid at byte 0, int status at byte 8, float loss_rows[n_rows] at byte 16 (only used when the

@@ -499,6 +499,18 @@ static int launch_row_cfg(const T* logits, T* grad, int64_t n_rows, int64_t V, c
   return e == cudaSuccess ? HILDA_OK : HILDA_ERR_CUDA;
 }
 
+// Every (threads, register vectors, cluster, shared-memory vectors) the kernel is instantiated for: what
+// plan_row may return, plus the register-only cluster plans the shared-memory ones replaced, kept for
+// comparisons through the override. One list for the dispatch and for hilda_row_engine_has_kernel.
+#define ROW_CFG_LIST(X)                                                          \
+  X(256, 1, 1, 0) X(256, 2, 1, 0) X(256, 4, 1, 0) X(256, 8, 1, 0)                 \
+  X(256, 8, 1, 4) X(256, 8, 1, 6) X(256, 8, 1, 8) X(256, 10, 1, 9)                \
+  X(256, 8, 2, 4) X(256, 8, 2, 6) X(256, 8, 2, 8) X(256, 10, 2, 9)                \
+  X(256, 8, 4, 4) X(256, 8, 4, 6) X(256, 8, 4, 8) X(256, 10, 4, 9)                \
+  X(256, 8, 8, 4) X(256, 8, 8, 6) X(256, 8, 8, 8) X(256, 10, 8, 9)                \
+  X(512, 10, 8, 9)                                                               \
+  X(256, 8, 8, 0) X(256, 10, 8, 0)
+
 // Override of the plan on the calling host thread, for tuning runs (0 = automatic).
 extern thread_local int g_row_force_nv, g_row_force_cluster, g_row_force_ns;
 
@@ -519,14 +531,7 @@ static int launch_rows(const void* logits_v, void* grad_v, int64_t n_rows, int64
 #define ROW_CFG(TH_, NV_, CL_, NS_) \
   if (p.threads == TH_ && p.nv == NV_ && p.cluster == CL_ && p.ns == NS_)  \
     return launch_row_cfg<T, TH_, NV_, CL_, Op, NS_>(logits, grad, n_rows, V, op, status, st);
-  ROW_CFG(256, 1, 1, 0) ROW_CFG(256, 2, 1, 0) ROW_CFG(256, 4, 1, 0) ROW_CFG(256, 8, 1, 0)
-  ROW_CFG(256, 8, 1, 4) ROW_CFG(256, 8, 1, 6) ROW_CFG(256, 8, 1, 8) ROW_CFG(256, 10, 1, 9)
-  ROW_CFG(256, 8, 2, 4) ROW_CFG(256, 8, 2, 6) ROW_CFG(256, 8, 2, 8) ROW_CFG(256, 10, 2, 9)
-  ROW_CFG(256, 8, 4, 4) ROW_CFG(256, 8, 4, 6) ROW_CFG(256, 8, 4, 8) ROW_CFG(256, 10, 4, 9)
-  ROW_CFG(256, 8, 8, 4) ROW_CFG(256, 8, 8, 6) ROW_CFG(256, 8, 8, 8) ROW_CFG(256, 10, 8, 9)
-  ROW_CFG(512, 10, 8, 9)
-  // the register-only cluster plans the shared-memory ones replaced, kept for comparisons through the override
-  ROW_CFG(256, 8, 8, 0) ROW_CFG(256, 10, 8, 0)
+  ROW_CFG_LIST(ROW_CFG)
 #undef ROW_CFG
   return HILDA_ERR_SIZE;
 }

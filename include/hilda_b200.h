@@ -357,6 +357,13 @@ int hilda_selective_log_softmax(const void* logits, const int64_t* ids, const fl
  * calling host thread only. No counterpart in the reference. */
 void hilda_row_engine_force(int nv, int cluster, int ns);
 
+/* Host-only queries (no GPU needed, no counterpart in the reference): the plan the row engine takes
+ * for rows of V elements of `dtype` on 16-byte aligned tensors, out = {threads, register vectors per
+ * thread, CTAs per cluster, shared-memory vectors per thread}; returns 1, or 0 when the scalar kernel
+ * serves the shape. hilda_row_engine_has_kernel: 1 if the kernel is instantiated for that plan. */
+int hilda_row_engine_plan(int64_t V, int dtype, int* out);
+int hilda_row_engine_has_kernel(int threads, int nv, int cluster, int ns);
+
 #ifdef __cplusplus
 }
 #endif

@@ -118,6 +118,32 @@ def test_kernel_choice_setters_and_split_plan_without_a_gpu():
     assert lib.hilda_paged_attention_fp8_workspace_bytes(0, 16, 8, 16, 256) == 256
 
 
+def test_row_engine_plan_covers_every_vocabulary_and_is_instantiated():
+    """Host-side only: for every vocabulary size in a dense sweep (and the published ones) the plan of the
+    CrossEntropy / GRPO row engine holds the whole row (threads x vectors per thread x cluster >= the row's
+    vectors), stays within the portable cluster size, and names a kernel the library was built with."""
+    import ctypes
+    import hilda_kernel_b200._lib as L
+    lib = L.lib()
+    out = (ctypes.c_int * 4)()
+    named = [32000, 32001, 32768, 49152, 50257, 50304, 65536, 100352, 102400, 128256, 129280, 151643, 151936, 152064,
+             200064, 201088, 256000, 262144]
+    sizes = sorted(set(named) | set(range(8, 4096, 7)) | set(range(4096, 330000, 509)))
+    for dtype, vec, limit in ((0, 4, 8 * 512 * 19 * 4), (1, 8, 8 * 512 * 19 * 8), (2, 8, 8 * 512 * 19 * 8)):
+        for v in sizes:
+            vector = lib.hilda_row_engine_plan(v, dtype, out)
+            th, nv, cl, ns = out[0], out[1], out[2], out[3]
+            if not vector:
+                assert v < 4 * vec or v // vec > limit // vec, (v, dtype)   # only tiny or huge rows take the scalar kernel
+                continue
+            assert cl in (1, 2, 4, 8) and th in (256, 512)
+            # the vectors are the aligned body of the row; up to vec - 1 elements before and after it are scalars
+            assert (nv + ns) * cl * th >= v // vec, (v, dtype, th, nv, cl, ns)
+            assert ns * th * 16 <= 100 * 1024
+            assert lib.hilda_row_engine_has_kernel(th, nv, cl, ns) == 1, (v, dtype, th, nv, cl, ns)
+    assert lib.hilda_row_engine_has_kernel(256, 8, 4, 5) == 0
+
+
 def test_top_level_kernels_package_like_the_reference_benches():
     """hilda-kernel's bench scripts put their package's parent directory first on sys.path and import
     ``kernels.<op>`` (benchmarks/bench_rms_norm.py:17-19, bench_rope.py:19, bench_grpo.py:6-8). With

@@ -202,7 +202,9 @@ class VocabParallelFLCE:
                 opts = dist.ProcessGroupNCCL.Options()
                 opts.config.max_ctas = max(1, self.overlap_sms)
                 opts.config.min_ctas = 1
-                self._reduce_group = dist.new_group(ranks, backend="nccl", pg_options=opts)
+                # only the members of self.group get here: the new group is agreed among them alone
+                self._reduce_group = dist.new_group(ranks, backend="nccl", pg_options=opts,
+                                                    use_local_synchronization=True)
         return self._reduce_group
 
     def _side_stream(self, dev):

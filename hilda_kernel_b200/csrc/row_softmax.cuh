@@ -169,7 +169,6 @@ constexpr int row_min_blocks(int threads, int nv) {
   return nv <= 10 ? (threads <= 256 ? 4 : (threads <= 320 ? 3 : 2)) : 2;
 }
 
-//
 // NS > 0: besides its NV register vectors a thread owns NS more vectors of the row in dynamic shared
 // memory (slot [j][tid], private to the thread, filled by 16-byte cp.async): the register file limits
 // a CTA to NV vectors per thread at four CTAs per SM, the idle shared memory holds the rest, so a row

@@ -69,8 +69,10 @@ def make_inputs(device, seed=4):
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 25 ms while the timed region runs (a default
-    run's region is 0.4 s at one GPU, 60 ms at eight)."""
+    """nvidia-smi clocks / throttle reasons sampled while the timed region runs. The sampler is started
+    before the warm-up steps (nvidia-smi needs some 100 ms to deliver its first line, and a default run's
+    region is 0.8 s at one GPU but 120 ms at eight) and every line is stamped on arrival; only the lines
+    that arrived inside the timed region are summarised."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
@@ -92,9 +94,10 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
 
-    def stop(self):
+    def stop(self, t0=None, t1=None):
+        """t0, t1: host times (time.perf_counter) that bracket the timed region."""
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -102,8 +105,13 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
+        rows = [r for t, r in self.rows if t0 is None or (t0 <= t <= t1 + 0.03)]
+        window = "timed region"
+        if len(rows) < 2 and t0 is not None:  # a very short region: the lines nearest to it, said so
+            rows = [r for t, r in self.rows if t0 - 0.25 <= t <= t1 + 0.25]
+            window = "timed region +- 0.25 s"
         sm, mx, power, reasons = [], [], [], set()
-        for r in self.rows:
+        for r in rows:
             try:
                 sm.append(float(r[1])); mx.append(float(r[2])); power.append(float(r[3]))
                 for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
@@ -113,7 +121,8 @@ class ClockSampler:
             except (ValueError, IndexError):
                 continue
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+                "power_w_max": max(power) if power else None, "samples": len(sm), "window": window,
+                "reasons": sorted(reasons)}
 
 
 def dist_env():
@@ -906,15 +915,17 @@ def run_ours(args):
             out = step()
             if i % 4 == 3:
                 torch.cuda.synchronize()
-    for _ in range(max(args.warmup, 3)):
-        out = step()
-    barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        out = step()
+    barrier()
     # the headline: K steps, nothing but the operator's own launches inside the timed region
+    t_region0 = time.perf_counter()
     ms_step, out = timed_steps(args.steps)
-    clocks = sampler.stop() if rank == 0 else None
+    t_region1 = time.perf_counter()
+    clocks = sampler.stop(t_region0, t_region1) if rank == 0 else None
     loss = float(out[0])
     value = BT / ms_step * 1e3
     # a second pass with every GEMM launch bracketed by CUDA events (the library's profile hook):
